@@ -1,0 +1,93 @@
+// Shared device helpers for the sm_100a kernels of mini_infer_b200.
+//
+// Every kernel is a template over the storage type of its activations and of
+// its weights (float or __nv_bfloat16); arithmetic is always float.  The
+// reference has the same helpers for FP16 only (src/kernels/warp_reduce.cuh:10-62).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mi {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// Error codes returned by the extern "C" launchers (0 = launched).
+enum Status : int {
+    kOk = 0,
+    kBadDType = -1,      // dtype code not 0/1 or a combination that is not built
+    kBadShape = -2,      // a size the kernel refuses (message in mi_last_error)
+    kLaunchFailed = -3,  // cudaGetLastError after the launch was not cudaSuccess
+};
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; `scratch` holds at least 32 floats.  All threads get the sum.
+// The order of additions depends only on blockDim, never on the data of other rows.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+void set_last_error(const char* fmt, ...);
+
+inline int finish_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_last_error("%s: %s", what, cudaGetErrorString(e));
+        return kLaunchFailed;
+    }
+    return kOk;
+}
+
+}  // namespace mi
+
+// Dispatch helpers: run `BODY` with `AT`/`WT` bound to the C++ types of the codes.
+#define MI_DISPATCH_1(code, T, ...)                                        \
+    do {                                                                   \
+        if ((code) == mi::kF32) { using T = float; __VA_ARGS__; }          \
+        else if ((code) == mi::kBF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else { mi::set_last_error("unknown dtype code %d", (int)(code)); return mi::kBadDType; } \
+    } while (0)
+
+#define MI_DISPATCH_2(acode, AT, wcode, WT, ...)                           \
+    MI_DISPATCH_1(acode, AT, MI_DISPATCH_1(wcode, WT, __VA_ARGS__))

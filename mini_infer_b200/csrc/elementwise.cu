@@ -1,0 +1,251 @@
+// Row-wise kernels: embedding gather, residual add + RMSNorm, bias + rotary
+// position encoding + cache write, SwiGLU, expert combine.
+//
+// Counterparts in the reference (all FP16, one op per kernel, default stream):
+//   embedding gather      src/kernels/model_utils_kernel.cu:45-64
+//   residual add          src/kernels/model_utils_kernel.cu:31-42
+//   RMSNorm               src/kernels/rmsnorm_kernel.cu:30-67
+//   bias add              src/kernels/model_utils_kernel.cu:11-28
+//   rotary tables + apply src/kernels/rope_kernel.cu:27-77
+//   cache scatter         src/kernels/model_utils_kernel.cu:108-164
+//   SwiGLU                src/kernels/swiglu_kernel.cu:16-26
+//   expert accumulate     src/kernels/moe_kernel.cu:65-146
+// Here the residual stream is float in both precision paths, sums are float,
+// and ops that follow one another on the same row are one kernel.
+
+#include "common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+
+namespace mi {
+
+static thread_local char g_last_error[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+    va_end(ap);
+}
+
+// ---------------------------------------------------------------------------
+// embedding: hidden[t, :] = table[ids[t], :]
+// ---------------------------------------------------------------------------
+template <typename WT>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
+                                    float* __restrict__ hidden, int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    // ids are validated on the host; clamp so that a bad id can never read outside the table
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const WT* row = table + (int64_t)id * H;
+    float* out = hidden + (int64_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+// ---------------------------------------------------------------------------
+// hidden += delta (optional); out = hidden * rsqrt(mean(hidden^2) + eps) * w
+// With `rows`, output row r is computed from hidden row rows[r] and hidden is
+// left untouched (the same row may be asked for twice).
+// ---------------------------------------------------------------------------
+template <typename AT, typename WT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
+                                   const int* __restrict__ rows, const WT* __restrict__ weight,
+                                   AT* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* h = hidden + (int64_t)src * H;
+    const float* d = delta ? delta + (int64_t)src * H : nullptr;
+    AT* o = out + (int64_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = h[i];
+        if (d) {
+            v += d[i];
+            if (!rows) h[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rrms = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = h[i];
+        if (d && rows) v += d[i];
+        o[i] = from_float<AT>(v * rrms * to_float(weight[i]));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// q/k/v post-processing for one token per block:
+//   add bias; rotate the first rot_dim dims of every q and k head by
+//   angle = position * inv_freq[i] (pairs (i, i + rot_dim/2));
+//   q -> q_out[t, head, :]; k, v -> cache slot slot_mapping[t]
+// cache layout per layer: [page, kv_head, page_size, d]
+// ---------------------------------------------------------------------------
+template <typename AT, typename WT>
+__global__ void qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
+                                const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                const int* __restrict__ slot_mapping, AT* __restrict__ q_out,
+                                AT* __restrict__ k_cache, AT* __restrict__ v_cache,
+                                int nh, int nkv, int d, int rot_dim, int page_size) {
+    const int t = blockIdx.x;
+    const int width = (nh + 2 * nkv) * d;
+    const float* row = qkv + (int64_t)t * width;
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1;
+    int64_t kbase = -1;
+    if (nkv > 0) {
+        const int slot = slot_mapping[t];
+        if (slot >= 0) {
+            const int page = slot / page_size, off = slot - page * page_size;
+            kbase = (int64_t)page * nkv * page_size * d + (int64_t)off * d;
+        }
+    }
+    // rotary pairs of q and k heads
+    const int n_rot_heads = nh + nkv;
+    for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const int c0 = head * d + i, c1 = c0 + half;
+        float x0 = row[c0], x1 = row[c1];
+        if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
+        float y0 = x0, y1 = x1;
+        if (inv_freq) {
+            const float ang = pos * inv_freq[i];
+            const float c = cosf(ang), s = sinf(ang);
+            y0 = x0 * c - x1 * s;
+            y1 = x1 * c + x0 * s;
+        }
+        if (head < nh) {
+            AT* q = q_out + ((int64_t)t * nh + head) * d;
+            q[i] = from_float<AT>(y0);
+            q[i + half] = from_float<AT>(y1);
+        } else if (kbase >= 0) {
+            AT* k = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
+            k[i] = from_float<AT>(y0);
+            k[i + half] = from_float<AT>(y1);
+        }
+    }
+    // dims beyond rot_dim of q and k heads pass through
+    const int rest = d - rot_dim;
+    if (rest > 0) {
+        for (int idx = threadIdx.x; idx < n_rot_heads * rest; idx += blockDim.x) {
+            const int head = idx / rest, i = rot_dim + (idx - head * rest);
+            const int c = head * d + i;
+            float x = row[c];
+            if (bias) x += to_float(bias[c]);
+            if (head < nh) q_out[((int64_t)t * nh + head) * d + i] = from_float<AT>(x);
+            else if (kbase >= 0) k_cache[kbase + (int64_t)(head - nh) * page_size * d + i] = from_float<AT>(x);
+        }
+    }
+    // v heads
+    if (kbase >= 0) {
+        for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+            const int head = idx / d, i = idx - head * d;
+            const int c = (nh + nkv) * d + idx;
+            float x = row[c];
+            if (bias) x += to_float(bias[c]);
+            v_cache[kbase + (int64_t)head * page_size * d + i] = from_float<AT>(x);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]
+// ---------------------------------------------------------------------------
+template <typename AT>
+__global__ void swiglu_kernel(const AT* __restrict__ gu, AT* __restrict__ out, int64_t total, int I) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float g = to_float(gu[t * 2 * I + i]);
+        const float u = to_float(gu[t * 2 * I + I + i]);
+        out[idx] = from_float<AT>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// out[t, :] = sum_k w[t, k] * y[inv_perm[t*K + k], :]   (k ascending: slot order)
+//           + gate[t] * shared[t, :]                     (if shared)
+// ---------------------------------------------------------------------------
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv_perm,
+                                   const float* __restrict__ w, const float* __restrict__ shared,
+                                   const float* __restrict__ gate, float* __restrict__ out, int H, int K) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < K; ++k) {
+            const int r = inv_perm[t * K + k];
+            acc += w[t * K + k] * y[(int64_t)r * H + i];
+        }
+        if (shared) acc += gate[t] * shared[(int64_t)t * H + i];
+        out[(int64_t)t * H + i] = acc;
+    }
+}
+
+}  // namespace mi
+
+using namespace mi;
+
+extern "C" {
+
+const char* mi_last_error() { return g_last_error; }
+
+int mi_embed_gather(const int* ids, const void* table, int wdtype, float* hidden, int T, int H, int V,
+                    cudaStream_t stream) {
+    if (T <= 0) return kOk;
+    MI_DISPATCH_1(wdtype, WT,
+        embed_gather_kernel<WT><<<T, 256, 0, stream>>>(ids, (const WT*)table, hidden, H, V));
+    return finish_launch("embed_gather");
+}
+
+int mi_add_rmsnorm(float* hidden, const float* delta, const int* rows, const void* weight, int wdtype,
+                   void* out, int adtype, int n_rows, int H, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return kOk;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        add_rmsnorm_kernel<AT, WT><<<n_rows, threads, 0, stream>>>(
+            hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+    return finish_launch("add_rmsnorm");
+}
+
+int mi_qkv_post(const float* qkv, const void* bias, int wdtype, const int* positions, const float* inv_freq,
+                const int* slot_mapping, void* q_out, void* k_cache, void* v_cache, int adtype,
+                int T, int nh, int nkv, int d, int rot_dim, int page_size, cudaStream_t stream) {
+    if (T <= 0) return kOk;
+    if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) {
+        set_last_error("qkv_post: rot_dim %d must be even and within head_dim %d", rot_dim, d);
+        return kBadShape;
+    }
+    if (!inv_freq) rot_dim = d;  // no rotation: treat all dims as "pairs" that are copied
+    if (d & 1) {
+        set_last_error("qkv_post: head_dim %d must be even", d);
+        return kBadShape;
+    }
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        qkv_post_kernel<AT, WT><<<T, 256, 0, stream>>>(
+            qkv, (const WT*)bias, positions, inv_freq, slot_mapping, (AT*)q_out, (AT*)k_cache,
+            (AT*)v_cache, nh, nkv, d, rot_dim, page_size));
+    return finish_launch("qkv_post");
+}
+
+int mi_swiglu(const void* gu, void* out, int adtype, int64_t T, int I, cudaStream_t stream) {
+    const int64_t total = T * I;
+    if (total <= 0) return kOk;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    MI_DISPATCH_1(adtype, AT,
+        swiglu_kernel<AT><<<(int)blocks, 256, 0, stream>>>((const AT*)gu, (AT*)out, total, I));
+    return finish_launch("swiglu");
+}
+
+int mi_moe_combine(const float* y, const int* inv_perm, const float* w, const float* shared,
+                   const float* gate, float* out, int T, int H, int K, cudaStream_t stream) {
+    if (T <= 0) return kOk;
+    moe_combine_kernel<<<T, 256, 0, stream>>>(y, inv_perm, w, shared, gate, out, H, K);
+    return finish_launch("moe_combine");
+}
+
+}  // extern "C"

@@ -1,0 +1,268 @@
+// Mixture-of-experts kernels: router (logits, softmax, top-k, shared gate),
+// token permutation, and the plain grouped expert products.
+//
+// The reference computes router logits with cuBLAS into FP16
+// (src/layers/moe.cpp:215-220), selects with one thread per token
+// (src/kernels/moe_kernel.cu:12-63), copies the indices to the host, runs every
+// used expert on all tokens and masks (src/layers/moe.cpp:239-270).  Here the
+// routing stays on the device: router logits are float dot products in a fixed
+// order per token, the (token, slot) pairs are sorted by expert with a stable
+// counting sort, and each expert multiplies only its own rows.
+
+#include "common.cuh"
+
+namespace mi {
+
+// ---------------------------------------------------------------------------
+// Router: one warp per token.
+//   z_e = x . Wr[e]              (float, lane-strided then butterfly sum)
+//   p = softmax(z) over all experts
+//   K rounds of arg-max over p, lowest index wins ties (moe_kernel.cu:28-47)
+//   w_k = p[idx_k]  (divided by their sum when norm_topk)
+//   gate = sigmoid(x . Wsg)      (moe_kernel.cu:137-139)
+// ---------------------------------------------------------------------------
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                  int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ gate,
+                  float* __restrict__ probs_out, int T, int H, int E, int K, int norm_topk) {
+    extern __shared__ float smem[];  // [4][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float* p = smem + warp * E;
+    const AT* xr = x + (int64_t)t * H;
+    for (int e = 0; e < E; ++e) {
+        const WT* w = wr + (int64_t)e * H;
+        float acc = 0.f;
+        for (int i = lane; i < H; i += 32) acc += to_float(xr[i]) * to_float(w[i]);
+        acc = warp_sum(acc);
+        if (lane == 0) p[e] = acc;
+    }
+    if (wsg) {
+        float acc = 0.f;
+        for (int i = lane; i < H; i += 32) acc += to_float(xr[i]) * to_float(wsg[i]);
+        acc = warp_sum(acc);
+        if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-acc));
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float v = expf(p[e] - mx);
+        p[e] = v;
+        sum += v;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+        const float v = p[e] / sum;
+        p[e] = v;
+        if (probs_out) probs_out[(int64_t)t * E + e] = v;
+    }
+    __syncwarp();
+    float wsum = 0.f;
+    float my_w = 0.f;  // lane k keeps weight k (K <= 32 checked on the host)
+    for (int k = 0; k < K; ++k) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = p[e];
+            if (v > best) { best = v; bi = e; }  // ascending e within a lane: first maximum kept
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == k) my_w = best;
+        wsum += best;
+        if (lane == 0) {
+            topk_idx[(int64_t)t * K + k] = bi;
+            p[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane < K) topk_w[(int64_t)t * K + lane] = norm_topk ? my_w / wsum : my_w;
+}
+
+// ---------------------------------------------------------------------------
+// Permutation (one block): counts per expert, exclusive scan, stable placement.
+//   offsets[E+1]; sorted_token[N] = token of sorted row; inv_perm[t*K+k] = sorted row
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, int* __restrict__ sorted_token,
+                   int* __restrict__ inv_perm, int N, int E, int K) {
+    extern __shared__ int sh[];  // [E+1]
+    const int tid = threadIdx.x;
+    for (int e = tid; e <= E; e += blockDim.x) sh[e] = 0;
+    __syncthreads();
+    for (int i = tid; i < N; i += blockDim.x) {
+        const int e = topk_idx[i];
+        if (e >= 0 && e < E) atomicAdd(&sh[e + 1], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e <= E; ++e) { run += sh[e]; sh[e] = run; }  // sh[e] = start of expert e
+    }
+    __syncthreads();
+    for (int e = tid; e <= E; e += blockDim.x) offsets[e] = sh[e];
+    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nwarps) {
+        int run = sh[e];
+        for (int base = 0; base < N; base += 32) {
+            const int i = base + lane;
+            const bool mine = (i < N) && (topk_idx[i] == e);
+            const unsigned bal = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int pos = run + __popc(bal & ((1u << lane) - 1u));
+                sorted_token[pos] = i / K;
+                inv_perm[i] = pos;
+            }
+            run += __popc(bal);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Plain grouped product (float arithmetic on CUDA cores; the 32-bit path and the
+// reference for the tensor-core kernels):
+//   rows r of expert e (offsets[e] <= r < offsets[e+1]), a_r = A[gather ? gather[r] : r, :]
+//   mode 0: C[r, n] = a_r . W[e, n, :]
+//   mode 1: C[r, n] = silu(a_r . W[e, n, :]) * (a_r . W[e, Nout + n, :])      (W is [E, 2*Nout, Kd])
+// Tiles of 32 rows x 32 columns; the k loop runs in steps of 32 in ascending
+// order whatever the number of rows, so a row's sum never depends on its neighbours.
+// ---------------------------------------------------------------------------
+constexpr int GB = 32;
+
+template <typename AT, typename WT, typename CT, int MODE>
+__global__ void __launch_bounds__(256)
+grouped_gemm_plain_kernel(const AT* __restrict__ A, const int* __restrict__ gather, const WT* __restrict__ W,
+                          const int* __restrict__ offsets, CT* __restrict__ C, int E, int Nout, int Kd) {
+    __shared__ float As[GB][GB + 1];
+    __shared__ float Ws[GB][GB + 1];
+    __shared__ float Us[MODE == 1 ? GB : 1][GB + 1];
+    // which expert and row tile does blockIdx.y stand for?
+    int slot = blockIdx.y, e = 0, row0 = 0, rows = 0;
+    bool found = false;
+    for (e = 0; e < E; ++e) {
+        const int b0 = offsets[e], cnt = offsets[e + 1] - b0;
+        const int tiles = (cnt + GB - 1) / GB;
+        if (slot < tiles) { row0 = b0 + slot * GB; rows = min(GB, cnt - slot * GB); found = true; break; }
+        slot -= tiles;
+    }
+    if (!found) return;
+    const int n0 = blockIdx.x * GB;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // ty 0..7, 4 rows each
+    const int wrows = MODE == 1 ? 2 * Nout : Nout;
+    const WT* We = W + (int64_t)e * wrows * Kd;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acu[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < Kd; k0 += GB) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < GB * GB; idx += 256) {
+            const int r = idx >> 5, c = idx & 31;
+            float av = 0.f, wv = 0.f, uv = 0.f;
+            if (k0 + c < Kd) {
+                if (r < rows) {
+                    const int src = gather ? gather[row0 + r] : row0 + r;
+                    av = to_float(A[(int64_t)src * Kd + k0 + c]);
+                }
+                if (n0 + r < Nout) {
+                    wv = to_float(We[(int64_t)(n0 + r) * Kd + k0 + c]);
+                    if (MODE == 1) uv = to_float(We[(int64_t)(Nout + n0 + r) * Kd + k0 + c]);
+                }
+            }
+            As[r][c] = av;
+            Ws[r][c] = wv;
+            if (MODE == 1) Us[r][c] = uv;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < GB; ++kk) {
+            const float wv = Ws[tx][kk];
+            const float uv = MODE == 1 ? Us[tx][kk] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float av = As[ty * 4 + i][kk];
+                acc[i] += av * wv;
+                if (MODE == 1) acu[i] += av * uv;
+            }
+        }
+    }
+    const int n = n0 + tx;
+    if (n < Nout) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = ty * 4 + i;
+            if (r < rows) {
+                float v = acc[i];
+                if (MODE == 1) v = v / (1.0f + expf(-v)) * acu[i];
+                C[(int64_t)(row0 + r) * Nout + n] = from_float<CT>(v);
+            }
+        }
+    }
+}
+
+}  // namespace mi
+
+using namespace mi;
+
+extern "C" {
+
+int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, int* topk_idx,
+                  float* topk_w, float* gate, float* probs_out, int T, int H, int E, int K, int norm_topk,
+                  cudaStream_t stream) {
+    if (T <= 0) return kOk;
+    if (K < 1 || K > 32 || K > E) {
+        set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
+        return kBadShape;
+    }
+    const size_t smem = sizeof(float) * 4 * (size_t)E;
+    if (smem > 48 * 1024) {
+        set_last_error("router: %d experts exceed the 3072 this kernel holds in shared memory", E);
+        return kBadShape;
+    }
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        moe_router_kernel<AT, WT><<<(T + 3) / 4, 128, smem, stream>>>(
+            (const AT*)x, (const WT*)wr, (const WT*)wsg, topk_idx, topk_w, gate, probs_out, T, H, E, K,
+            norm_topk));
+    return finish_launch("moe_router");
+}
+
+int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int T, int E, int K,
+                   cudaStream_t stream) {
+    if (E + 1 > 12000) {
+        set_last_error("permute: %d experts exceed the shared-memory table", E);
+        return kBadShape;
+    }
+    moe_permute_kernel<<<1, 1024, sizeof(int) * (E + 1), stream>>>(topk_idx, offsets, sorted_token, inv_perm,
+                                                                   T * K, E, K);
+    return finish_launch("moe_permute");
+}
+
+// Plain grouped product; `n_rows` is the total number of sorted rows (T*K), used for the grid only.
+// cdtype: type of C (0 float, 1 bfloat16).  mode 1 = SwiGLU pair (W holds 2*Nout rows per expert).
+int mi_grouped_gemm_plain(const void* A, int adtype, const int* gather, const void* W, int wdtype,
+                          const int* offsets, void* C, int cdtype, int n_rows, int E, int Nout, int Kd,
+                          int mode, cudaStream_t stream) {
+    if (n_rows <= 0) return kOk;
+    const int max_tiles = (n_rows + GB - 1) / GB + E;
+    if (max_tiles > 65535) {
+        set_last_error("grouped product: %d row tiles exceed the grid limit", max_tiles);
+        return kBadShape;
+    }
+    const dim3 grid((Nout + GB - 1) / GB, max_tiles);
+#define MI_GG(MODE)                                                                                     \
+    MI_DISPATCH_2(adtype, AT, wdtype, WT, MI_DISPATCH_1(cdtype, CT,                                     \
+        grouped_gemm_plain_kernel<AT, WT, CT, MODE><<<grid, 256, 0, stream>>>(                          \
+            (const AT*)A, gather, (const WT*)W, offsets, (CT*)C, E, Nout, Kd)))
+    if (mode == 0) MI_GG(0); else MI_GG(1);
+#undef MI_GG
+    return finish_launch("grouped_gemm_plain");
+}
+
+}  // extern "C"

@@ -1,0 +1,257 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch may hold portions of prompts beside single decoded tokens, cut
+anywhere; the step runs only the tokens it is given, as one flat batch of
+``T = sum(len(tokens))`` rows, reads everything older from the cache, and
+returns logits at the wanted places only.
+
+Reference: ``forward_paged_batched`` (src/model/transformer_model.h:128-143)
+takes a rectangle ``[B, S]`` that is either all prompts padded to a bucket or
+all single tokens (src/scheduler/scheduler.cpp:206-209, :298-300), needs the
+caller to have grown the block tables (src/layers/attention.h:106-108), and
+re-uploads the tables in every layer (src/layers/attention.cpp:783-814).  Here
+the batch is ragged, pages are reserved by the step itself (all or nothing),
+and the metadata crosses to the device once per step.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..parts.base import KVGroupView, Runtime, StepContext
+from .model import Model
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request, and the places among them whose logits are wanted."""
+
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepResult:
+    """``logits [R, V]`` float32 on the device (None if nothing was wanted); ``index[r]`` is
+    ``(request, place among its tokens of this step)`` of row ``r``."""
+
+    logits: Optional[torch.Tensor]
+    index: List[Tuple[Hashable, int]]
+    num_tokens: int
+
+
+class StepError(ValueError):
+    """The batch was refused before anything ran."""
+
+
+class ModelRunner:
+    """Owns the device side of the cache and runs steps.
+
+    ``num_pages`` pages of ``page_size`` tokens per cache group; at most
+    ``max_requests`` live requests (state slots), ``max_tokens_per_step`` rows per
+    step, ``max_context`` tokens per request.
+    """
+
+    def __init__(self, model: Model, rt: Runtime, *, page_size: int, num_pages: int, max_requests: int,
+                 max_tokens_per_step: int, max_context: int):
+        if rt.device.type != "cuda":
+            raise RuntimeError("ModelRunner: the engine runs on a CUDA device only; there is no CPU path")
+        self.model = model
+        self.rt = rt
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.max_tokens = int(max_tokens_per_step)
+        self.max_context = int(max_context)
+        self.vocab_size = model.spec.vocab_size
+        groups = model.kv_groups
+        self.cache = CacheManager(groups, [num_pages] * len(groups), page_size, max_requests)
+        dev, act = rt.device, rt.act
+        self.kv_tensors = []
+        for g in groups:
+            shape = (g.num_layers, num_pages, g.num_kv_heads, page_size, g.head_dim)
+            self.kv_tensors.append((torch.zeros(shape, dtype=act, device=dev),
+                                    torch.zeros(shape, dtype=act, device=dev)))
+        self.state_tensors = [torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype, device=dev)
+                              for _, need in model.state_needs]
+        self.scratch = {k: torch.empty(n, dtype=torch.float32, device=dev)
+                        for k, n in model.scratch_need(max_requests, max_context).items()}
+        self.max_pages = -(-self.max_context // self.page_size)
+        self._layout_staging()
+
+    # ------------------------------------------------------------------ #
+    # staging: one pinned buffer, one copy per step
+    # ------------------------------------------------------------------ #
+    def _layout_staging(self) -> None:
+        T, B, G = self.max_tokens, self.max_requests, len(self.model.kv_groups)
+        off = 0
+        self._sec: Dict[str, Tuple[int, int]] = {}
+
+        def sec(name, n):
+            nonlocal off
+            self._sec[name] = (off, n)
+            off += (n + 3) // 4 * 4      # keep every section 16-byte aligned
+
+        for name in ("token_ids", "positions", "req_of_token", "logit_rows"):
+            sec(name, T)
+        sec("q_start", B + 1)
+        for name in ("kv_len", "state_slot", "fresh"):
+            sec(name, B)
+        for g in range(G):
+            sec(f"slot_mapping{g}", T)
+            sec(f"block_table{g}", B * self.max_pages)
+        self._host = torch.zeros(off, dtype=torch.int32).pin_memory()
+        self._dev = torch.zeros(off, dtype=torch.int32, device=self.rt.device)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+
+    def _hview(self, name: str, n: int) -> torch.Tensor:
+        o, cap = self._sec[name]
+        return self._host[o:o + n]
+
+    def _dview(self, name: str, n: int) -> torch.Tensor:
+        o, cap = self._sec[name]
+        return self._dev[o:o + n]
+
+    # ------------------------------------------------------------------ #
+    # requests
+    # ------------------------------------------------------------------ #
+    def add_request(self, rid: Hashable) -> None:
+        slot = self.cache.add_request(rid)
+        for st in self.state_tensors:
+            st[slot].zero_()
+
+    def release(self, rid: Hashable) -> None:
+        self.cache.release(rid)
+
+    def has_request(self, rid: Hashable) -> bool:
+        return self.cache.has_request(rid)
+
+    def num_tokens(self, rid: Hashable) -> int:
+        return self.cache.num_tokens(rid)
+
+    # ------------------------------------------------------------------ #
+    # the step
+    # ------------------------------------------------------------------ #
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("step: empty batch")
+        if len(entries) > self.max_requests:
+            raise StepError(f"step: {len(entries)} requests exceed the limit {self.max_requests}")
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.rid in seen:
+                raise StepError(f"step: request {e.rid!r} appears twice in one batch")
+            seen.add(e.rid)
+            if not self.cache.has_request(e.rid):
+                raise StepError(f"step: unknown request {e.rid!r}")
+            n = len(e.tokens)
+            if n < 1:
+                raise StepError(f"step: request {e.rid!r} brings no tokens")
+            total += n
+            if self.cache.num_tokens(e.rid) + n > self.max_context:
+                raise StepError(f"step: request {e.rid!r} would reach {self.cache.num_tokens(e.rid) + n} "
+                                f"tokens, the context limit is {self.max_context}")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise StepError(f"step: token id {t} of request {e.rid!r} outside [0, {self.vocab_size})")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"step: wanted place {w} of request {e.rid!r} outside its {n} tokens")
+        if total > self.max_tokens:
+            raise StepError(f"step: {total} tokens exceed the budget {self.max_tokens}")
+
+    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, Optional[torch.Tensor], List]:
+        """Validate, reserve pages (all entries or none), stage and upload the metadata."""
+        self.validate(entries)
+        starts = []
+        done = []
+        try:
+            for e in entries:
+                starts.append(self.cache.reserve(e.rid, len(e.tokens)))
+                done.append(e.rid)
+        except OutOfPages:
+            for rid in done:
+                self.cache.cancel(rid)
+            raise
+        B = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        self._copied.synchronize()      # the previous step's upload has left the pinned buffer
+        h = self._hview
+        tok, pos, rot, rows = h("token_ids", T), h("positions", T), h("req_of_token", T), h("logit_rows", T)
+        qs, kvl, ss, fr = h("q_start", B + 1), h("kv_len", B), h("state_slot", B), h("fresh", B)
+        index: List[Tuple[Hashable, int]] = []
+        t0 = 0
+        max_q = max_kv = 0
+        host_kv, host_slot = [], []
+        tok_l, pos_l, rot_l, row_l = [], [], [], []
+        for b, (e, start) in enumerate(zip(entries, starts)):
+            n = len(e.tokens)
+            tok_l.extend(int(t) for t in e.tokens)
+            pos_l.extend(range(start, start + n))
+            rot_l.extend([b] * n)
+            qs[b] = t0
+            kvl[b] = start + n
+            ss[b] = self.cache.slot_of(e.rid)
+            fr[b] = 1 if start == 0 else 0
+            host_kv.append(start + n)
+            host_slot.append(self.cache.slot_of(e.rid))
+            for w in e.want:
+                row_l.append(t0 + int(w))
+                index.append((e.rid, int(w)))
+            max_q = max(max_q, n)
+            max_kv = max(max_kv, start + n)
+            t0 += n
+        qs[B] = T
+        tok[:] = torch.tensor(tok_l, dtype=torch.int32)
+        pos[:] = torch.tensor(pos_l, dtype=torch.int32)
+        rot[:] = torch.tensor(rot_l, dtype=torch.int32)
+        R = len(row_l)
+        if R:
+            rows[:R] = torch.tensor(row_l, dtype=torch.int32)
+        for g in range(len(self.model.kv_groups)):
+            sm = h(f"slot_mapping{g}", T)
+            bt = h(f"block_table{g}", B * self.max_pages).view(B, self.max_pages)
+            bt.fill_(-1)
+            sm_l = []
+            for b, (e, start) in enumerate(zip(entries, starts)):
+                table = self.cache.block_table(g, e.rid)
+                bt[b, :len(table)] = torch.tensor(table, dtype=torch.int32)
+                sm_l.extend(self.cache.slot_mapping(g, e.rid, start, len(e.tokens)))
+            sm[:] = torch.tensor(sm_l, dtype=torch.int32)
+        self._dev.copy_(self._host, non_blocking=True)
+        self._copied.record()
+        d = self._dview
+        views = []
+        for g in range(len(self.model.kv_groups)):
+            k, v = self.kv_tensors[g]
+            views.append(KVGroupView(
+                block_table=d(f"block_table{g}", B * self.max_pages).view(B, self.max_pages),
+                slot_mapping=d(f"slot_mapping{g}", T), page_size=self.page_size, k=k, v=v))
+        ctx = StepContext(
+            num_tokens=T, num_requests=B, max_q_len=max_q, max_kv_len=max_kv, all_decode=(max_q == 1),
+            token_ids=d("token_ids", T), positions=d("positions", T), q_start=d("q_start", B + 1),
+            kv_len=d("kv_len", B), req_of_token=d("req_of_token", T), state_slot=d("state_slot", B),
+            fresh=d("fresh", B), kv_groups=views, states=self.state_tensors, scratch=self.scratch,
+            host_q_start=[int(x) for x in qs.tolist()], host_kv_len=host_kv, host_state_slot=host_slot)
+        logit_rows = d("logit_rows", R) if R else None
+        return ctx, logit_rows, index
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> StepResult:
+        ctx, logit_rows, index = self.prepare(entries)
+        try:
+            logits = self.model.forward(ctx, logit_rows)
+        except Exception:
+            for e in entries:
+                self.cache.cancel(e.rid)
+            raise
+        for e in entries:
+            self.cache.commit(e.rid)
+        return StepResult(logits, index, ctx.num_tokens)

@@ -1,0 +1,317 @@
+"""Python faces of the CUDA kernels: check the tensors, pass the pointers.
+
+Every function runs on the current CUDA stream of the tensors' device and
+returns its output tensor.  Shapes a kernel cannot take are refused with an
+error; nothing falls back to PyTorch.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .library import check, library
+
+F32 = torch.float32
+BF16 = torch.bfloat16
+I32 = torch.int32
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise TypeError(f"{what}: dtype {t.dtype} is not float32 or bfloat16") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _chk(t: Optional[torch.Tensor], what: str, dtype=None, shape=None) -> None:
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: tensor is on {t.device}; the kernels run on CUDA only and have no fallback")
+    if not t.is_contiguous():
+        raise ValueError(f"{what}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{what}: expected {dtype}, got {t.dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(s is not None and s != a for s, a in zip(shape, t.shape)):
+            raise ValueError(f"{what}: expected shape {list(shape)}, got {list(t.shape)}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# --------------------------------------------------------------------------- #
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` as float32 ``[T, H]``."""
+    _chk(ids, "embed_gather ids", I32)
+    _chk(table, "embed_gather table")
+    T = ids.numel()
+    V, H = table.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=F32, device=table.device)
+    _chk(out, "embed_gather out", F32, (T, H))
+    check(library().mi_embed_gather(_ptr(ids), _ptr(table), _code(table, "embed_gather table"), _ptr(out),
+                                    T, H, V, _stream()), "embed_gather")
+    return out
+
+
+def add_rmsnorm(hidden: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hidden += delta`` (if given; written back unless ``rows``), then RMSNorm.
+
+    ``rows`` (int32) selects and orders the rows to normalise; ``hidden`` is then
+    left untouched.
+    """
+    _chk(hidden, "add_rmsnorm hidden", F32)
+    T, H = hidden.shape
+    _chk(delta, "add_rmsnorm delta", F32, (T, H))
+    _chk(weight, "add_rmsnorm weight", None, (H,))
+    _chk(rows, "add_rmsnorm rows", I32)
+    n = T if rows is None else rows.numel()
+    if out is None:
+        out = torch.empty(n, H, dtype=out_dtype, device=hidden.device)
+    _chk(out, "add_rmsnorm out", out_dtype, (n, H))
+    check(library().mi_add_rmsnorm(_ptr(hidden), _ptr(delta), _ptr(rows), _ptr(weight),
+                                   _code(weight, "add_rmsnorm weight"), _ptr(out), _code(out, "add_rmsnorm out"),
+                                   n, H, float(eps), _stream()), "add_rmsnorm")
+    return out
+
+
+def qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+             inv_freq: Optional[torch.Tensor], rot_dim: int, slot_mapping: Optional[torch.Tensor],
+             k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], nh: int, nkv: int, d: int,
+             page_size: int, out_dtype: torch.dtype, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Bias, rotary position encoding of q and k, cache write of k and v.
+
+    ``qkv`` is float32 ``[T, (nh + 2*nkv) * d]`` (``nkv = 0``: queries only, nothing
+    is written).  ``k_cache``/``v_cache`` are one layer's ``[pages, nkv, page_size, d]``.
+    Returns ``q [T, nh, d]`` in ``out_dtype``.
+    """
+    _chk(qkv, "qkv_post qkv", F32)
+    T = qkv.shape[0]
+    width = (nh + 2 * nkv) * d
+    _chk(qkv, "qkv_post qkv", F32, (T, width))
+    _chk(bias, "qkv_post bias", None, (width,))
+    _chk(positions, "qkv_post positions", I32, (T,))
+    _chk(inv_freq, "qkv_post inv_freq", F32)
+    if inv_freq is not None and inv_freq.numel() != rot_dim // 2:
+        raise ValueError(f"qkv_post: {inv_freq.numel()} frequencies for {rot_dim} rotary dims")
+    if nkv > 0:
+        _chk(slot_mapping, "qkv_post slot_mapping", I32, (T,))
+        _chk(k_cache, "qkv_post k_cache", out_dtype, (None, nkv, page_size, d))
+        _chk(v_cache, "qkv_post v_cache", out_dtype, (None, nkv, page_size, d))
+        if slot_mapping is None or k_cache is None or v_cache is None:
+            raise ValueError("qkv_post: key/value heads need a cache and a slot mapping")
+    if q_out is None:
+        q_out = torch.empty(T, nh, d, dtype=out_dtype, device=qkv.device)
+    _chk(q_out, "qkv_post q_out", out_dtype, (T, nh, d))
+    wcode = _code(bias, "qkv_post bias") if bias is not None else 0
+    check(library().mi_qkv_post(_ptr(qkv), _ptr(bias), wcode, _ptr(positions), _ptr(inv_freq),
+                                _ptr(slot_mapping), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                _code(q_out, "qkv_post q_out"), T, nh, nkv, d, rot_dim, page_size, _stream()),
+          "qkv_post")
+    return q_out
+
+
+def swiglu(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gu[:, :I]) * gu[:, I:]`` for ``gu [T, 2I]``."""
+    _chk(gu, "swiglu input")
+    T, two_i = gu.shape
+    if two_i % 2:
+        raise ValueError("swiglu: the input width must be even (gate | up)")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty(T, inter, dtype=gu.dtype, device=gu.device)
+    _chk(out, "swiglu out", gu.dtype, (T, inter))
+    check(library().mi_swiglu(_ptr(gu), _ptr(out), _code(gu, "swiglu input"), T, inter, _stream()), "swiglu")
+    return out
+
+
+def moe_combine(y: torch.Tensor, inv_perm: torch.Tensor, weights: torch.Tensor,
+                shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = sum_k weights[t,k] * y[inv_perm[t,k]] + gate[t] * shared[t]`` (float32)."""
+    T, K = weights.shape
+    _chk(y, "moe_combine y", F32, (T * K, None))
+    H = y.shape[1]
+    _chk(inv_perm, "moe_combine inv_perm", I32)
+    _chk(weights, "moe_combine weights", F32)
+    _chk(shared, "moe_combine shared", F32, (T, H))
+    _chk(gate, "moe_combine gate", F32, (T,))
+    if (shared is None) != (gate is None):
+        raise ValueError("moe_combine: shared output and gate come together")
+    if out is None:
+        out = torch.empty(T, H, dtype=F32, device=y.device)
+    _chk(out, "moe_combine out", F32, (T, H))
+    check(library().mi_moe_combine(_ptr(y), _ptr(inv_perm), _ptr(weights), _ptr(shared), _ptr(gate), _ptr(out),
+                                   T, H, K, _stream()), "moe_combine")
+    return out
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+              q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int, window: int = 0,
+              scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of a ragged batch over the paged cache (tiled kernel, any head size <= 256)."""
+    _chk(q, "attention q")
+    T, nh, d = q.shape
+    _chk(k_cache, "attention k_cache", q.dtype)
+    _, nkv, page_size, d2 = k_cache.shape
+    _chk(v_cache, "attention v_cache", q.dtype, tuple(k_cache.shape))
+    if d2 != d:
+        raise ValueError(f"attention: head_dim of q ({d}) and of the cache ({d2}) differ")
+    _chk(block_table, "attention block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "attention q_start", I32, (B + 1,))
+    _chk(kv_len, "attention kv_len", I32, (B,))
+    if out is None:
+        out = torch.empty_like(q)
+    _chk(out, "attention out", q.dtype, (T, nh, d))
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    check(library().mi_attn_tiled(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention q"),
+                                  _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len),
+                                  nh, nkv, d, page_size, max_pages, int(window), float(scale), _stream()),
+          "attention")
+    return out
+
+
+def decode_attention_supported(d: int) -> bool:
+    return bool(library().mi_attn_decode_supported(int(d)))
+
+
+def decode_split_size() -> int:
+    return int(library().mi_attn_decode_split_size())
+
+
+def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                     q_start: torch.Tensor, kv_len: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                     max_splits: int, window: int = 0, scale: Optional[float] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Split-KV attention when every request brings exactly one token.
+
+    ``part_o`` (``>= B*nh*max_splits*d`` floats) and ``part_ml`` (``>= B*nh*max_splits*2``)
+    are scratch; ``max_splits >= ceil(longest kv_len / decode_split_size())``.
+    """
+    _chk(q, "decode_attention q")
+    T, nh, d = q.shape
+    _chk(k_cache, "decode_attention k_cache", q.dtype)
+    _, nkv, page_size, d2 = k_cache.shape
+    _chk(v_cache, "decode_attention v_cache", q.dtype, tuple(k_cache.shape))
+    if d2 != d:
+        raise ValueError(f"decode_attention: head_dim of q ({d}) and of the cache ({d2}) differ")
+    _chk(block_table, "decode_attention block_table", I32)
+    B, max_pages = block_table.shape
+    if T != B:
+        raise ValueError(f"decode_attention: {T} tokens for {B} requests; each request brings exactly one")
+    _chk(q_start, "decode_attention q_start", I32, (B + 1,))
+    _chk(kv_len, "decode_attention kv_len", I32, (B,))
+    _chk(part_o, "decode_attention part_o", F32)
+    _chk(part_ml, "decode_attention part_ml", F32)
+    if part_o.numel() < B * nh * max_splits * d or part_ml.numel() < B * nh * max_splits * 2:
+        raise ValueError("decode_attention: scratch too small for this batch and split count")
+    if out is None:
+        out = torch.empty_like(q)
+    _chk(out, "decode_attention out", q.dtype, (T, nh, d))
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    check(library().mi_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "decode_attention q"),
+                                   _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o),
+                                   _ptr(part_ml), B, nh, nkv, d, page_size, max_pages, int(max_splits),
+                                   int(window), float(scale), _stream()), "decode_attention")
+    return out
+
+
+def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
+               norm_topk: bool, want_probs: bool = False
+               ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Router of one layer.  Returns ``(idx [T,K] int32, w [T,K] f32, gate [T] f32 | None, probs | None)``."""
+    _chk(x, "moe_router x")
+    T, H = x.shape
+    _chk(router_w, "moe_router weight", None, (None, H))
+    E = router_w.shape[0]
+    if shared_gate_w is not None:
+        _chk(shared_gate_w, "moe_router shared gate", router_w.dtype)
+        if shared_gate_w.numel() != H:
+            raise ValueError("moe_router: the shared-expert gate must have hidden_size entries")
+    dev = x.device
+    idx = torch.empty(T, top_k, dtype=I32, device=dev)
+    w = torch.empty(T, top_k, dtype=F32, device=dev)
+    gate = torch.empty(T, dtype=F32, device=dev) if shared_gate_w is not None else None
+    probs = torch.empty(T, E, dtype=F32, device=dev) if want_probs else None
+    check(library().mi_moe_router(_ptr(x), _code(x, "moe_router x"), _ptr(router_w), _ptr(shared_gate_w),
+                                  _code(router_w, "moe_router weight"), _ptr(idx), _ptr(w), _ptr(gate),
+                                  _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _stream()),
+          "moe_router")
+    return idx, w, gate, probs
+
+
+def moe_permute(topk_idx: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Stable sort of the (token, slot) pairs by expert.
+
+    Returns ``(offsets [E+1], sorted_token [T*K], inv_perm [T*K])``, all int32.
+    """
+    _chk(topk_idx, "moe_permute idx", I32)
+    T, K = topk_idx.shape
+    dev = topk_idx.device
+    offsets = torch.empty(num_experts + 1, dtype=I32, device=dev)
+    sorted_token = torch.empty(T * K, dtype=I32, device=dev)
+    inv_perm = torch.empty(T * K, dtype=I32, device=dev)
+    check(library().mi_moe_permute(_ptr(topk_idx), _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T,
+                                   int(num_experts), K, _stream()), "moe_permute")
+    return offsets, sorted_token, inv_perm
+
+
+def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
+                       n_rows: int, swiglu_pair: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per-expert product of sorted rows (float arithmetic).
+
+    ``w`` is ``[E, Nout, K]`` or, with ``swiglu_pair``, ``[E, 2*Nout, K]`` (gate rows,
+    then up rows) and the result is ``silu(gate) * up``.  Row ``r`` of the result
+    uses ``a[gather[r]]`` (or ``a[r]``) and the expert whose offset range holds ``r``.
+    """
+    _chk(a, "grouped_gemm a")
+    Kd = a.shape[1]
+    _chk(w, "grouped_gemm w", None, (None, None, Kd))
+    E, wrows, _ = w.shape
+    nout = wrows // 2 if swiglu_pair else wrows
+    _chk(gather, "grouped_gemm gather", I32)
+    _chk(offsets, "grouped_gemm offsets", I32, (E + 1,))
+    out = torch.empty(n_rows, nout, dtype=out_dtype, device=a.device)
+    check(library().mi_grouped_gemm_plain(_ptr(a), _code(a, "grouped_gemm a"), _ptr(gather), _ptr(w),
+                                          _code(w, "grouped_gemm w"), _ptr(offsets), _ptr(out),
+                                          _code(out, "grouped_gemm out"), int(n_rows), E, nout, Kd,
+                                          1 if swiglu_pair else 0, _stream()), "grouped_gemm_plain")
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+                top_p: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
+                probs_scratch: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 ``logits [R, V]``; rows with temperature <= 0 are greedy."""
+    _chk(logits, "sample_rows logits", F32)
+    R, V = logits.shape
+    _chk(temperature, "sample_rows temperature", F32, (R,))
+    _chk(top_p, "sample_rows top_p", F32, (R,))
+    _chk(u, "sample_rows u", F32, (R,))
+    if temperature is not None and probs_scratch is None:
+        probs_scratch = torch.empty(R, V, dtype=F32, device=logits.device)
+    _chk(probs_scratch, "sample_rows scratch", F32, (R, V))
+    if out is None:
+        out = torch.empty(R, dtype=I32, device=logits.device)
+    _chk(out, "sample_rows out", I32, (R,))
+    check(library().mi_sample_rows(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(u), _ptr(probs_scratch),
+                                   _ptr(out), R, V, _stream()), "sample_rows")
+    return out

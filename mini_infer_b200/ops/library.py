@@ -1,0 +1,74 @@
+"""Load the CUDA library and declare its C entry points.
+
+There is exactly one way to run an op: through this library, on a CUDA device.
+If it cannot be built or loaded the import of an op fails with the reason; no
+op has a CPU or PyTorch fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from typing import Optional
+
+_lib: Optional[ctypes.CDLL] = None
+_lib_path: Optional[str] = None
+
+P = c_void_p
+I = c_int
+F = c_float
+L = c_int64
+
+_SIGNATURES = {
+    "mi_embed_gather": [P, P, I, P, I, I, I, P],
+    "mi_add_rmsnorm": [P, P, P, P, I, P, I, I, I, F, P],
+    "mi_qkv_post": [P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+    "mi_swiglu": [P, P, I, L, I, P],
+    "mi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
+    "mi_attn_tiled": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "mi_attn_decode": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "mi_moe_router": [P, I, P, P, I, P, P, P, P, I, I, I, I, I, P],
+    "mi_moe_permute": [P, P, P, P, I, I, I, P],
+    "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],
+    "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded library; built at the first call of a fresh checkout."""
+    global _lib, _lib_path
+    if _lib is not None:
+        return _lib
+    from ..csrc.build import build
+    path = build()
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        raise RuntimeError(f"mini_infer_b200: cannot load {path}: {e}") from e
+    for name, argtypes in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    lib.mi_last_error.restype = c_char_p
+    lib.mi_last_error.argtypes = []
+    lib.mi_attn_decode_supported.argtypes = [I]
+    lib.mi_attn_decode_supported.restype = c_int
+    lib.mi_attn_decode_split_size.argtypes = []
+    lib.mi_attn_decode_split_size.restype = c_int
+    _lib = lib
+    _lib_path = path
+    return lib
+
+
+def library_path() -> Optional[str]:
+    return _lib_path
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = library().mi_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{what} refused or failed (code {code}): {msg}")

@@ -1,0 +1,109 @@
+"""Grouped-query attention over the paged cache.
+
+Reference: src/layers/attention.cpp:666-878 (three cuBLAS products, three bias
+kernels, two rotary kernels, two scatter kernels, the paged attention kernel,
+one more product, with block tables rebuilt and uploaded in every layer).
+Here: one library product for q, k and v together, one kernel for bias +
+rotation + cache write, one attention kernel chosen by the shape of the batch,
+one library product for the output.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.registry import part_class, register_part
+from ..config.spec import PartSpec
+from ..ops import functional as F
+from .base import CacheBinding, KVNeed, Mixer, Runtime, StepContext, TensorDecl, linear
+
+
+class GQAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``bias``
+    (q/k/v projections carry a bias), ``window`` (0 = all keys), ``position``
+    (a ``PartSpec`` of category ``position``), ``shares_cache`` (this layer has no
+    k/v projections and reads the cache another schedule entry wrote).
+
+    Tensors: ``<prefix>{q,k,v}_proj.weight [out, hidden]``, ``.bias [out]`` if
+    ``bias``, ``<prefix>o_proj.weight [hidden, num_heads*head_dim]``.
+    """
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = self.params
+        self.H = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.d = int(p["head_dim"])
+        self.bias = bool(p.get("bias", False))
+        self.window = int(p.get("window", 0))
+        self.shares_cache = bool(p.get("shares_cache", False))
+        pos: PartSpec = p.get("position") or PartSpec("none")
+        self.position = part_class("position", pos.kind)(pos.params, prefix)
+        if self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
+        if self.d % 2 or not 2 <= self.d <= 256:
+            raise ValueError(f"attention: head_dim {self.d} must be even and at most 256")
+
+    # -- weights ----------------------------------------------------------- #
+    def _proj_names(self) -> List[str]:
+        return ["q_proj"] if self.shares_cache else ["q_proj", "k_proj", "v_proj"]
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        out = []
+        for n in self._proj_names():
+            rows = (self.nh if n == "q_proj" else self.nkv) * self.d
+            out.append(TensorDecl(f"{self.prefix}{n}.weight", (rows, self.H), "matrix"))
+            if self.bias:
+                out.append(TensorDecl(f"{self.prefix}{n}.bias", (rows,), "bias"))
+        out.append(TensorDecl(f"{self.prefix}o_proj.weight", (self.H, self.nh * self.d), "matrix"))
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        prec, dev = rt.precision, rt.device
+        names = self._proj_names()
+        self.w_qkv = torch.cat([prec.matrix(tensors[f"{self.prefix}{n}.weight"], dev) for n in names], dim=0)
+        self.b_qkv = None
+        if self.bias:
+            bs = [prec.small(tensors[f"{self.prefix}{n}.bias"], dev) for n in names]
+            if len({b.dtype for b in bs}) > 1:
+                bs = [b.float() for b in bs]
+            self.b_qkv = torch.cat(bs, dim=0).contiguous()
+        self.w_o = prec.matrix(tensors[f"{self.prefix}o_proj.weight"], dev)
+        self.inv_freq = self.position.table(dev)
+        self.rot_dim = self.position.rot_dim if self.inv_freq is not None else self.d
+
+    # -- cache ------------------------------------------------------------- #
+    def cache_need(self):
+        return KVNeed(self.nkv, self.d, self.window)
+
+    def scratch_need(self, max_requests: int, max_context: int) -> Dict[str, int]:
+        if not F.decode_attention_supported(self.d):
+            return {}
+        splits = -(-max_context // F.decode_split_size())
+        return {"attn_part_o": max_requests * self.nh * splits * self.d,
+                "attn_part_ml": max_requests * self.nh * splits * 2}
+
+    # -- forward ----------------------------------------------------------- #
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        view = ctx.kv_groups[cache.group]
+        kc = view.k[cache.layer_slot]
+        vc = view.v[cache.layer_slot]
+        qkv = linear(x, self.w_qkv, torch.float32)
+        nkv_in = 0 if self.shares_cache else self.nkv
+        q = F.qkv_post(qkv, self.b_qkv, ctx.positions, self.inv_freq, self.rot_dim,
+                       view.slot_mapping if nkv_in else None, kc if nkv_in else None, vc if nkv_in else None,
+                       self.nh, nkv_in, self.d, view.page_size, self.rt.act)
+        if ctx.all_decode and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d):
+            splits = -(-ctx.max_kv_len // F.decode_split_size())
+            a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
+                                   ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window)
+        else:
+            a = F.attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
+        return linear(a.view(ctx.num_tokens, self.nh * self.d), self.w_o, torch.float32)
+
+
+register_part("mixer", "gqa_attention", GQAttention)

@@ -1,0 +1,281 @@
+"""Interfaces of the parts a model is put together from.
+
+A part is built from a :class:`~mini_infer_b200.config.spec.PartSpec` (its kind
+and constants) and a checkpoint prefix; it declares the tensors it needs,
+takes them at load time, and runs on the tensors the step hands it.  No part
+imports a model or asks which model it is in.
+
+Categories and what each must provide:
+
+``norm``          ``apply(hidden, delta, rows) -> normed``: add ``delta`` into the
+                  float32 residual stream ``hidden`` (if given) and return the
+                  normalised rows in the activation dtype.
+``position``      ``table(device)`` and ``rot_dim``: the rotation frequencies the
+                  attention kernels apply to queries and keys (or none).
+``mixer``         ``cache_need()`` (what it keeps per token or per request),
+                  ``forward(x, ctx, cache) -> y`` with ``x [T, H]`` activations and
+                  ``y [T, H]`` float32.
+``feed_forward``  ``forward(x, ctx) -> y``, same shapes.
+``block``         ``forward(layer, hidden, pending, ctx, cache) -> pending``: the
+                  arrangement of norms, mixer and feed-forward around the residual.
+``embedding``     ``forward(token_ids) -> hidden`` float32.
+``lm_head``       ``forward(x) -> logits`` float32.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+
+# --------------------------------------------------------------------------- #
+# tensors a part expects in the checkpoint
+# --------------------------------------------------------------------------- #
+
+@dataclass(frozen=True)
+class TensorDecl:
+    """One checkpoint tensor: full name, shape, and its role.
+
+    ``role`` decides the random initialisation (``matrix``, ``bias``: N(0, 0.02);
+    ``norm``: 1 + N(0, 0.02)) and the storage rule: in the bfloat16 path a
+    ``matrix`` feeds tensor-core products and is held in bfloat16, while ``norm``
+    and ``bias`` tensors, which are only ever read into 32-bit arithmetic, keep
+    32 bits if the file stores them so.
+    """
+
+    name: str
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+
+
+# --------------------------------------------------------------------------- #
+# precision path
+# --------------------------------------------------------------------------- #
+
+@dataclass(frozen=True)
+class Precision:
+    """One of the two paths through the whole model.
+
+    ``float32``: weights, activations, cache and every product in true 32-bit
+    (TF32 and reduced-precision reductions are switched off).
+    ``bfloat16``: matrices, activations between products and the cache in
+    bfloat16; the residual stream, norms, softmax, router, rotation angles and
+    every accumulation in float32.
+    """
+
+    name: str
+
+    @property
+    def act(self) -> torch.dtype:
+        return torch.float32 if self.name == "float32" else torch.bfloat16
+
+    def matrix(self, t: torch.Tensor, device) -> torch.Tensor:
+        return t.to(device=device, dtype=self.act).contiguous()
+
+    def small(self, t: torch.Tensor, device) -> torch.Tensor:
+        """Norm weights and biases: widened in the 32-bit path; otherwise kept as stored
+        (float16 is widened to float32: it has no kernel type of its own)."""
+        if self.name == "float32" or t.dtype == torch.float16:
+            return t.to(device=device, dtype=torch.float32).contiguous()
+        return t.to(device=device).contiguous()
+
+
+def precision_from_name(name: str) -> Precision:
+    alias = {"fp32": "float32", "float32": "float32", "f32": "float32",
+             "bf16": "bfloat16", "bfloat16": "bfloat16"}
+    if name not in alias:
+        raise ValueError(f"unknown dtype '{name}': choose bfloat16 or float32")
+    return Precision(alias[name])
+
+
+@dataclass
+class Runtime:
+    """What a part needs to know about where it runs."""
+
+    precision: Precision
+    device: torch.device
+
+    @property
+    def act(self) -> torch.dtype:
+        return self.precision.act
+
+
+def configure_matmul_exactness() -> None:
+    """No TF32, no reduced-precision split-k reductions: library products accumulate in float32."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+    torch.set_float32_matmul_precision("highest")
+
+
+# --------------------------------------------------------------------------- #
+# what a mixer keeps
+# --------------------------------------------------------------------------- #
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Keys and values per token: ``window = 0`` keeps all of them, ``window = W``
+    only the last ``W`` (older pages are given back)."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A fixed-size state per request (``shape`` per slot), zeroed when a request starts."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+# --------------------------------------------------------------------------- #
+# what a step hands to the parts
+# --------------------------------------------------------------------------- #
+
+@dataclass
+class KVGroupView:
+    """Device metadata of one cache group for the current step."""
+
+    block_table: torch.Tensor      # [B, max_pages] int32, -1 = no page
+    slot_mapping: torch.Tensor     # [T] int32: page * page_size + offset of each new token
+    page_size: int
+    k: torch.Tensor                # [layers_in_group, pages, nkv, page_size, d]
+    v: torch.Tensor
+
+
+@dataclass
+class CacheBinding:
+    """Where one schedule entry's mixer finds its cache."""
+
+    kind: str                       # "kv" | "state" | "none"
+    group: int = -1                 # index of the KV group, or of the state tensor
+    layer_slot: int = -1            # layer index inside the KV group
+    writes: bool = True             # False: reads the cache another entry writes
+
+
+@dataclass
+class StepContext:
+    """Everything about the current batch that parts may read.  All device tensors are int32."""
+
+    num_tokens: int
+    num_requests: int
+    max_q_len: int                  # longest portion in the batch
+    max_kv_len: int                 # longest context in the batch (after this step)
+    all_decode: bool                # every request brings exactly one token
+    token_ids: torch.Tensor         # [T]
+    positions: torch.Tensor         # [T] absolute position of each token in its request
+    q_start: torch.Tensor           # [B+1] first token of each request in the batch
+    kv_len: torch.Tensor            # [B] context length of each request after this step
+    req_of_token: torch.Tensor      # [T]
+    state_slot: torch.Tensor        # [B] state slot of each request
+    fresh: torch.Tensor             # [B] 1 if the request's first token is in this step
+    kv_groups: List[KVGroupView] = field(default_factory=list)
+    states: List[torch.Tensor] = field(default_factory=list)   # [slots, *shape] per state user
+    scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
+    # host copies, for parts written in plain PyTorch (tests' toy parts)
+    host_q_start: Sequence[int] = ()
+    host_kv_len: Sequence[int] = ()
+    host_state_slot: Sequence[int] = ()
+
+
+# --------------------------------------------------------------------------- #
+# part base classes
+# --------------------------------------------------------------------------- #
+
+class Part:
+    category = ""
+
+    def __init__(self, params: Mapping[str, Any], prefix: str):
+        self.params = dict(params)
+        self.prefix = prefix
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        """Take the declared tensors (CPU or device, stored dtype) and keep what forward needs."""
+        self.rt = rt
+
+
+class Norm(Part):
+    category = "norm"
+
+    def apply(self, hidden: torch.Tensor, delta: Optional[torch.Tensor],
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+    rot_dim = 0
+
+    def table(self, device) -> Optional[torch.Tensor]:
+        return None
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "feed_forward"
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    category = "embedding"
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class LMHead(Part):
+    category = "lm_head"
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    category = "block"
+
+    def forward(self, layer: "BuiltLayer", hidden: torch.Tensor, pending: Optional[torch.Tensor],
+                ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass
+class BuiltLayer:
+    """The instantiated parts of one :class:`LayerSpec`."""
+
+    name: str
+    mixer: Mixer
+    feed_forward: FeedForward
+    mixer_norm: Norm
+    feed_forward_norm: Norm
+    block: Block
+
+    def parts(self) -> List[Part]:
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.block]
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x @ w.T`` through the library product the reference also uses for every dense
+    projection (cuBLAS, src/layers/attention.cpp:45-55, src/layers/mlp.cpp:120-130),
+    accumulating in float32; ``w`` is ``[out, in]`` as stored in checkpoints."""
+    if x.dtype == out_dtype:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)

@@ -1,0 +1,130 @@
+"""Feed-forward parts: the dense SwiGLU MLP and the sparse expert block.
+
+Reference: dense MLP as three cuBLAS products and an elementwise kernel
+(src/layers/mlp.cpp:225-303, src/kernels/swiglu_kernel.cu:16-26); expert block
+in src/layers/moe.cpp:185-296 (router product into FP16, one-thread-per-token
+top-k, indices copied to the host, every used expert run on all tokens and
+masked, shared expert added last).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.registry import register_part
+from ..ops import functional as F
+from .base import FeedForward, Runtime, StepContext, TensorDecl, linear
+
+
+class SwiGLUMLP(FeedForward):
+    """``(silu(x Wg^T) * (x Wu^T)) Wd^T``.  params: ``hidden_size``, ``intermediate_size``.
+
+    Tensors: ``<prefix>{gate,up}_proj.weight [I, H]``, ``<prefix>down_proj.weight [H, I]``.
+    """
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.H = int(self.params["hidden_size"])
+        self.I = int(self.params["intermediate_size"])
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        p = self.prefix
+        return [TensorDecl(p + "gate_proj.weight", (self.I, self.H)),
+                TensorDecl(p + "up_proj.weight", (self.I, self.H)),
+                TensorDecl(p + "down_proj.weight", (self.H, self.I))]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        m, dev, p = rt.precision.matrix, rt.device, self.prefix
+        self.w_gate_up = torch.cat([m(tensors[p + "gate_proj.weight"], dev),
+                                    m(tensors[p + "up_proj.weight"], dev)], dim=0)
+        self.w_down = m(tensors[p + "down_proj.weight"], dev)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        gu = linear(x, self.w_gate_up, self.rt.act)
+        return linear(F.swiglu(gu), self.w_down, torch.float32)
+
+
+class SparseMoE(FeedForward):
+    """Softmax router, top-k routed SwiGLU experts, optional sigmoid-gated shared expert.
+
+    params: ``hidden_size``, ``num_experts``, ``top_k``, ``expert_intermediate_size``,
+    ``shared_intermediate_size`` (0 = no shared expert), ``norm_topk_prob``.
+
+    Tensors: ``<prefix>gate.weight [E, H]``;
+    ``<prefix>experts.{e}.{gate,up}_proj.weight [mI, H]``, ``.down_proj.weight [H, mI]``;
+    ``<prefix>shared_expert.{gate,up,down}_proj.weight``, ``<prefix>shared_expert_gate.weight [1, H]``.
+    """
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = self.params
+        self.H = int(p["hidden_size"])
+        self.E = int(p["num_experts"])
+        self.K = int(p["top_k"])
+        self.mI = int(p["expert_intermediate_size"])
+        self.sI = int(p.get("shared_intermediate_size", 0))
+        self.norm_topk = bool(p.get("norm_topk_prob", False))
+        if not 1 <= self.K <= min(self.E, 32):
+            raise ValueError(f"moe: top_k {self.K} must lie in [1, min(32, num_experts={self.E})]")
+        self.last_routing = None
+        self.keep_routing = False
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        p = self.prefix
+        out = [TensorDecl(p + "gate.weight", (self.E, self.H))]
+        for e in range(self.E):
+            q = f"{p}experts.{e}."
+            out += [TensorDecl(q + "gate_proj.weight", (self.mI, self.H)),
+                    TensorDecl(q + "up_proj.weight", (self.mI, self.H)),
+                    TensorDecl(q + "down_proj.weight", (self.H, self.mI))]
+        if self.sI > 0:
+            q = p + "shared_expert."
+            out += [TensorDecl(q + "gate_proj.weight", (self.sI, self.H)),
+                    TensorDecl(q + "up_proj.weight", (self.sI, self.H)),
+                    TensorDecl(q + "down_proj.weight", (self.H, self.sI)),
+                    TensorDecl(p + "shared_expert_gate.weight", (1, self.H))]
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        m, dev, p = rt.precision.matrix, rt.device, self.prefix
+        # router and shared gate feed float32 dot products only
+        self.w_router = rt.precision.small(tensors[p + "gate.weight"], dev)
+        self.w_gate_up = torch.empty(self.E, 2 * self.mI, self.H, dtype=rt.act, device=dev)
+        self.w_down = torch.empty(self.E, self.H, self.mI, dtype=rt.act, device=dev)
+        for e in range(self.E):
+            q = f"{p}experts.{e}."
+            self.w_gate_up[e, :self.mI].copy_(tensors[q + "gate_proj.weight"])
+            self.w_gate_up[e, self.mI:].copy_(tensors[q + "up_proj.weight"])
+            self.w_down[e].copy_(tensors[q + "down_proj.weight"])
+        self.w_shared_gate = None
+        if self.sI > 0:
+            q = p + "shared_expert."
+            self.w_shared_gate_up = torch.cat([m(tensors[q + "gate_proj.weight"], dev),
+                                               m(tensors[q + "up_proj.weight"], dev)], dim=0)
+            self.w_shared_down = m(tensors[q + "down_proj.weight"], dev)
+            g = rt.precision.small(tensors[p + "shared_expert_gate.weight"], dev).reshape(-1)
+            self.w_shared_gate = g.to(self.w_router.dtype).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        T = x.shape[0]
+        idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
+                                           want_probs=self.keep_routing)
+        if self.keep_routing:
+            self.last_routing = (idx, w, probs)
+        offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
+        n = T * self.K
+        act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
+        y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
+        shared = None
+        if self.sI > 0:
+            gu = linear(x, self.w_shared_gate_up, self.rt.act)
+            shared = linear(F.swiglu(gu), self.w_shared_down, torch.float32)
+        return F.moe_combine(y, inv_perm, w, shared, gate)
+
+
+register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)
+register_part("feed_forward", "sparse_moe", SparseMoE)

@@ -1,0 +1,127 @@
+"""Generation through the whole engine: model, cache, scheduler, sampler.
+
+Reference: ``Engine::generate_paged`` (src/core/engine.cpp:233-330) prefills one
+prompt and decodes token by token for one request; ``generate_batched_paged``
+(:348-486) does the same for a fixed batch.  Here every call goes through the
+continuous-batching scheduler, whatever the number of prompts.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .defaults import DEFAULT_PAGE_SIZE
+from .loading import load_model
+from .model import Model
+from .request import Request
+from .scheduler import IterationStats, Scheduler, SchedulerConfig
+from .step import ModelRunner, StepEntry
+
+
+@dataclass
+class GenerationOutput:
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    finish_reason: Optional[str]
+    ttft: Optional[float] = None
+    seconds: float = 0.0
+    preemptions: int = 0
+
+
+class GPUExecutor:
+    """What the scheduler drives: the model runner and the sampler."""
+
+    def __init__(self, runner: ModelRunner, sampler: Sampler):
+        self.runner = runner
+        self.sampler = sampler
+        self.cache = runner.cache
+
+    def add_request(self, rid: Hashable) -> None:
+        self.runner.add_request(rid)
+
+    def release(self, rid: Hashable) -> None:
+        self.runner.release(rid)
+
+    def run(self, entries: Sequence[StepEntry], sample_for: Sequence[Request]) -> Dict[Hashable, int]:
+        res = self.runner.step(entries)
+        if not sample_for:
+            return {}
+        assert [rid for rid, _ in res.index] == [r.rid for r in sample_for]
+        toks = self.sampler.sample(res.logits, [r.params for r in sample_for], [r.stream for r in sample_for],
+                                   [len(r.generated) for r in sample_for])
+        return {r.rid: t for r, t in zip(sample_for, toks)}
+
+
+class LLM:
+    """A loaded model ready to generate.
+
+    ``max_seq_len`` is the context limit of a request (the reference's ``--max-seq-len``,
+    src/core/main.cc:47, :75); ``num_pages`` defaults to what ``max_running`` requests of
+    that length need, capped by ``memory_fraction`` of the free device memory.
+    """
+
+    def __init__(self, model: Union[str, Model], dtype: str = "bfloat16", device: str = "cuda:0",
+                 max_seq_len: int = 2048, page_size: Optional[int] = None, num_pages: Optional[int] = None,
+                 max_running: int = 64, max_tokens_per_step: int = 2048, prefill_chunk: int = 0,
+                 memory_fraction: float = 0.85, runtime=None):
+        if isinstance(model, str):
+            self.model, self.rt, self.config_json = load_model(model, dtype, device)
+        else:
+            self.model, self.rt, self.config_json = model, runtime, None
+            if runtime is None:
+                raise ValueError("LLM: a built model needs its runtime")
+        page_size = page_size or DEFAULT_PAGE_SIZE
+        max_seq_len = int(max_seq_len)
+        pages_per_req = -(-max_seq_len // page_size)
+        if num_pages is None:
+            num_pages = max_running * pages_per_req
+            item = 4 if self.rt.precision.name == "float32" else 2
+            per_page = sum(2 * g.num_layers * g.num_kv_heads * g.head_dim * page_size * item
+                           for g in self.model.kv_groups)
+            free, _ = torch.cuda.mem_get_info(self.rt.device)
+            if per_page:
+                num_pages = max(pages_per_req, min(num_pages, int(free * memory_fraction) // per_page))
+        max_tokens_per_step = max(max_tokens_per_step, max_running)
+        self.runner = ModelRunner(self.model, self.rt, page_size=page_size, num_pages=num_pages,
+                                  max_requests=max_running, max_tokens_per_step=max_tokens_per_step,
+                                  max_context=max_seq_len)
+        self.sampler = Sampler(self.rt.device, self.model.spec.vocab_size, max_running)
+        self.executor = GPUExecutor(self.runner, self.sampler)
+        self.sched_cfg = SchedulerConfig(max_tokens_per_step=max_tokens_per_step, max_running=max_running,
+                                         prefill_chunk=prefill_chunk, max_context=max_seq_len)
+        self.last_history: List[IterationStats] = []
+        self._calls = 0
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[GenerationOutput]:
+        """Token ids in, token ids out; request ``i`` samples from random stream ``i``."""
+        if params is None:
+            params = SamplingParams()
+        plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        if len(plist) != len(prompts):
+            raise ValueError("LLM.generate: one SamplingParams per prompt (or one for all)")
+        V = self.model.spec.vocab_size
+        for p in prompts:
+            for t in p:
+                if not 0 <= int(t) < V:
+                    raise ValueError(f"LLM.generate: token id {t} outside [0, {V})")
+        sched = Scheduler(self.executor, self.sched_cfg)
+        self._calls += 1
+        reqs = [Request((self._calls, i), list(p), sp, stream=i) for i, (p, sp) in enumerate(zip(prompts, plist))]
+        t0 = time.perf_counter()
+        for r in reqs:
+            sched.submit(r)
+        sched.run_until_done()
+        self.last_history = sched.history
+        out = []
+        for r in reqs:
+            out.append(GenerationOutput(r.prompt, list(r.generated), r.finish_reason, r.metrics.ttft,
+                                        (r.metrics.finished or time.perf_counter()) - t0,
+                                        r.metrics.preemptions))
+        return out

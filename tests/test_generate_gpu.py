@@ -1,0 +1,145 @@
+"""Generation through the entry points: greedy and sampled tokens equal the plain model's,
+alone, batched, cut into portions, and under preemption; the command line keeps its contract."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_model as pm
+import tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name in ("A", "B", "C"):
+        f = str(tmp_path_factory.mktemp(f"gen_{name}"))
+        tiny.make_folder(f, tiny.CONFIGS[name], seed=31, dtype=torch.float32)
+        out[name] = (f, tiny.CONFIGS[name], tiny.read_weights(f))
+    return out
+
+
+def clear_prompt(cfg, w, n, seed, new_tokens, temperature=0.0, top_p=1.0, stream=0, sseed=42):
+    """A prompt whose plain generation meets no near-tie in routing or in the arg-max."""
+    for s in range(seed, seed + 100):
+        toks = tiny.pick_tokens(cfg, w, n, s)
+        gen = pm.generate(cfg, w, toks, new_tokens, temperature, top_p, sseed, stream)
+        full = toks + gen
+        if tiny.min_routing_gap(cfg, w, full) < 1e-4:
+            continue
+        logits = pm.forward(cfg, w, full)[len(toks) - 1:-1]
+        top2 = torch.topk(logits, 2, dim=-1).values
+        if temperature == 0.0 and float((top2[:, 0] - top2[:, 1]).min()) < 1e-4:
+            continue
+        return toks, gen
+    raise RuntimeError("no clear prompt found")
+
+
+def test_greedy_three_prompts_like_the_benchmark_workload(folders):
+    """Configuration A: prompts of 5, 11 and 17 random tokens, 8 greedy tokens each."""
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    folder, cfg, w = folders["A"]
+    cases = [clear_prompt(cfg, w, n, 100 * n, 8) for n in (5, 11, 17)]
+    llm = LLM(folder, dtype="float32", max_seq_len=128, max_running=4, max_tokens_per_step=64)
+    outs = llm.generate([c[0] for c in cases], SamplingParams(greedy=True, max_new_tokens=8))
+    for o, (toks, gen) in zip(outs, cases):
+        assert o.token_ids == gen and o.finish_reason == "length"
+    # one at a time gives the same
+    for toks, gen in cases:
+        assert llm.generate([toks], SamplingParams(greedy=True, max_new_tokens=8))[0].token_ids == gen
+    assert llm.runner.cache.used_pages() == [0]
+
+
+def test_temperature_four_requests_in_portions_like_the_benchmark_workload(folders):
+    """Configuration B: prompts of 1, 9, 23 and 40 tokens, prefilled in portions of 8 beside
+    decoding requests, 12 tokens at temperature 0.8 under a fixed seed."""
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    folder, cfg, w = folders["B"]
+    cases = [clear_prompt(cfg, w, n, 77 * n, 12, temperature=0.8, top_p=1.0, stream=i, sseed=1234)
+             for i, n in enumerate((1, 9, 23, 40))]
+    llm = LLM(folder, dtype="float32", max_seq_len=256, max_running=4, max_tokens_per_step=16, prefill_chunk=8)
+    sp = SamplingParams(greedy=False, temperature=0.8, top_p=1.0, seed=1234, max_new_tokens=12)
+    outs = llm.generate([c[0] for c in cases], sp)
+    for o, (toks, gen) in zip(outs, cases):
+        assert o.token_ids == gen
+    steps = llm.last_history
+    assert any(s.prefill_tokens and s.decode_tokens for s in steps)          # portions beside decodes
+    assert all(s.num_tokens <= 16 for s in steps)
+
+
+def test_top_p_and_stop_token(folders):
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    folder, cfg, w = folders["C"]
+    toks, gen = clear_prompt(cfg, w, 30, 5, 10, temperature=1.2, top_p=0.7, stream=0, sseed=9)
+    llm = LLM(folder, dtype="float32", max_seq_len=128, max_running=2)
+    o = llm.generate([toks], SamplingParams(greedy=False, temperature=1.2, top_p=0.7, seed=9, max_new_tokens=10))[0]
+    assert o.token_ids == gen
+    stop = gen[4]
+    first = gen.index(stop)
+    o = llm.generate([toks], SamplingParams(greedy=False, temperature=1.2, top_p=0.7, seed=9, max_new_tokens=10,
+                                            stop_token_ids=(stop,)))[0]
+    assert o.token_ids == gen[:first + 1] and o.finish_reason == "stop"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_recomputes_the_same_tokens(folders, dtype):
+    """So few pages that decoding requests are preempted and recomputed; tokens must not change."""
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    folder, cfg, w = folders["A"]
+    cases = [clear_prompt(cfg, w, n, 40 * n, 20) for n in (14, 9, 12)]
+    roomy = LLM(folder, dtype=dtype, max_seq_len=64, max_running=4, page_size=4, num_pages=64)
+    want = [o.token_ids for o in roomy.generate([c[0] for c in cases], SamplingParams(greedy=True, max_new_tokens=20))]
+    if dtype == "float32":
+        assert want == [c[1] for c in cases]
+    tight = LLM(folder, dtype=dtype, max_seq_len=64, max_running=4, page_size=4, num_pages=14)
+    outs = tight.generate([c[0] for c in cases], SamplingParams(greedy=True, max_new_tokens=20))
+    assert sum(o.preemptions for o in outs) >= 1
+    assert [o.token_ids for o in outs] == want
+    assert tight.runner.cache.used_pages() == [0]
+
+
+def test_sdk_entry_point(folders):
+    from mini_infer_sdk import InferenceConfig, MiniInfer, SamplingConfig, SamplingMode
+    folder, cfg, w = folders["A"]
+    toks, gen = clear_prompt(cfg, w, 12, 900, 6)
+    eng = MiniInfer(model_path=folder, config=InferenceConfig(max_new_tokens=6, max_seq_len=64, dtype="float32",
+                                                              max_running=2))
+    r = eng.generate(toks)
+    assert r.generated_ids == gen and r.prompt_tokens == 12 and r.generated_tokens == 6
+    assert r.tokens == toks + gen and r.finish_reason == "length" and r.tokens_per_sec > 0
+    assert r.text == " ".join(str(t) for t in gen)                          # no tokenizer in a random-weight folder
+    rs = eng.generate_ids([toks, toks[:5]], InferenceConfig(max_new_tokens=3, sampling=SamplingConfig(
+        mode=SamplingMode.TOP_P, temperature=0.9, top_p=0.8, seed=3)))
+    assert rs[0].generated_ids == pm.generate(cfg, w, toks, 3, 0.9, 0.8, 3, 0)
+    assert rs[1].generated_ids == pm.generate(cfg, w, toks[:5], 3, 0.9, 0.8, 3, 1)
+    with pytest.raises(NotImplementedError):
+        MiniInfer(endpoint="http://localhost:8000")
+
+
+def test_command_line_contract(folders):
+    folder, cfg, w = folders["A"]
+    toks, gen = clear_prompt(cfg, w, 9, 333, 5)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "mini_infer"), "generate", "--model", folder, "--prompt-ids",
+           ",".join(map(str, toks)), "--max-new-tokens", "5", "--greedy", "--paged", "--dtype", "float32",
+           "--max-seq-len", "64", "--json"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = p.stdout.splitlines()
+    i = lines.index("--- generated ---")
+    assert lines[i + 1] == " ".join(map(str, gen)) and lines[i + 2] == "--- end ---"
+    assert lines[i + 3].startswith("[mini-infer] 5 tokens in ") and lines[i + 3].endswith("tok/s)")
+    assert json.loads(lines[i + 4])["token_ids"] == gen
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mini_infer"), "serve", "--model", folder],
+                         capture_output=True, text=True)
+    assert bad.returncode == 2 and "not part of this engine" in bad.stderr

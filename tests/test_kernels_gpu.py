@@ -1,0 +1,403 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch reference of the same op, at sizes
+other than the tiny models' (odd widths, head sizes in steps of 16 and between, vocabularies and
+widths that are no power of two), in float32 and bfloat16."""
+
+import math
+import random
+
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def F():
+    from mini_infer_b200.ops import functional
+    return functional
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, ref, tol, what=""):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    err = float((got - ref).abs().max())
+    scale = max(float(ref.abs().max()), 1e-6)
+    assert err <= tol * scale, f"{what}: error {err:.3e} vs scale {scale:.3e} (tolerance {tol:.1e})"
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1e-2}
+
+
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+def test_embed_gather(wdt):
+    table = rnd(1003, 200, dtype=wdt)
+    ids = torch.tensor([0, 1002, 5, 5, 77, 400], dtype=torch.int32, device=DEV)
+    out = F().embed_gather(ids, table)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("H", [72, 200, 2048 + 8])
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_add_rmsnorm(H, adt, wdt):
+    T, eps = 7, 1e-5
+    h = rnd(T, H, seed=1)
+    d = rnd(T, H, seed=2)
+    w = (1 + rnd(H, seed=3) * 0.1).to(wdt)
+    ref_h = h + d
+    ref = pm.rms_norm(ref_h, w.float(), eps)
+    h1 = h.clone()
+    out = F().add_rmsnorm(h1, d, w, eps, adt)
+    assert out.dtype == adt
+    assert torch.allclose(h1, ref_h, atol=0, rtol=0)                          # residual written back exactly
+    close(out, ref, 4e-6 if adt == torch.float32 else 8e-3, "add_rmsnorm")
+    # without delta, hidden untouched
+    h2 = h.clone()
+    out2 = F().add_rmsnorm(h2, None, w, eps, adt)
+    assert torch.equal(h2, h)
+    close(out2, pm.rms_norm(h, w.float(), eps), 4e-6 if adt == torch.float32 else 8e-3)
+    # with rows (one of them twice): hidden untouched, rows ordered as asked
+    rows = torch.tensor([5, 0, 5, 3], dtype=torch.int32, device=DEV)
+    h3 = h.clone()
+    out3 = F().add_rmsnorm(h3, d, w, eps, adt, rows=rows)
+    assert torch.equal(h3, h) and out3.shape == (4, H)
+    close(out3, ref[rows.long()], 4e-6 if adt == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,rot", [(5, 1, 24, 24), (4, 2, 64, 32), (3, 3, 16, 16), (2, 1, 128, 128)])
+def test_qkv_post(adt, nh, nkv, d, rot):
+    T, ps, pages = 9, 4, 6
+    width = (nh + 2 * nkv) * d
+    qkv = rnd(T, width, seed=4)
+    bias = rnd(width, seed=5).to(adt if adt == torch.bfloat16 else torch.float32)
+    pos = torch.tensor([0, 1, 2, 3, 17, 18, 400, 4000, 5], dtype=torch.int32, device=DEV)
+    theta = 1e6
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
+    inv = inv.float().to(DEV)
+    slots = torch.tensor(random.Random(0).sample(range(ps * pages), T), dtype=torch.int32, device=DEV)
+    kc = torch.zeros(pages, nkv, ps, d, dtype=adt, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = F().qkv_post(qkv, bias, pos, inv, rot, slots, kc, vc, nh, nkv, d, ps, adt)
+    x = qkv + bias.float()
+    xq = x[:, :nh * d].view(T, nh, d)
+    xk = x[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+    xv = x[:, (nh + nkv) * d:].view(T, nkv, d)
+
+    def rope(t):
+        a = pos.float()[:, None] * inv[None, :]
+        c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+        h = rot // 2
+        y = t.clone()
+        y[..., :h] = t[..., :h] * c - t[..., h:rot] * s
+        y[..., h:rot] = t[..., h:rot] * c + t[..., :h] * s
+        return y
+    tol = 3e-6 if adt == torch.float32 else 8e-3
+    close(q, rope(xq), tol, "q")
+    page, off = slots.long() // ps, slots.long() % ps
+    close(kc[page, :, off, :], rope(xk), tol, "k cache")
+    close(vc[page, :, off, :], xv, tol, "v cache")
+    written = torch.zeros(pages * ps, dtype=torch.bool)
+    written[slots.long().cpu()] = True
+    flat = kc.permute(0, 2, 1, 3).reshape(pages * ps, -1).float().cpu()
+    assert float(flat[~written].abs().max()) == 0.0                           # nothing else touched
+    # queries only (a layer that reads another layer's cache), no rotation
+    q2 = F().qkv_post(qkv[:, :nh * d].contiguous(), None, pos, None, 0, None, None, None, nh, 0, d, ps, adt)
+    close(q2, qkv[:, :nh * d].view(T, nh, d), tol)
+
+
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+def test_swiglu(adt):
+    gu = rnd(13, 2 * 70, dtype=adt, scale=2.0)
+    out = F().swiglu(gu)
+    g, u = gu.float()[:, :70], gu.float()[:, 70:]
+    close(out, g / (1 + torch.exp(-g)) * u, 1e-6 if adt == torch.float32 else 8e-3)
+
+
+def test_moe_combine():
+    T, K, H = 6, 3, 100
+    y = rnd(T * K, H, seed=1)
+    w = rnd(T, K, seed=2).abs()
+    perm = torch.randperm(T * K, generator=torch.Generator().manual_seed(1)).to(torch.int32).to(DEV)
+    shared = rnd(T, H, seed=3)
+    gate = torch.sigmoid(rnd(T, seed=4))
+    out = F().moe_combine(y, perm, w, shared, gate)
+    ref = (w[:, :, None] * y[perm.long()].view(T, K, H)).sum(1) + gate[:, None] * shared
+    close(out, ref, 2e-6)
+    out2 = F().moe_combine(y, perm, w, None, None)
+    close(out2, (w[:, :, None] * y[perm.long()].view(T, K, H)).sum(1), 2e-6)
+
+
+# --------------------------------------------------------------------------- #
+# attention
+# --------------------------------------------------------------------------- #
+
+def paged_case(kv_lens, q_lens, nh, nkv, d, ps, adt, seed=0, shuffle=True, extra_pages=3):
+    """Random K/V for whole sequences, packed into a paged cache with shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(kv_lens)
+    pages_per = [-(-n // ps) for n in kv_lens]
+    total = sum(pages_per) + extra_pages
+    order = list(range(total))
+    if shuffle:
+        random.Random(seed).shuffle(order)
+    kc = torch.full((total, nkv, ps, d), 7.0, dtype=adt)          # poison: unused slots must not matter
+    vc = torch.full((total, nkv, ps, d), -7.0, dtype=adt)
+    max_pages = max(pages_per) + 1
+    table = torch.full((B, max_pages), -1, dtype=torch.int32)
+    seqs, qs = [], []
+    nxt = 0
+    for b, n in enumerate(kv_lens):
+        k = torch.randn(n, nkv, d, generator=g).to(adt)
+        v = torch.randn(n, nkv, d, generator=g).to(adt)
+        q = torch.randn(n, nh, d, generator=g).to(adt)
+        seqs.append((q, k, v))
+        for i in range(pages_per[b]):
+            p = order[nxt]
+            nxt += 1
+            table[b, i] = p
+            lo, hi = i * ps, min(n, (i + 1) * ps)
+            kc[p, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            vc[p, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        qs.append(q[n - q_lens[b]:])
+    q_start = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    return {"q": torch.cat(qs).to(DEV), "kc": kc.to(DEV), "vc": vc.to(DEV), "table": table.to(DEV),
+            "q_start": q_start.to(DEV), "kv_len": torch.tensor(kv_lens, dtype=torch.int32, device=DEV),
+            "seqs": seqs, "q_lens": q_lens}
+
+
+def plain_attention(case, window=0):
+    outs = []
+    for (q, k, v), ql in zip(case["seqs"], case["q_lens"]):
+        o = pm.attention_scores_softmax_pv(q.float(), k.float(), v.float(), window)
+        outs.append(o[len(q) - ql:])
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d", [(6, 2, 16), (3, 3, 24), (4, 1, 40), (8, 2, 64), (2, 2, 128), (2, 1, 256),
+                                      (5, 5, 80)])
+def test_attention_tiled_ragged(adt, nh, nkv, d):
+    case = paged_case(kv_lens=[1, 37, 130, 64, 16], q_lens=[1, 37, 50, 1, 2], nh=nh, nkv=nkv, d=d, ps=16,
+                      adt=adt, seed=d)
+    out = F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 50)
+    close(out, plain_attention(case), 3e-6 if adt == torch.float32 else 1e-2, "attention")
+
+
+@pytest.mark.parametrize("ps", [1, 4, 64])
+@pytest.mark.parametrize("window", [0, 7, 16, 33])
+def test_attention_tiled_windows_and_page_sizes(ps, window):
+    case = paged_case(kv_lens=[70, 33, 5], q_lens=[70, 3, 1], nh=4, nkv=2, d=32, ps=ps, adt=torch.float32, seed=ps)
+    out = F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 70,
+                        window=window)
+    close(out, plain_attention(case, window), 3e-6, f"window {window} page {ps}")
+
+
+def test_attention_finds_a_far_key_and_respects_the_window_edge():
+    """One key among hundreds is made to stand out; it must dominate exactly when it is visible."""
+    n, d, ps = 400, 64, 16
+    for adt in (torch.float32, torch.bfloat16):
+        for far, window, visible in ((3, 0, True), (250, 150, True), (249, 150, False), (399, 1, True)):
+            case = paged_case([n], [1], 2, 1, d, ps, adt, seed=far)
+            q, k, v = case["seqs"][0]
+            k[far] = q[n - 1, 0] * 4.0                              # aligned with the last query: a huge score
+            v[far] = 50.0
+            page, off = int(case["table"][0, far // ps]), far % ps
+            case["kc"][page, :, off] = k[far].to(DEV)
+            case["vc"][page, :, off] = v[far].to(DEV)
+            out = F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"],
+                                case["kv_len"], 1, window=window)
+            ref = plain_attention(case, window)
+            close(out, ref, 3e-6 if adt == torch.float32 else 1e-2, f"far key {far} window {window}")
+            assert (float(out[0, 0].float().mean()) > 40.0) == visible
+            if mi_decode_ok(d):
+                po, pml, splits = decode_scratch(1, 2, n, d)
+                out2 = F().decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"],
+                                            case["kv_len"], po, pml, splits, window=window)
+                close(out2, ref, 3e-6 if adt == torch.float32 else 1e-2, f"decode far key {far}")
+
+
+def mi_decode_ok(d):
+    return F().decode_attention_supported(d)
+
+
+def decode_scratch(B, nh, max_kv, d):
+    splits = -(-max_kv // F().decode_split_size())
+    return (torch.empty(B * nh * splits * d, dtype=torch.float32, device=DEV),
+            torch.empty(B * nh * splits * 2, dtype=torch.float32, device=DEV), splits)
+
+
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 64), (3, 3, 128), (7, 1, 128), (2, 1, 256)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_decode_attention(adt, nh, nkv, d, window):
+    kv = [1, 255, 256, 257, 700, 1030, 16]
+    case = paged_case(kv, [1] * len(kv), nh, nkv, d, 16, adt, seed=nh)
+    po, pml, splits = decode_scratch(len(kv), nh, max(kv), d)
+    out = F().decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],
+                               po, pml, splits, window=window)
+    ref = plain_attention(case, window)
+    close(out, ref, 3e-6 if adt == torch.float32 else 1e-2, "decode attention")
+    # a larger split budget than needed (as under a fixed launch shape) changes nothing
+    po2, pml2, splits2 = decode_scratch(len(kv), nh, 4096, d)
+    out2 = F().decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],
+                                po2, pml2, splits2, window=window)
+    assert torch.equal(out, out2)
+    tiled = F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 1,
+                          window=window)
+    close(out, tiled, 3e-6 if adt == torch.float32 else 1e-2, "decode vs tiled")
+
+
+def test_attention_refuses_bad_shapes():
+    from mini_infer_b200.ops.library import KernelError
+    case = paged_case([5], [1], 3, 2, 16, 16, torch.float32)
+    with pytest.raises(KernelError, match="multiple"):
+        F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 1)
+    q = torch.zeros(1, 1, 300, device=DEV)
+    kc = torch.zeros(1, 1, 16, 300, device=DEV)
+    with pytest.raises(KernelError, match="head_dim"):
+        F().attention(q, kc, kc.clone(), case["table"], case["q_start"], case["kv_len"], 1)
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        F().swiglu(torch.zeros(2, 4))
+
+
+# --------------------------------------------------------------------------- #
+# mixture of experts
+# --------------------------------------------------------------------------- #
+
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("E,K,norm", [(6, 3, False), (8, 2, True), (60, 4, False), (130, 8, True), (5, 1, True),
+                                      (33, 32, False)])
+def test_router(adt, wdt, E, K, norm):
+    T, H = 19, 200
+    x = rnd(T, H, dtype=adt, seed=E)
+    wr = rnd(E, H, dtype=wdt, scale=0.3, seed=K)
+    wsg = rnd(H, dtype=wdt, scale=0.2, seed=9)
+    idx, w, gate, probs = F().moe_router(x, wr, wsg, K, norm, want_probs=True)
+    rp, ri, rw = pm.route(x.float().cpu(), wr.float().cpu(), K, norm)
+    close(probs, rp, 5e-6, "router probabilities")
+    # where the reference's K-th and (K+1)-th probabilities are not within rounding, the choice is the same
+    s = torch.sort(rp, dim=-1, descending=True).values
+    clear = torch.ones(T, dtype=torch.bool)
+    for k in range(min(K, E - 1)):
+        clear &= (s[:, k] - s[:, k + 1]) > 1e-6
+    assert torch.equal(idx.cpu().long()[clear], ri[clear])
+    close(w.cpu()[clear], rw[clear], 5e-6, "router weights")
+    ref_gate = torch.sigmoid(x.float().cpu() @ wsg.float().cpu())
+    close(gate, ref_gate, 5e-6, "shared gate")
+    if norm:
+        assert torch.allclose(w.sum(-1).cpu(), torch.ones(T), atol=1e-5)
+
+
+def test_router_ties_go_to_the_lowest_index():
+    T, H, E = 4, 64, 10
+    x = rnd(T, H)
+    wr = rnd(E, H, scale=0.2)
+    wr[7] = wr[2]
+    wr[5] = wr[2]
+    wr[2] *= 1.0
+    idx, w, _, probs = F().moe_router(x, wr, None, 3, False, want_probs=True)
+    for t in range(T):
+        chosen = idx[t].tolist()
+        for e in (5, 7):
+            if e in chosen:
+                assert 2 in chosen and chosen.index(2) < chosen.index(e)
+        if 7 in chosen:
+            assert 5 in chosen and chosen.index(5) < chosen.index(7)
+        assert len(set(chosen)) == 3
+    from mini_infer_b200.ops.library import KernelError
+    with pytest.raises(KernelError, match="experts per token"):
+        F().moe_router(x, wr, None, 11, False)
+
+
+@pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8)])
+def test_permute(T, E, K):
+    g = torch.Generator().manual_seed(T)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
+    flat = idx.flatten().cpu().long()
+    counts = torch.bincount(flat, minlength=E)
+    assert offsets.cpu().tolist() == [0] + counts.cumsum(0).tolist()
+    order = torch.sort(flat, stable=True).indices                            # stable: token order inside an expert
+    assert sorted_token.cpu().tolist() == (order // K).tolist()
+    inv = torch.empty(T * K, dtype=torch.long)
+    inv[order] = torch.arange(T * K)
+    assert inv_perm.cpu().tolist() == inv.tolist()
+
+
+@pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,K,H,I", [(1, 8, 2, 64, 32), (45, 6, 3, 96, 48), (130, 12, 4, 200, 70), (9, 60, 4, 128, 24)])
+def test_grouped_gemm_plain(adt, T, E, K, H, I):
+    g = torch.Generator().manual_seed(E)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
+    x = rnd(T, H, dtype=adt, seed=1)
+    wgu = rnd(E, 2 * I, H, dtype=adt, scale=0.2, seed=2)
+    wd = rnd(E, H, I, dtype=adt, scale=0.2, seed=3)
+    act = F().grouped_gemm_plain(x, sorted_token, wgu, offsets, T * K, True, adt)
+    xs = x.float()[sorted_token.long()]
+    expert_of_row = torch.repeat_interleave(torch.arange(E, device=DEV), (offsets[1:] - offsets[:-1]).long())
+    ref_act = torch.empty(T * K, I, device=DEV)
+    for r in range(T * K):
+        e = int(expert_of_row[r])
+        gte = xs[r] @ wgu[e, :I].float().T
+        up = xs[r] @ wgu[e, I:].float().T
+        ref_act[r] = gte / (1 + torch.exp(-gte)) * up
+    close(act, ref_act, 3e-6 if adt == torch.float32 else 1e-2, "gate/up product")
+    y = F().grouped_gemm_plain(act, None, wd, offsets, T * K, False, torch.float32)
+    ref_y = torch.stack([act[r].float() @ wd[int(expert_of_row[r])].float().T for r in range(T * K)])
+    close(y, ref_y, 3e-6 if adt == torch.float32 else 1e-2, "down product")
+
+
+# --------------------------------------------------------------------------- #
+# sampling
+# --------------------------------------------------------------------------- #
+
+def test_greedy_rows_lowest_index_wins():
+    V = 151_937                                                              # no power of two, not even
+    logits = rnd(5, V)
+    logits[1, 100] = 50.0
+    logits[1, 99_000] = 50.0
+    logits[2, V - 1] = 60.0
+    logits[3, 0] = 60.0
+    out = F().sample_rows(logits).cpu().tolist()
+    ref = [pm.greedy(logits[r].cpu()) for r in range(5)]
+    assert out == ref and out[1] == 100 and out[2] == V - 1 and out[3] == 0
+
+
+@pytest.mark.parametrize("V", [301, 5000, 151_936])
+def test_temperature_and_nucleus_rows(V):
+    R = 24
+    logits = rnd(R, V, scale=3.0, seed=V)
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.3] * 6)
+    tops = torch.tensor([1.0] * 8 + [0.9] * 8 + [0.3] * 8)
+    us = torch.tensor([pm.uniform_for(5, r, r) for r in range(R)], dtype=torch.float32)
+    us[4], us[5] = 0.0, 0.99999994
+    out = F().sample_rows(logits, temps.to(DEV), tops.to(DEV), us.to(DEV)).cpu().tolist()
+    for r in range(R):
+        ref = pm.sample(logits[r].cpu(), float(temps[r]), float(tops[r]), float(us[r]))
+        if out[r] != ref:
+            # a draw that lands within rounding of a boundary of the cumulative sum may fall either side
+            p = torch.softmax(logits[r].cpu().double() / float(temps[r]), -1)
+            lo, hi = sorted((out[r], ref))
+            between = float(p[lo:hi + 1].sum())
+            assert abs(hi - lo) == 1 or between < 1e-5, (r, out[r], ref)
+
+
+def test_sampling_frequencies_follow_the_distribution():
+    logits = torch.tensor([[0.0, 1.0, 5.0, 2.0, 4.0]], device=DEV).repeat(4000, 1)
+    us = torch.tensor([pm.uniform_for(9, 1, n) for n in range(4000)], dtype=torch.float32, device=DEV)
+    t = torch.ones(4000, device=DEV)
+    out = F().sample_rows(logits, t, torch.ones(4000, device=DEV), us)
+    freq = torch.bincount(out.cpu().long(), minlength=5).float() / 4000
+    assert float((freq - torch.softmax(logits[0].cpu(), -1)).abs().max()) < 0.03
+    out2 = F().sample_rows(logits, t, torch.full((4000,), 0.6, device=DEV), us)   # nucleus {2, 4}
+    assert set(out2.cpu().tolist()) == {2, 4}

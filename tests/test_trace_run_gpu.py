@@ -1,0 +1,62 @@
+"""bin/trace_run as a user runs it: a subprocess fed JSON lines, files of logits out."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+import tiny
+import traces
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def replay(folder, dtype, steps, out_dir, max_tokens):
+    lines = []
+    for i, st in enumerate(steps):
+        lines.append(json.dumps({"step": i, "entries": [{"id": rid, "tokens": toks, "want": want}
+                                                        for rid, toks, want in st["entries"]], "end": st["end"]}))
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", out_dir,
+                        "--max-tokens", str(max_tokens)], input="\n".join(lines) + "\n", capture_output=True,
+                       text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert p.stdout.split() == [x for i in range(len(steps)) for x in ("done", str(i))]
+    return p
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "float32")])
+def test_trace_run_mixed(tmp_path, name, dtype):
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(str(tmp_path / "model"), cfg, seed=17, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    reqs = {f"q{i}": tiny.pick_tokens(cfg, w, n, 50 + i, min_gap=2e-3) for i, n in enumerate([40, 66, 12, 35, 90, 20])}
+    steps = traces.mixed(reqs, max_live=4, seed=9)
+    for st in steps[::3]:                                   # some steps want nothing, some only the last place
+        st["entries"] = [(rid, toks, []) for rid, toks, _ in st["entries"]]
+    for st in steps[1::3]:
+        st["entries"] = [(rid, toks, [len(toks) - 1]) for rid, toks, _ in st["entries"]]
+    out = str(tmp_path / "out")
+    replay(folder, dtype, steps, out, traces.live_token_peak(steps, 64))
+    ref = {rid: pm.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    fed = {rid: 0 for rid in reqs}
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    V = cfg["vocab_size"]
+    for i, st in enumerate(steps):
+        wanted = [(rid, fed[rid] + k) for rid, toks, want in st["entries"] for k in want]
+        path = os.path.join(out, f"{i}.f32")
+        if not wanted:
+            assert not os.path.exists(path)
+        else:
+            arr = np.fromfile(path, dtype="<f4")
+            assert arr.size == len(wanted) * V
+            arr = torch.from_numpy(arr.reshape(len(wanted), V).copy())
+            for row, (rid, pos) in zip(arr, wanted):
+                assert float((row - ref[rid][pos]).abs().max()) <= tol * float(ref[rid].abs().max()), (i, rid, pos)
+        for rid, toks, _ in st["entries"]:
+            fed[rid] += len(toks)

@@ -1,0 +1,299 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of mini_infer_b200 on one B200, as one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The model has the layer sizes of Qwen1.5-MoE-A2.7B (24 layers, hidden 2048, 16 heads of 128,
+60 experts of 1408 with top-4 routing, a shared expert of 5632, vocabulary 151936), random
+bfloat16 weights and seeded uniform-random token ids.  The headline ``value`` is decoded tokens
+per second at batch 8 with 2,048-token prompts in a 4,096-token context: K timed decode steps,
+timed on the device with CUDA events after W warm-up steps.  ``e2e`` is the same metric through
+the scheduler that the Python entry point drives (host token ids in through pinned memory, sampled
+ids back to the host, every step).  ``prefill`` times one 2,048-token prompt; ``points`` holds
+decode at batch 1 and 64; ``roofline`` divides the bytes a decode step must read (every weight it
+uses once, the cache of the live requests) by its time.  Every step reads far more than the
+126 MB of L2 (gigabytes of weights), so no separate flush is needed between timed iterations.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE configs[2]: Qwen1.5-MoE-A2.7B layer sizes
+A27B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "vocab_size": 151936, "hidden_size": 2048, "intermediate_size": 5632, "num_hidden_layers": 24,
+    "num_attention_heads": 16, "num_key_value_heads": 16, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "max_position_embeddings": 8192, "tie_word_embeddings": False, "hidden_act": "silu",
+    "num_experts": 60, "num_experts_per_tok": 4, "moe_intermediate_size": 1408,
+    "shared_expert_intermediate_size": 5632, "norm_topk_prob": False, "decoder_sparse_step": 1,
+    "mlp_only_layers": [], "use_sliding_window": False, "sliding_window": 32768, "max_window_layers": 21,
+}
+FULL_LAYERS = 24
+PUBLISHED_DECODE_B1 = 37.0          # the reference's only Qwen2-MoE number: "~37 tok/s", batch 1, FP16, RTX A6000
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            j = json.load(f)
+        return {"hbm_gbs": j["hbm_gbs"], "bf16_tflops": j["bf16_tflops"],
+                "bf16_tflops_sustained": j.get("bf16_tflops_sustained", j["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device=0):
+        self.device = device
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def weight_bytes_decode(cfg, layers, distinct_experts_per_layer, item=2):
+    """Bytes of weights one decode step reads: every matrix it uses once."""
+    H, d = cfg["hidden_size"], cfg["hidden_size"] // cfg["num_attention_heads"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    mI, sI, E, V = cfg["moe_intermediate_size"], cfg["shared_expert_intermediate_size"], cfg["num_experts"], cfg["vocab_size"]
+    attn = (nh + 2 * nkv) * d * H + (nh + 2 * nkv) * d + nh * d * H
+    norms = 2 * H
+    router = (E + 1) * H
+    shared = 3 * sI * H
+    per_expert = 3 * mI * H
+    total = 0
+    for n_exp in distinct_experts_per_layer:
+        total += attn + norms + router + shared + n_exp * per_expert
+    total += H + V * H            # final norm, output head (the embedding rows read are negligible)
+    return total * item
+
+
+def prefill_flops(cfg, layers, T):
+    """Multiply-add flops (2 per MAC) of one whole prompt of T tokens, logits at the last row."""
+    H, d = cfg["hidden_size"], cfg["hidden_size"] // cfg["num_attention_heads"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    mI, sI, E, K, V = (cfg["moe_intermediate_size"], cfg["shared_expert_intermediate_size"], cfg["num_experts"],
+                       cfg["num_experts_per_tok"], cfg["vocab_size"])
+    per_tok = 2 * ((nh + 2 * nkv) * d * H + nh * d * H + (E + 1) * H + 3 * sI * H + K * 3 * mI * H)
+    attn = 2 * 2 * nh * d * (T * (T + 1) // 2)           # QK^T and PV over the causal half
+    return layers * (per_tok * T + attn) + 2 * V * H
+
+
+def run_ours(args):
+    import torch
+    from mini_infer_b200.engine.llm import GPUExecutor
+    from mini_infer_b200.engine.loading import random_model
+    from mini_infer_b200.engine.request import Request
+    from mini_infer_b200.engine.scheduler import Scheduler, SchedulerConfig
+    from mini_infer_b200.engine.step import ModelRunner, StepEntry
+    from mini_infer_b200.engine.defaults import DEFAULT_PAGE_SIZE
+    from mini_infer_b200.ops.library import launch_count
+    from mini_infer_b200.sampling import SamplingParams
+    from mini_infer_b200.sampling.sampler import Sampler
+
+    pk = peaks()
+    cfg = dict(A27B)
+    cfg["num_hidden_layers"] = args.layers
+    dev = "cuda:0"
+    t0 = time.time()
+    model, rt = random_model(cfg, seed=args.seed, dtype="bfloat16", device=dev)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+    page = DEFAULT_PAGE_SIZE
+    prompt_len, ctx_len = args.prompt_len, args.context
+    max_b = max(args.batch, 64 if args.points else args.batch, 1)
+    per_req_tokens = prompt_len + args.steps + args.warmup + 8
+    num_pages = max_b * (-(-per_req_tokens // page)) + 8
+    runner = ModelRunner(model, rt, page_size=page, num_pages=num_pages, max_requests=max_b,
+                         max_tokens_per_step=max(2048, max_b), max_context=ctx_len)
+    sampler = Sampler(rt.device, cfg["vocab_size"], max_b)
+    g = torch.Generator().manual_seed(args.seed)
+
+    def random_prompt(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+
+    def time_events(fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    # ---- prefill: one request of prompt_len tokens, logits at the last row ------------------- #
+    def prefill_once():
+        runner.add_request("pf")
+        toks = random_prompt(prompt_len)
+        ms = time_events(lambda: runner.step([StepEntry("pf", toks, [prompt_len - 1])]))
+        runner.release("pf")
+        return ms
+    for _ in range(2):
+        prefill_once()
+    pf_ms = min(prefill_once() for _ in range(3))
+    pf_flops = prefill_flops(cfg, args.layers, prompt_len)
+    prefill = {"value": round(prompt_len / (pf_ms / 1e3), 1), "tokens": prompt_len, "ms": round(pf_ms, 3),
+               "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(pf_flops / (pf_ms / 1e3) / 1e12, 2), "of": pk["source"]}
+
+    # ---- decode through the scheduler (what the Python entry point drives) -------------------- #
+    def decode_run(batch, steps, warmup, clocks=False):
+        ex = GPUExecutor(runner, sampler)
+        sched = Scheduler(ex, SchedulerConfig(max_tokens_per_step=max(2048, batch), max_running=batch,
+                                              prefill_chunk=2048, max_context=ctx_len))
+        sp = SamplingParams(greedy=True, max_new_tokens=steps + warmup + 4)
+        for i in range(batch):
+            sched.submit(Request(("bench", batch, i), random_prompt(prompt_len), sp, stream=i))
+        while any(r.remaining > 1 for r in sched.running) or sched.waiting:     # untimed prefill
+            sched.step()
+        for _ in range(warmup):
+            sched.step()
+        sampler_clock = ClockSampler() if clocks else None
+        if sampler_clock:
+            sampler_clock.start()
+        torch.cuda.synchronize()
+        launches0 = launch_count()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        a.record()
+        for _ in range(steps):
+            st = sched.step()
+            assert st.decode_tokens == batch and st.prefill_tokens == 0
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - w0
+        dev_ms = a.elapsed_time(b)
+        launches = launch_count() - launches0
+        clock = sampler_clock.stop() if sampler_clock else None
+        kv_tokens = sum(r.num_computed for r in sched.running)
+        for r in list(sched.running):
+            sched._finish(r, "length")
+        return {"dev_ms": dev_ms, "wall_s": wall, "launches": launches, "clock": clock, "kv_tokens": kv_tokens}
+
+    main = decode_run(args.batch, args.steps, args.warmup, clocks=True)
+    ms_per_step = main["dev_ms"] / args.steps
+    value = args.batch * args.steps / (main["dev_ms"] / 1e3)
+    e2e_value = args.batch * args.steps / main["wall_s"]
+
+    # ---- roofline of the decode step ----------------------------------------------------------- #
+    E, K = cfg["num_experts"], cfg["num_experts_per_tok"]
+    expected_distinct = E * (1.0 - (1.0 - K / E) ** args.batch)
+    wbytes = weight_bytes_decode(cfg, args.layers, [expected_distinct] * args.layers)
+    d = cfg["hidden_size"] // cfg["num_attention_heads"]
+    kv_bytes = main["kv_tokens"] * args.layers * 2 * cfg["num_key_value_heads"] * d * 2
+    achieved = (wbytes + kv_bytes) / (ms_per_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(wbytes + kv_bytes),
+                "of": pk["source"]}
+
+    points = {}
+    if args.points:
+        for b, key in ((1, "decode_b1"), (64, "decode_b64")):
+            r = decode_run(b, max(4, args.steps // 2), 3)
+            points[key] = round(b * max(4, args.steps // 2) / (r["dev_ms"] / 1e3), 1)
+
+    staging_bytes = runner._host.numel() * 4
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen1.5-MoE-A2.7B sizes, 2048-token prompts)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(points.get("decode_b1", 0.0) / PUBLISHED_DECODE_B1, 2) if points else None,
+        "dtype": "bf16", "data": "synthetic: random-init weights, seeded uniform-random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen1.5-MoE-A2.7B layer sizes (Qwen2MoeForCausalLM)", "global_batch": args.batch,
+                   "seq_len": prompt_len, "context": ctx_len, "parallelism": "single GPU",
+                   "layers": args.layers, "layers_of_named_config": FULL_LAYERS, "hidden": 2048, "heads": 16,
+                   "kv_heads": 16, "head_dim": 128, "experts": 60, "top_k": 4, "moe_intermediate": 1408,
+                   "shared_intermediate": 5632, "vocab": 151936, "page_size": page,
+                   "l2": "every step reads GBs of weights (inputs larger than L2)",
+                   "vs_baseline_note": "decode_b1 / the reference's ~37 tok/s (batch 1, FP16, RTX A6000)"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": staging_bytes,
+                "d2h_bytes_per_step": args.batch * 4},
+        "gpu_launches": main["launches"],
+        "clocks": main["clock"],
+        "prefill": prefill, "roofline": roofline, "points": points,
+        "load_seconds": round(load_s, 1),
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def run_reference(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "Deyu-Kong/mini-infer is a CMake/C++ project with no setup.py or pyproject.toml at its root "
+                       "('pip install ... /root/reference' fails: not installable); its binary targets sm_86, needs "
+                       "a real checkpoint with tokenizer.json and runs Qwen2-MoE in FP16 only"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the named configuration's 24 (same layer sizes) where memory or time needs it")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -162,6 +162,41 @@ attn_tiled_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, cons
 // The number of splits of a request depends on its own kv_len only.
 // Partials: part_o [B, nh, max_splits, D], part_ml [B, nh, max_splits, 2].
 // ---------------------------------------------------------------------------
+// E consecutive elements (E a multiple of 8, 16-byte aligned) as floats, with 16-byte loads
+template <typename AT, int E> __device__ __forceinline__ void load_vec(const AT* p, float (&out)[E]);
+template <> __device__ __forceinline__ void load_vec<float, 8>(const float* p, float (&out)[8]) {
+    const float4* v = reinterpret_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { const float4 x = __ldg(v + i); out[4*i] = x.x; out[4*i+1] = x.y; out[4*i+2] = x.z; out[4*i+3] = x.w; }
+}
+template <> __device__ __forceinline__ void load_vec<float, 16>(const float* p, float (&out)[16]) {
+    const float4* v = reinterpret_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float4 x = __ldg(v + i); out[4*i] = x.x; out[4*i+1] = x.y; out[4*i+2] = x.z; out[4*i+3] = x.w; }
+}
+template <> __device__ __forceinline__ void load_vec<float, 32>(const float* p, float (&out)[32]) {
+    const float4* v = reinterpret_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { const float4 x = __ldg(v + i); out[4*i] = x.x; out[4*i+1] = x.y; out[4*i+2] = x.z; out[4*i+3] = x.w; }
+}
+__device__ __forceinline__ void unpack8(const uint4 x, float* out) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); out[2*i] = f.x; out[2*i+1] = f.y; }
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16, 8>(const __nv_bfloat16* p, float (&out)[8]) {
+    unpack8(__ldg(reinterpret_cast<const uint4*>(p)), out);
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16, 16>(const __nv_bfloat16* p, float (&out)[16]) {
+    const uint4* v = reinterpret_cast<const uint4*>(p);
+    unpack8(__ldg(v), out); unpack8(__ldg(v + 1), out + 8);
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16, 32>(const __nv_bfloat16* p, float (&out)[32]) {
+    const uint4* v = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) unpack8(__ldg(v + i), out + 8 * i);
+}
+
 constexpr int DEC_SPLIT = 256;
 constexpr int DEC_GROUPS = 16;
 
@@ -187,11 +222,9 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     const unsigned gmask = 0xFFu << ((tid & 31) & ~7);
     const int t = q_start[b];
     float qr[E];
-    {
-        const AT* qp = q + ((int64_t)t * nh + h) * D + sub * E;
+    load_vec<AT, E>(q + ((int64_t)t * nh + h) * D + sub * E, qr);
 #pragma unroll
-        for (int i = 0; i < E; ++i) qr[i] = to_float(qp[i]) * scale;
-    }
+    for (int i = 0; i < E; ++i) qr[i] *= scale;
     float m_run = -INFINITY, l_run = 0.f;
     float acc[E];
 #pragma unroll
@@ -199,26 +232,49 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     const int* table = block_table + (int64_t)b * max_pages;
     const int k_lo = max(sp * DEC_SPLIT, k_first);
     const int k_hi = min(kvl, (sp + 1) * DEC_SPLIT);
-    for (int kj = sp * DEC_SPLIT + grp; kj < k_hi; kj += DEC_GROUPS) {
-        if (kj < k_lo) continue;
-        const int page = table[kj / page_size];
-        if (page < 0) continue;
-        const int64_t off = ((int64_t)page * nkv + hk) * page_size * D + (int64_t)(kj % page_size) * D + sub * E;
-        float kr[E], vr[E];
+    // two keys per round: both are loaded before either is used
+    for (int kj = sp * DEC_SPLIT + grp; kj < k_hi; kj += 2 * DEC_GROUPS) {
+        const int kj2 = kj + DEC_GROUPS;
+        int64_t off1 = -1, off2 = -1;
+        if (kj >= k_lo) {
+            const int page = table[kj / page_size];
+            if (page >= 0) off1 = ((int64_t)page * nkv + hk) * page_size * D + (int64_t)(kj % page_size) * D + sub * E;
+        }
+        if (kj2 >= k_lo && kj2 < k_hi) {
+            const int page = table[kj2 / page_size];
+            if (page >= 0) off2 = ((int64_t)page * nkv + hk) * page_size * D + (int64_t)(kj2 % page_size) * D + sub * E;
+        }
+        float k1[E], v1[E], k2[E], v2[E];
+        if (off1 >= 0) { load_vec<AT, E>(k_cache + off1, k1); load_vec<AT, E>(v_cache + off1, v1); }
+        if (off2 >= 0) { load_vec<AT, E>(k_cache + off2, k2); load_vec<AT, E>(v_cache + off2, v2); }
+        if (off1 >= 0) {
+            float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < E; ++i) { kr[i] = to_float(k_cache[off + i]); vr[i] = to_float(v_cache[off + i]); }
-        float dot = 0.f;
+            for (int i = 0; i < E; ++i) dot += qr[i] * k1[i];
 #pragma unroll
-        for (int i = 0; i < E; ++i) dot += qr[i] * kr[i];
+            for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
+            const float m_new = fmaxf(m_run, dot);
+            const float alpha = expf(m_run - m_new);
+            const float p = expf(dot - m_new);
+            l_run = l_run * alpha + p;
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
-        const float m_new = fmaxf(m_run, dot);
-        const float alpha = expf(m_run - m_new);
-        const float p = expf(dot - m_new);
-        l_run = l_run * alpha + p;
+            for (int i = 0; i < E; ++i) acc[i] = acc[i] * alpha + p * v1[i];
+            m_run = m_new;
+        }
+        if (off2 >= 0) {
+            float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < E; ++i) acc[i] = acc[i] * alpha + p * vr[i];
-        m_run = m_new;
+            for (int i = 0; i < E; ++i) dot += qr[i] * k2[i];
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
+            const float m_new = fmaxf(m_run, dot);
+            const float alpha = expf(m_run - m_new);
+            const float p = expf(dot - m_new);
+            l_run = l_run * alpha + p;
+#pragma unroll
+            for (int i = 0; i < E; ++i) acc[i] = acc[i] * alpha + p * v2[i];
+            m_run = m_new;
+        }
     }
     // merge the 16 groups in group order
     __shared__ float sm_m[DEC_GROUPS], sm_l[DEC_GROUPS];
@@ -373,7 +429,7 @@ int mi_attn_decode(const void* q, const void* k_cache, const void* v_cache, int 
     MI_DISPATCH_1(adtype, AT,
         if (d == 64) MI_DEC(64); else if (d == 128) MI_DEC(128); else MI_DEC(256));
 #undef MI_DEC
-    return finish_launch("attn_decode");
+    return finish_launch("attn_decode", 2);
 }
 
 }  // extern "C"

@@ -70,14 +70,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 void set_last_error(const char* fmt, ...);
 
-inline int finish_launch(const char* what) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        set_last_error("%s: %s", what, cudaGetErrorString(e));
-        return kLaunchFailed;
-    }
-    return kOk;
-}
+// Checks cudaGetLastError after a launcher queued `n_kernels` kernels and counts them.
+int finish_launch(const char* what, int n_kernels = 1);
 
 }  // namespace mi
 

@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -27,6 +28,18 @@ void set_last_error(const char* fmt, ...) {
     va_start(ap, fmt);
     vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
     va_end(ap);
+}
+
+static std::atomic<long long> g_launches{0};
+
+int finish_launch(const char* what, int n_kernels) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_last_error("%s: %s", what, cudaGetErrorString(e));
+        return kLaunchFailed;
+    }
+    g_launches.fetch_add(n_kernels, std::memory_order_relaxed);
+    return kOk;
 }
 
 // ---------------------------------------------------------------------------
@@ -192,6 +205,9 @@ using namespace mi;
 extern "C" {
 
 const char* mi_last_error() { return g_last_error; }
+
+// Kernels of this library queued since it was loaded (all threads).
+long long mi_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int mi_embed_gather(const int* ids, const void* table, int wdtype, float* hidden, int T, int H, int V,
                     cudaStream_t stream) {

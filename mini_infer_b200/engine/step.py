@@ -59,7 +59,7 @@ class ModelRunner:
     """
 
     def __init__(self, model: Model, rt: Runtime, *, page_size: int, num_pages: int, max_requests: int,
-                 max_tokens_per_step: int, max_context: int):
+                 max_tokens_per_step: int, max_context: int, cuda_graphs: bool = True):
         if rt.device.type != "cuda":
             raise RuntimeError("ModelRunner: the engine runs on a CUDA device only; there is no CPU path")
         self.model = model
@@ -83,6 +83,14 @@ class ModelRunner:
                         for k, n in model.scratch_need(max_requests, max_context).items()}
         self.max_pages = -(-self.max_context // self.page_size)
         self._layout_staging()
+        # Decode steps (one token per request, logits wanted for each) are launch-bound: their
+        # forward pass is captured once per batch size as a CUDA graph and replayed.  Parts that
+        # keep host-side state per step, or were not written with replay in mind, switch this off.
+        self.cuda_graphs = bool(cuda_graphs) and not model.state_needs and \
+            all(getattr(p, "graph_safe", False) for p in model.all_parts())
+        self._graphs: Dict[int, Tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ #
     # staging: one pinned buffer, one copy per step
@@ -243,11 +251,45 @@ class ModelRunner:
         logit_rows = d("logit_rows", R) if R else None
         return ctx, logit_rows, index
 
+    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+        if not self.cuda_graphs:
+            return False
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return False
+        return not any(getattr(p, "keep_routing", False) for p in self.model.all_parts())
+
+    def _decode_with_graph(self, ctx: StepContext, logit_rows: torch.Tensor) -> torch.Tensor:
+        """Replay (or first capture) the forward pass for this batch size.  The captured pass reads
+        the same staging views every time and is launched with the worst-case context length, so
+        only the data in the staging buffer changes between replays."""
+        B = ctx.num_requests
+        ctx.max_kv_len = self.max_context
+        if B not in self._graphs:
+            side = torch.cuda.Stream(device=self.rt.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.model.forward(ctx, logit_rows)          # warm-up: library workspaces, lazy init
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(self.rt.device)
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self._graph_pool):
+                out = self.model.forward(ctx, logit_rows)
+            self._graphs[B] = (g, out)
+        g, out = self._graphs[B]
+        g.replay()
+        self.graph_replays += 1
+        return out
+
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> StepResult:
         ctx, logit_rows, index = self.prepare(entries)
         try:
-            logits = self.model.forward(ctx, logit_rows)
+            if self._graph_eligible(entries):
+                logits = self._decode_with_graph(ctx, logit_rows)
+            else:
+                logits = self.model.forward(ctx, logit_rows)
         except Exception:
             for e in entries:
                 self.cache.cancel(e.rid)

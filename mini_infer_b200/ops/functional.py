@@ -296,6 +296,30 @@ def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch
     return out
 
 
+def grouped_gemm_skinny_supported(kd: int) -> bool:
+    return bool(library().mi_grouped_gemm_skinny_supported(int(kd)))
+
+
+def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
+                        n_rows: int, swiglu_pair: bool) -> torch.Tensor:
+    """The grouped product for a few rows per expert (decode), bfloat16 on tensor cores.
+
+    Same contract as :func:`grouped_gemm_plain`; the result is bfloat16 with ``swiglu_pair``
+    (the activation that feeds the down projection) and float32 without.
+    """
+    _chk(a, "grouped_gemm_skinny a", BF16)
+    Kd = a.shape[1]
+    _chk(w, "grouped_gemm_skinny w", BF16, (None, None, Kd))
+    E, wrows, _ = w.shape
+    nout = wrows // 2 if swiglu_pair else wrows
+    _chk(gather, "grouped_gemm_skinny gather", I32)
+    _chk(offsets, "grouped_gemm_skinny offsets", I32, (E + 1,))
+    out = torch.empty(n_rows, nout, dtype=BF16 if swiglu_pair else F32, device=a.device)
+    check(library().mi_grouped_gemm_skinny(_ptr(a), _ptr(gather), _ptr(w), _ptr(offsets), _ptr(out), E, nout, Kd,
+                                           1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny")
+    return out
+
+
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                 top_p: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
                 probs_scratch: Optional[torch.Tensor] = None,

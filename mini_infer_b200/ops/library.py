@@ -31,6 +31,7 @@ _SIGNATURES = {
     "mi_moe_permute": [P, P, P, P, I, I, I, P],
     "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
+    "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],
 }
 
 
@@ -51,13 +52,22 @@ def library() -> ctypes.CDLL:
         fn.restype = c_int
     lib.mi_last_error.restype = c_char_p
     lib.mi_last_error.argtypes = []
+    lib.mi_launch_count.restype = ctypes.c_longlong
+    lib.mi_launch_count.argtypes = []
     lib.mi_attn_decode_supported.argtypes = [I]
     lib.mi_attn_decode_supported.restype = c_int
+    lib.mi_grouped_gemm_skinny_supported.argtypes = [I]
+    lib.mi_grouped_gemm_skinny_supported.restype = c_int
     lib.mi_attn_decode_split_size.argtypes = []
     lib.mi_attn_decode_split_size.restype = c_int
     _lib = lib
     _lib_path = path
     return lib
+
+
+def launch_count() -> int:
+    """Kernels of this library queued so far in this process."""
+    return int(library().mi_launch_count())
 
 
 def library_path() -> Optional[str]:

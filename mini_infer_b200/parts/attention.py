@@ -30,6 +30,8 @@ class GQAttention(Mixer):
     ``bias``, ``<prefix>o_proj.weight [hidden, num_heads*head_dim]``.
     """
 
+    graph_safe = True
+
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         p = self.params

@@ -20,6 +20,8 @@ from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, 
 
 
 class PreNormResidual(Block):
+    graph_safe = True
+
     def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending: Optional[torch.Tensor],
                 ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         x = layer.mixer_norm.apply(hidden, pending)
@@ -31,6 +33,8 @@ class PreNormResidual(Block):
 class TokenEmbedding(Embedding):
     """params: ``vocab_size``, ``hidden_size``.  Tensor: ``<prefix>weight [V, H]``; no scaling
     (src/model/transformer_model.cpp:561-565)."""
+
+    graph_safe = True
 
     def tensor_decls(self) -> List[TensorDecl]:
         return [TensorDecl(self.prefix + "weight", (self.params["vocab_size"], self.params["hidden_size"]))]
@@ -47,6 +51,8 @@ class LinearHead(LMHead):
     """params: ``vocab_size``, ``hidden_size``, ``tied_to`` (name of the embedding tensor, or
     None).  Tensor: ``<prefix>weight [V, H]`` unless tied (src/model/transformer_model.cpp:355-361;
     the reference deep-copies the tied matrix, here it is the same storage)."""
+
+    graph_safe = True
 
     def tensor_decls(self) -> List[TensorDecl]:
         if self.params.get("tied_to"):

@@ -24,6 +24,8 @@ class SwiGLUMLP(FeedForward):
     Tensors: ``<prefix>{gate,up}_proj.weight [I, H]``, ``<prefix>down_proj.weight [H, I]``.
     """
 
+    graph_safe = True
+
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.H = int(self.params["hidden_size"])
@@ -57,6 +59,10 @@ class SparseMoE(FeedForward):
     ``<prefix>experts.{e}.{gate,up}_proj.weight [mI, H]``, ``.down_proj.weight [H, mI]``;
     ``<prefix>shared_expert.{gate,up,down}_proj.weight``, ``<prefix>shared_expert_gate.weight [1, H]``.
     """
+
+    graph_safe = True
+    # up to this many rows per expert on average, the decode-sized grouped product is used
+    SKINNY_ROWS_PER_EXPERT = 8
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -108,6 +114,8 @@ class SparseMoE(FeedForward):
             self.w_shared_down = m(tensors[q + "down_proj.weight"], dev)
             g = rt.precision.small(tensors[p + "shared_expert_gate.weight"], dev).reshape(-1)
             self.w_shared_gate = g.to(self.w_router.dtype).contiguous()
+        self._skinny = (rt.act == torch.bfloat16 and F.grouped_gemm_skinny_supported(self.H)
+                        and F.grouped_gemm_skinny_supported(self.mI))
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = x.shape[0]
@@ -117,8 +125,13 @@ class SparseMoE(FeedForward):
             self.last_routing = (idx, w, probs)
         offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
         n = T * self.K
-        act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
-        y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
+        if self._skinny and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
+            # a few rows per expert: bound by reading each used expert once
+            act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
+            y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
+        else:
+            act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
+            y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         shared = None
         if self.sI > 0:
             gu = linear(x, self.w_shared_gate_up, self.rt.act)

@@ -18,6 +18,8 @@ from .base import Norm, Runtime, TensorDecl
 class RMSNorm(Norm):
     """params: ``size``, ``eps``.  Tensor: ``<prefix>weight [size]``."""
 
+    graph_safe = True
+
     def tensor_decls(self) -> List[TensorDecl]:
         return [TensorDecl(self.prefix + "weight", (self.params["size"],), "norm")]
 

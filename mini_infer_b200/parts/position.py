@@ -25,6 +25,8 @@ from .base import PositionEncoding
 class RotaryEncoding(PositionEncoding):
     """params: ``head_dim``, ``theta``, optional ``rot_dim`` (default ``head_dim``)."""
 
+    graph_safe = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         d = int(self.params["head_dim"])
@@ -44,6 +46,7 @@ class RotaryEncoding(PositionEncoding):
 
 
 class NoPositionEncoding(PositionEncoding):
+    graph_safe = True
     rot_dim = 0
 
     def table(self, device) -> Optional[torch.Tensor]:

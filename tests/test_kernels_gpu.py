@@ -357,6 +357,30 @@ def test_grouped_gemm_plain(adt, T, E, K, H, I):
     close(y, ref_y, 3e-6 if adt == torch.float32 else 1e-2, "down product")
 
 
+@pytest.mark.parametrize("T,E,K,H,I", [(1, 8, 2, 64, 32), (8, 60, 4, 256, 96), (64, 12, 4, 128, 72), (37, 6, 3, 96, 40),
+                                       (200, 5, 1, 64, 24)])
+def test_grouped_gemm_skinny_equals_plain(T, E, K, H, I):
+    """The decode-sized tensor-core product against the plain kernel: 0, 1, 8, 9, 16 and more rows
+    per expert; feature counts that are no multiple of the 16-row tile."""
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
+    x = rnd(T, H, dtype=torch.bfloat16, seed=1)
+    wgu = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.2, seed=2)
+    wd = rnd(E, H, I, dtype=torch.bfloat16, scale=0.2, seed=3)
+    assert F().grouped_gemm_skinny_supported(H)
+    act = F().grouped_gemm_skinny(x, sorted_token, wgu, offsets, T * K, True)
+    ref = F().grouped_gemm_plain(x, sorted_token, wgu, offsets, T * K, True, torch.float32)
+    close(act, ref, 6e-3, "gate/up product")
+    if F().grouped_gemm_skinny_supported(I):
+        y = F().grouped_gemm_skinny(act, None, wd, offsets, T * K, False)
+        ref_y = F().grouped_gemm_plain(act, None, wd, offsets, T * K, False, torch.float32)
+        close(y, ref_y, 2e-5, "down product")
+    from mini_infer_b200.ops.library import KernelError
+    with pytest.raises(KernelError, match="multiple of 32"):
+        F().grouped_gemm_skinny(x[:, :48].contiguous(), sorted_token, wgu[:, :, :48].contiguous(), offsets, T * K, True)
+
+
 # --------------------------------------------------------------------------- #
 # sampling
 # --------------------------------------------------------------------------- #

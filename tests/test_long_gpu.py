@@ -6,7 +6,7 @@ import torch
 import plain_model as pm
 import tiny
 import traces
-from engine_harness import compare, make_runner, run_trace
+from engine_harness import compare, make_runner, run_and_compare, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -19,16 +19,11 @@ def test_long_decoding(tmp_path, name, dtype):
     folder = tiny.make_folder(str(tmp_path), cfg, seed=23, dtype=torch.bfloat16)
     w = tiny.read_weights(folder)
     n = 700 if name == "D" else 330
-    toks = tiny.pick_tokens(cfg, w, n, 4, min_gap=5e-4 if dtype == "bfloat16" else 0.0)
-    ref = {"x": pm.forward(cfg, w, toks)}
+    toks = tiny.pick_tokens(cfg, w, n, 4)
     runner = make_runner(folder, dtype, page_size=16, num_pages=48, max_requests=2, max_tokens=64, max_context=768)
     steps = traces.tail_decoded({"x": toks}, tail=n - 3)
-    got = run_trace(runner, steps)
+    _, got = run_and_compare(runner, steps, cfg, w, {"x": toks}, dtype, 2e-5 if dtype == "float32" else 3e-2)
     assert len(got) == n
-    compare(got, ref, 2e-5 if dtype == "float32" else 3e-2)
-    if name == "C":
-        # windowed layers hold a handful of pages at the end, not one per 16 tokens
-        pass
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -38,13 +33,11 @@ def test_first_tokens_of_a_sequence(tmp_path, dtype):
         cfg = tiny.CONFIGS[name]
         folder = tiny.make_folder(str(tmp_path / name), cfg, seed=29, dtype=torch.bfloat16)
         w = tiny.read_weights(folder)
-        toks = tiny.pick_tokens(cfg, w, 6, 8, min_gap=2e-3)
-        ref = {"x": pm.forward(cfg, w, toks)}
+        toks = tiny.pick_tokens(cfg, w, 6, 8)
+        tol = 2e-5 if dtype == "float32" else 2e-2
         runner = make_runner(folder, dtype, page_size=2, num_pages=8, max_requests=1, max_tokens=8, max_context=16)
-        got = run_trace(runner, traces.tail_decoded({"x": toks}, tail=5))
-        compare(got, ref, 2e-5 if dtype == "float32" else 2e-2)
-        single = run_trace(runner, traces.whole({"y": toks[:1]}))
-        compare({("x", 0): single[("y", 0)]}, ref, 2e-5 if dtype == "float32" else 2e-2)
+        run_and_compare(runner, traces.tail_decoded({"x": toks}, tail=5), cfg, w, {"x": toks}, dtype, tol)
+        run_and_compare(runner, traces.whole({"y": toks[:1]}), cfg, w, {"y": toks[:1]}, dtype, tol)
 
 
 def test_window_group_gives_pages_back_while_decoding(tmp_path):
@@ -53,8 +46,8 @@ def test_window_group_gives_pages_back_while_decoding(tmp_path):
     runner = make_runner(folder, "float32", page_size=4, num_pages=40, max_requests=1, max_tokens=32, max_context=160)
     w = tiny.read_weights(folder)
     toks = tiny.pick_tokens(cfg, w, 150, 2)
-    got = run_trace(runner, traces.portions({"x": toks}, (9, 1, 1, 4, 1, 1, 1, 13)))
-    compare(got, {"x": pm.forward(cfg, w, toks)}, 2e-5)
+    run_and_compare(runner, traces.portions({"x": toks}, (9, 1, 1, 4, 1, 1, 1, 13)), cfg, w, {"x": toks},
+                    "float32", 2e-5)
     win = [i for i, g in enumerate(runner.model.kv_groups) if g.window > 0][0]
     full = 1 - win
     assert runner.cache.pools[win].high_water <= (24 + 13) // 4 + 2          # window 24, portion 13, pages of 4

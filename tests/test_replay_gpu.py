@@ -15,7 +15,7 @@ import torch
 import plain_model
 import tiny
 import traces
-from engine_harness import compare, make_runner, run_trace
+from engine_harness import compare, make_runner, run_and_compare, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -32,12 +32,8 @@ def case(request, tmp_path_factory):
     folder = str(tmp_path_factory.mktemp(f"model_{name}"))
     tiny.make_folder(folder, cfg, seed=11 + ord(name), dtype=torch.bfloat16)
     weights = tiny.read_weights(folder)
-    reqs, ref = {}, {}
-    for i, n in enumerate(LENGTHS[name]):
-        toks = tiny.pick_tokens(cfg, weights, n, seed=1000 * (i + 1), min_gap=2e-3)
-        reqs[f"r{i}"] = toks
-        ref[f"r{i}"] = plain_model.forward(cfg, weights, toks)
-    return {"name": name, "cfg": cfg, "folder": folder, "reqs": reqs, "ref": ref}
+    reqs = {f"r{i}": tiny.pick_tokens(cfg, weights, n, seed=1000 * (i + 1)) for i, n in enumerate(LENGTHS[name])}
+    return {"name": name, "cfg": cfg, "folder": folder, "reqs": reqs, "weights": weights}
 
 
 @pytest.fixture(scope="module", params=["float32", "bfloat16"])
@@ -50,20 +46,21 @@ def _runner(case, dtype, num_pages=64, page_size=16):
                        max_tokens=512, max_context=512)
 
 
+def _check(case, dtype, runner, steps):
+    return run_and_compare(runner, steps, case["cfg"], case["weights"], case["reqs"], dtype, TOL[dtype])
+
+
 def test_whole(case, dtype):
-    got = run_trace(_runner(case, dtype), traces.whole(case["reqs"]))
+    _, got = _check(case, dtype, _runner(case, dtype), traces.whole(case["reqs"]))
     assert len(got) == sum(len(t) for t in case["reqs"].values())
-    compare(got, case["ref"], TOL[dtype])
 
 
 def test_tail_decoded_one_by_one(case, dtype):
-    got = run_trace(_runner(case, dtype), traces.tail_decoded(case["reqs"], 32))
-    compare(got, case["ref"], TOL[dtype])
+    _check(case, dtype, _runner(case, dtype), traces.tail_decoded(case["reqs"], 32))
 
 
 def test_portions_of_changing_size(case, dtype):
-    got = run_trace(_runner(case, dtype), traces.portions(case["reqs"]))
-    compare(got, case["ref"], TOL[dtype])
+    _check(case, dtype, _runner(case, dtype), traces.portions(case["reqs"]))
 
 
 @pytest.mark.parametrize("page_size", [16, 4])
@@ -73,9 +70,8 @@ def test_mixed_with_pages_used_again(case, dtype, page_size):
     total = sum(-(-len(t) // 64) * 64 for t in case["reqs"].values())
     assert peak < total, "the trace must not fit the pool without reuse"
     runner = _runner(case, dtype, num_pages=peak // page_size, page_size=page_size)
-    got = run_trace(runner, steps)
+    _, got = _check(case, dtype, runner, steps)
     assert len(got) == sum(len(t) for t in case["reqs"].values())
-    compare(got, case["ref"], TOL[dtype])
     assert runner.cache.used_pages() == [0] * len(runner.cache.pools)
     assert all(p.high_water <= p.num_pages for p in runner.cache.pools)
 

@@ -12,6 +12,7 @@ import torch
 import plain_model as pm
 import tiny
 import traces
+from engine_harness import GAP_TOL, reference_logits
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -23,7 +24,7 @@ def replay(folder, dtype, steps, out_dir, max_tokens):
         lines.append(json.dumps({"step": i, "entries": [{"id": rid, "tokens": toks, "want": want}
                                                         for rid, toks, want in st["entries"]], "end": st["end"]}))
     p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", out_dir,
-                        "--max-tokens", str(max_tokens)], input="\n".join(lines) + "\n", capture_output=True,
+                        "--max-tokens", str(max_tokens), "--dump-routing"], input="\n".join(lines) + "\n", capture_output=True,
                        text=True, timeout=900)
     assert p.returncode == 0, p.stderr[-3000:]
     assert p.stdout.split() == [x for i in range(len(steps)) for x in ("done", str(i))]
@@ -35,7 +36,7 @@ def test_trace_run_mixed(tmp_path, name, dtype):
     cfg = tiny.CONFIGS[name]
     folder = tiny.make_folder(str(tmp_path / "model"), cfg, seed=17, dtype=torch.bfloat16)
     w = tiny.read_weights(folder)
-    reqs = {f"q{i}": tiny.pick_tokens(cfg, w, n, 50 + i, min_gap=2e-3) for i, n in enumerate([40, 66, 12, 35, 90, 20])}
+    reqs = {f"q{i}": tiny.pick_tokens(cfg, w, n, 50 + i) for i, n in enumerate([40, 66, 12, 35, 90, 20])}
     steps = traces.mixed(reqs, max_live=4, seed=9)
     for st in steps[::3]:                                   # some steps want nothing, some only the last place
         st["entries"] = [(rid, toks, []) for rid, toks, _ in st["entries"]]
@@ -43,7 +44,19 @@ def test_trace_run_mixed(tmp_path, name, dtype):
         st["entries"] = [(rid, toks, [len(toks) - 1]) for rid, toks, _ in st["entries"]]
     out = str(tmp_path / "out")
     replay(folder, dtype, steps, out, traces.live_token_peak(steps, 64))
-    ref = {rid: pm.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    # the experts the engine chose, per request, layer and position (see engine_harness)
+    routing, fed = {}, {rid: 0 for rid in reqs}
+    for i, st in enumerate(steps):
+        with open(os.path.join(out, f"{i}.routing.json")) as f:
+            chosen = json.load(f)
+        t = 0
+        for rid, toks, _ in st["entries"]:
+            for j in range(len(toks)):
+                for li, rows in chosen.items():
+                    routing.setdefault(rid, {}).setdefault(int(li), {})[fed[rid] + j] = rows[t + j]
+            t += len(toks)
+            fed[rid] += len(toks)
+    ref = {rid: reference_logits(cfg, w, toks, routing.get(rid), GAP_TOL[dtype], rid) for rid, toks in reqs.items()}
     fed = {rid: 0 for rid in reqs}
     tol = 2e-5 if dtype == "float32" else 2e-2
     V = cfg["vocab_size"]

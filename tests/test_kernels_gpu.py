@@ -288,7 +288,8 @@ def test_router(adt, wdt, E, K, norm):
     s = torch.sort(rp, dim=-1, descending=True).values
     clear = torch.ones(T, dtype=torch.bool)
     for k in range(min(K, E - 1)):
-        clear &= (s[:, k] - s[:, k + 1]) > 1e-6
+        clear &= (s[:, k] - s[:, k + 1]) > 2e-7
+    assert clear.sum() >= (T // 2 if K <= 8 else 1)
     assert torch.equal(idx.cpu().long()[clear], ri[clear])
     close(w.cpu()[clear], rw[clear], 5e-6, "router weights")
     ref_gate = torch.sigmoid(x.float().cpu() @ wsg.float().cpu())
@@ -423,5 +424,5 @@ def test_sampling_frequencies_follow_the_distribution():
     out = F().sample_rows(logits, t, torch.ones(4000, device=DEV), us)
     freq = torch.bincount(out.cpu().long(), minlength=5).float() / 4000
     assert float((freq - torch.softmax(logits[0].cpu(), -1)).abs().max()) < 0.03
-    out2 = F().sample_rows(logits, t, torch.full((4000,), 0.6, device=DEV), us)   # nucleus {2, 4}
+    out2 = F().sample_rows(logits, t, torch.full((4000,), 0.8, device=DEV), us)   # nucleus {2, 4}
     assert set(out2.cpu().tolist()) == {2, 4}

@@ -146,7 +146,7 @@ def run_ours(args):
     page = DEFAULT_PAGE_SIZE
     prompt_len, ctx_len = args.prompt_len, args.context
     max_b = max(args.batch, 64 if args.points else args.batch, 1)
-    per_req_tokens = prompt_len + args.steps + args.warmup + 8
+    per_req_tokens = prompt_len + args.steps + args.warmup + 2 * max_b + 16
     num_pages = max_b * (-(-per_req_tokens // page)) + 8
     runner = ModelRunner(model, rt, page_size=page, num_pages=num_pages, max_requests=max_b,
                          max_tokens_per_step=max(2048, max_b), max_context=ctx_len)
@@ -185,7 +185,8 @@ def run_ours(args):
         ex = GPUExecutor(runner, sampler)
         sched = Scheduler(ex, SchedulerConfig(max_tokens_per_step=max(2048, batch), max_running=batch,
                                               prefill_chunk=2048, max_context=ctx_len))
-        sp = SamplingParams(greedy=True, max_new_tokens=steps + warmup + 4)
+        sp = SamplingParams(greedy=True, max_new_tokens=steps + warmup + 2 * batch + 8)   # early requests decode
+        # while later prompts are still being prefilled
         for i in range(batch):
             sched.submit(Request(("bench", batch, i), random_prompt(prompt_len), sp, stream=i))
         while any(r.remaining > 1 for r in sched.running) or sched.waiting:     # untimed prefill

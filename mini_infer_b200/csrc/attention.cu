@@ -197,6 +197,31 @@ template <> __device__ __forceinline__ void load_vec<__nv_bfloat16, 32>(const __
     for (int i = 0; i < 4; ++i) unpack8(__ldg(v + i), out + 8 * i);
 }
 
+// E consecutive elements held as they were loaded (16-byte words), unpacked to float when used
+template <typename AT, int E> struct RawVec;
+template <int E> struct RawVec<float, E> {
+    float4 w[E / 4];
+    __device__ __forceinline__ void load(const float* p) {
+#pragma unroll
+        for (int i = 0; i < E / 4; ++i) w[i] = __ldg(reinterpret_cast<const float4*>(p) + i);
+    }
+    __device__ __forceinline__ void unpack(float (&out)[E]) const {
+#pragma unroll
+        for (int i = 0; i < E / 4; ++i) { out[4*i] = w[i].x; out[4*i+1] = w[i].y; out[4*i+2] = w[i].z; out[4*i+3] = w[i].w; }
+    }
+};
+template <int E> struct RawVec<__nv_bfloat16, E> {
+    uint4 w[E / 8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+#pragma unroll
+        for (int i = 0; i < E / 8; ++i) w[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+    }
+    __device__ __forceinline__ void unpack(float (&out)[E]) const {
+#pragma unroll
+        for (int i = 0; i < E / 8; ++i) unpack8(w[i], &out[8 * i]);
+    }
+};
+
 constexpr int DEC_SPLIT = 256;
 constexpr int DEC_GROUPS = 16;
 
@@ -229,50 +254,52 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     float acc[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) acc[i] = 0.f;
-    const int* table = block_table + (int64_t)b * max_pages;
     const int k_lo = max(sp * DEC_SPLIT, k_first);
     const int k_hi = min(kvl, (sp + 1) * DEC_SPLIT);
-    // two keys per round: both are loaded before either is used
-    for (int kj = sp * DEC_SPLIT + grp; kj < k_hi; kj += 2 * DEC_GROUPS) {
-        const int kj2 = kj + DEC_GROUPS;
-        int64_t off1 = -1, off2 = -1;
-        if (kj >= k_lo) {
-            const int page = table[kj / page_size];
-            if (page >= 0) off1 = ((int64_t)page * nkv + hk) * page_size * D + (int64_t)(kj % page_size) * D + sub * E;
+    // the pages of this split, looked up once
+    __shared__ int64_t key_off[DEC_SPLIT];
+    {
+        const int* table = block_table + (int64_t)b * max_pages;
+        for (int i = tid; i < DEC_SPLIT; i += 128) {
+            const int kj = sp * DEC_SPLIT + i;
+            int64_t off = -1;
+            if (kj >= k_lo && kj < k_hi) {
+                const int page = table[kj / page_size];
+                if (page >= 0) off = ((int64_t)page * nkv + hk) * page_size * D + (int64_t)(kj % page_size) * D;
+            }
+            key_off[i] = off;
         }
-        if (kj2 >= k_lo && kj2 < k_hi) {
-            const int page = table[kj2 / page_size];
-            if (page >= 0) off2 = ((int64_t)page * nkv + hk) * page_size * D + (int64_t)(kj2 % page_size) * D + sub * E;
+    }
+    __syncthreads();
+    // KPR keys per round: all their loads are issued before any is used
+    constexpr int KPR = (sizeof(AT) == 2 || E <= 16) ? 4 : 2;
+    using Raw = RawVec<AT, E>;
+    for (int i0 = grp; i0 < DEC_SPLIT; i0 += KPR * DEC_GROUPS) {
+        int64_t off[KPR];
+        Raw kr[KPR], vr[KPR];
+#pragma unroll
+        for (int u = 0; u < KPR; ++u) {
+            const int i = i0 + u * DEC_GROUPS;
+            off[u] = i < DEC_SPLIT ? key_off[i] : -1;
+            if (off[u] >= 0) { kr[u].load(k_cache + off[u] + sub * E); vr[u].load(v_cache + off[u] + sub * E); }
         }
-        float k1[E], v1[E], k2[E], v2[E];
-        if (off1 >= 0) { load_vec<AT, E>(k_cache + off1, k1); load_vec<AT, E>(v_cache + off1, v1); }
-        if (off2 >= 0) { load_vec<AT, E>(k_cache + off2, k2); load_vec<AT, E>(v_cache + off2, v2); }
-        if (off1 >= 0) {
+#pragma unroll
+        for (int u = 0; u < KPR; ++u) {
+            if (off[u] < 0) continue;
+            float kf[E];
+            kr[u].unpack(kf);
             float dot = 0.f;
 #pragma unroll
-            for (int i = 0; i < E; ++i) dot += qr[i] * k1[i];
+            for (int i = 0; i < E; ++i) dot += qr[i] * kf[i];
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
             const float m_new = fmaxf(m_run, dot);
             const float alpha = expf(m_run - m_new);
             const float p = expf(dot - m_new);
             l_run = l_run * alpha + p;
+            vr[u].unpack(kf);
 #pragma unroll
-            for (int i = 0; i < E; ++i) acc[i] = acc[i] * alpha + p * v1[i];
-            m_run = m_new;
-        }
-        if (off2 >= 0) {
-            float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < E; ++i) dot += qr[i] * k2[i];
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
-            const float m_new = fmaxf(m_run, dot);
-            const float alpha = expf(m_run - m_new);
-            const float p = expf(dot - m_new);
-            l_run = l_run * alpha + p;
-#pragma unroll
-            for (int i = 0; i < E; ++i) acc[i] = acc[i] * alpha + p * v2[i];
+            for (int i = 0; i < E; ++i) acc[i] = acc[i] * alpha + p * kf[i];
             m_run = m_new;
         }
     }

@@ -14,38 +14,81 @@
 namespace mi {
 
 // ---------------------------------------------------------------------------
-// Router: one warp per token.
-//   z_e = x . Wr[e]              (float, lane-strided then butterfly sum)
+// Router: one block per token.
+//   z_e = x . Wr[e]              (float, one warp per expert: lane-strided, then butterfly sum)
 //   p = softmax(z) over all experts
 //   K rounds of arg-max over p, lowest index wins ties (moe_kernel.cu:28-47)
 //   w_k = p[idx_k]  (divided by their sum when norm_topk)
 //   gate = sigmoid(x . Wsg)      (moe_kernel.cu:137-139)
 // ---------------------------------------------------------------------------
+// Dot product of a float row in shared memory with a weight row in global memory; the lanes of a
+// warp take interleaved chunks of 8 (one 16-byte load of bfloat16) and a scalar tail.
+template <typename WT>
+__device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const WT* __restrict__ w, int H, int lane);
+
+template <>
+__device__ __forceinline__ float warp_dot<__nv_bfloat16>(const float* __restrict__ xs, const __nv_bfloat16* __restrict__ w,
+                                                         int H, int lane) {
+    float acc = 0.f;
+    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    const int main = aligned ? (H & ~7) : 0;
+    for (int i = lane * 8; i < main; i += 256) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(w + i));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc += xs[i + 2 * j] * f.x;
+            acc += xs[i + 2 * j + 1] * f.y;
+        }
+    }
+    for (int i = main + lane; i < H; i += 32) acc += xs[i] * __bfloat162float(w[i]);
+    return warp_sum(acc);
+}
+
+template <>
+__device__ __forceinline__ float warp_dot<float>(const float* __restrict__ xs, const float* __restrict__ w, int H, int lane) {
+    float acc = 0.f;
+    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    const int main = aligned ? (H & ~3) : 0;
+    for (int i = lane * 4; i < main; i += 128) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(w + i));
+        acc += xs[i] * v.x;
+        acc += xs[i + 1] * v.y;
+        acc += xs[i + 2] * v.z;
+        acc += xs[i + 3] * v.w;
+    }
+    for (int i = main + lane; i < H; i += 32) acc += xs[i] * w[i];
+    return warp_sum(acc);
+}
+
+// One block (8 warps) per token: the token's row goes to shared memory as float, the warps share
+// out the experts' dot products, warp 0 does softmax, top-k and the weights.  The order of the
+// additions of a dot product depends on H only.
 template <typename AT, typename WT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_router_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
                   int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ gate,
                   float* __restrict__ probs_out, int T, int H, int E, int K, int norm_topk) {
-    extern __shared__ float smem[];  // [4][E]
+    extern __shared__ float smem[];  // [H] token row, [E] logits / probabilities
+    float* xs = smem;
+    float* p = smem + H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= T) return;
-    float* p = smem + warp * E;
+    const int t = blockIdx.x;
     const AT* xr = x + (int64_t)t * H;
-    for (int e = 0; e < E; ++e) {
-        const WT* w = wr + (int64_t)e * H;
-        float acc = 0.f;
-        for (int i = lane; i < H; i += 32) acc += to_float(xr[i]) * to_float(w[i]);
-        acc = warp_sum(acc);
-        if (lane == 0) p[e] = acc;
+    for (int i = threadIdx.x; i < H; i += 256) xs[i] = to_float(xr[i]);
+    __syncthreads();
+    for (int e = warp; e < E + (wsg ? 1 : 0); e += 8) {
+        if (e < E) {
+            const float z = warp_dot<WT>(xs, wr + (int64_t)e * H, H, lane);
+            if (lane == 0) p[e] = z;
+        } else {
+            const float z = warp_dot<WT>(xs, wsg, H, lane);
+            if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-z));
+        }
     }
-    if (wsg) {
-        float acc = 0.f;
-        for (int i = lane; i < H; i += 32) acc += to_float(xr[i]) * to_float(wsg[i]);
-        acc = warp_sum(acc);
-        if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-acc));
-    }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
     mx = warp_max(mx);
@@ -221,13 +264,21 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
         set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
         return kBadShape;
     }
-    const size_t smem = sizeof(float) * 4 * (size_t)E;
-    if (smem > 48 * 1024) {
-        set_last_error("router: %d experts exceed the 3072 this kernel holds in shared memory", E);
+    const size_t smem = sizeof(float) * ((size_t)H + (size_t)E);
+    if (smem > 200 * 1024) {
+        set_last_error("router: hidden size %d plus %d experts exceed the shared memory of a block", H, E);
         return kBadShape;
     }
+    if (T > 0x7fffffff / 2) {
+        set_last_error("router: too many tokens");
+        return kBadShape;
+    }
+#define MI_ROUTER_ATTR(AT, WT)                                                                         \
+    if (smem > 48 * 1024)                                                                              \
+        cudaFuncSetAttribute(moe_router_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
-        moe_router_kernel<AT, WT><<<(T + 3) / 4, 128, smem, stream>>>(
+        MI_ROUTER_ATTR(AT, WT);
+        moe_router_kernel<AT, WT><<<T, 256, smem, stream>>>(
             (const AT*)x, (const WT*)wr, (const WT*)wsg, topk_idx, topk_w, gate, probs_out, T, H, E, K,
             norm_topk));
     return finish_launch("moe_router");

@@ -290,6 +290,8 @@ class ModelRunner:
                 logits = self._decode_with_graph(ctx, logit_rows)
             else:
                 logits = self.model.forward(ctx, logit_rows)
+                from ..ops.functional import check_tc_status
+                check_tc_status()
         except Exception:
             for e in entries:
                 self.cache.cancel(e.rid)

@@ -320,6 +320,65 @@ def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torc
     return out
 
 
+def grouped_gemm_tc_supported(kd: int, nout: int) -> bool:
+    return bool(library().mi_grouped_gemm_tc_supported(int(kd))) and nout % 2 == 0
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """``x[rows]`` for a bfloat16 matrix (the sorted copy the tensor-core grouped product reads)."""
+    _chk(x, "gather_rows x", BF16)
+    _chk(rows, "gather_rows rows", I32)
+    out = torch.empty(rows.numel(), x.shape[1], dtype=BF16, device=x.device)
+    check(library().mi_gather_rows_bf16(_ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1], _stream()),
+          "gather_rows")
+    return out
+
+
+_tc_status = {}
+_tc_pending = False
+
+
+def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, swiglu_pair: bool) -> torch.Tensor:
+    """The grouped product for many rows per expert (prefill): tcgen05 tensor cores fed by TMA.
+
+    ``a_sorted [N, K]`` holds the rows already in expert order.  Result as for
+    :func:`grouped_gemm_skinny`.  Call :func:`check_tc_status` after the step: a wait inside the
+    kernel that ran out is reported there rather than hanging the device.
+    """
+    global _tc_pending
+    _chk(a_sorted, "grouped_gemm_tc a", BF16)
+    n_rows, Kd = a_sorted.shape
+    _chk(w, "grouped_gemm_tc w", BF16, (None, None, Kd))
+    E, wrows, _ = w.shape
+    nout = wrows // 2 if swiglu_pair else wrows
+    _chk(offsets, "grouped_gemm_tc offsets", I32, (E + 1,))
+    dev = a_sorted.device
+    if dev not in _tc_status:
+        _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
+    out = torch.empty(n_rows, nout, dtype=BF16 if swiglu_pair else F32, device=dev)
+    check(library().mi_grouped_gemm_tc(_ptr(a_sorted), _ptr(w), _ptr(offsets), _ptr(out), _ptr(_tc_status[dev]),
+                                       n_rows, E, nout, Kd, 1 if swiglu_pair else 0, _stream()), "grouped_gemm_tc")
+    _tc_pending = True
+    return out
+
+
+def check_tc_status() -> None:
+    """Raise if a bounded wait inside a tensor-core kernel gave up since the last check (synchronises
+    only when such a kernel was launched)."""
+    global _tc_pending
+    if not _tc_pending:
+        return
+    _tc_pending = False
+    for dev, st in _tc_status.items():
+        code = int(st.item())
+        if code:
+            st.zero_()
+            from .library import KernelError
+            raise KernelError(f"tensor-core grouped product on {dev}: a wait ran out (code {code}: "
+                              f"1 = producer waiting for a free stage, 2 = MMA waiting for data, "
+                              f"3 = epilogue waiting for the accumulators); results of that step are invalid")
+
+
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                 top_p: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
                 probs_scratch: Optional[torch.Tensor] = None,

@@ -32,6 +32,8 @@ _SIGNATURES = {
     "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
     "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],
+    "mi_gather_rows_bf16": [P, P, P, I, I, P],
+    "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, P],
 }
 
 
@@ -56,6 +58,8 @@ def library() -> ctypes.CDLL:
     lib.mi_launch_count.argtypes = []
     lib.mi_attn_decode_supported.argtypes = [I]
     lib.mi_attn_decode_supported.restype = c_int
+    lib.mi_grouped_gemm_tc_supported.argtypes = [I]
+    lib.mi_grouped_gemm_tc_supported.restype = c_int
     lib.mi_grouped_gemm_skinny_supported.argtypes = [I]
     lib.mi_grouped_gemm_skinny_supported.restype = c_int
     lib.mi_attn_decode_split_size.argtypes = []

@@ -114,6 +114,8 @@ class SparseMoE(FeedForward):
             self.w_shared_down = m(tensors[q + "down_proj.weight"], dev)
             g = rt.precision.small(tensors[p + "shared_expert_gate.weight"], dev).reshape(-1)
             self.w_shared_gate = g.to(self.w_router.dtype).contiguous()
+        self._tc = (rt.act == torch.bfloat16 and F.grouped_gemm_tc_supported(self.H, self.mI)
+                    and F.grouped_gemm_tc_supported(self.mI, self.H) and self.H % 8 == 0)
         self._skinny = (rt.act == torch.bfloat16 and F.grouped_gemm_skinny_supported(self.H)
                         and F.grouped_gemm_skinny_supported(self.mI))
 
@@ -129,6 +131,11 @@ class SparseMoE(FeedForward):
             # a few rows per expert: bound by reading each used expert once
             act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
             y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
+        elif self._tc:
+            # many rows per expert: tensor-core tiles over the rows gathered into expert order
+            xs = F.gather_rows(x, sorted_token)
+            act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True)
+            y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
         else:
             act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
             y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)

@@ -382,6 +382,33 @@ def test_grouped_gemm_skinny_equals_plain(T, E, K, H, I):
         F().grouped_gemm_skinny(x[:, :48].contiguous(), sorted_token, wgu[:, :, :48].contiguous(), offsets, T * K, True)
 
 
+@pytest.mark.parametrize("T,E,K,H,I", [(300, 6, 3, 128, 64), (2048, 60, 4, 256, 192), (1000, 12, 2, 192, 320),
+                                       (129, 4, 1, 64, 128), (512, 8, 8, 2048, 1408)])
+def test_grouped_gemm_tensor_core_equals_plain(T, E, K, H, I):
+    """The tcgen05 grouped product against the plain kernel: experts with 0, 1, 127, 128, 129 and many
+    rows; feature counts that are and are not multiples of the 128-column tile."""
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    if E > 2 and K < E:
+        idx[idx == 1] = 0 if K == 1 else idx[idx == 1]          # K == 1: expert 1 gets no rows at all
+    idx = idx.to(DEV)
+    offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
+    x = rnd(T, H, dtype=torch.bfloat16, seed=1)
+    wgu = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.1, seed=2)
+    wd = rnd(E, H, I, dtype=torch.bfloat16, scale=0.1, seed=3)
+    assert F().grouped_gemm_tc_supported(H, I) and F().grouped_gemm_tc_supported(I, H)
+    xs = F().gather_rows(x, sorted_token)
+    assert torch.equal(xs, x[sorted_token.long()])
+    act = F().grouped_gemm_tc(xs, wgu, offsets, True)
+    F().check_tc_status()
+    ref = F().grouped_gemm_plain(x, sorted_token, wgu, offsets, T * K, True, torch.float32)
+    close(act, ref, 6e-3, "gate/up product")
+    y = F().grouped_gemm_tc(act, wd, offsets, False)
+    F().check_tc_status()
+    ref_y = F().grouped_gemm_plain(act, None, wd, offsets, T * K, False, torch.float32)
+    close(y, ref_y, 2e-5, "down product")
+
+
 # --------------------------------------------------------------------------- #
 # sampling
 # --------------------------------------------------------------------------- #

@@ -97,17 +97,23 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const float* __re
 //   q -> q_out[t, head, :]; k, v -> cache slot slot_mapping[t]
 // cache layout per layer: [page, kv_head, page_size, d]
 // ---------------------------------------------------------------------------
+constexpr int QKV_HEADS_PER_BLOCK = 4;
+
 template <typename AT, typename WT>
-__global__ void qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
-                                const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                const int* __restrict__ slot_mapping, AT* __restrict__ q_out,
-                                AT* __restrict__ k_cache, AT* __restrict__ v_cache,
-                                int nh, int nkv, int d, int rot_dim, int page_size) {
+__global__ void __launch_bounds__(128)
+qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
+                const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                const int* __restrict__ slot_mapping, AT* __restrict__ q_out,
+                AT* __restrict__ k_cache, AT* __restrict__ v_cache,
+                int nh, int nkv, int d, int rot_dim, int page_size) {
     const int t = blockIdx.x;
-    const int width = (nh + 2 * nkv) * d;
-    const float* row = qkv + (int64_t)t * width;
+    const int total_heads = nh + 2 * nkv;
+    const int h_lo = blockIdx.y * QKV_HEADS_PER_BLOCK;
+    const int h_hi = min(total_heads, h_lo + QKV_HEADS_PER_BLOCK);
+    const float* row = qkv + (int64_t)t * total_heads * d;
     const float pos = (float)positions[t];
     const int half = rot_dim >> 1;
+    const int rest = d - rot_dim;
     int64_t kbase = -1;
     if (nkv > 0) {
         const int slot = slot_mapping[t];
@@ -116,50 +122,39 @@ __global__ void qkv_post_kernel(const float* __restrict__ qkv, const WT* __restr
             kbase = (int64_t)page * nkv * page_size * d + (int64_t)off * d;
         }
     }
-    // rotary pairs of q and k heads
-    const int n_rot_heads = nh + nkv;
-    for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
-        const int head = idx / half, i = idx - head * half;
-        const int c0 = head * d + i, c1 = c0 + half;
-        float x0 = row[c0], x1 = row[c1];
-        if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
-        float y0 = x0, y1 = x1;
-        if (inv_freq) {
-            const float ang = pos * inv_freq[i];
-            const float c = cosf(ang), s = sinf(ang);
-            y0 = x0 * c - x1 * s;
-            y1 = x1 * c + x0 * s;
-        }
-        if (head < nh) {
-            AT* q = q_out + ((int64_t)t * nh + head) * d;
-            q[i] = from_float<AT>(y0);
-            q[i + half] = from_float<AT>(y1);
+    for (int head = h_lo; head < h_hi; ++head) {
+        if (head < nh + nkv) {
+            // a q or k head: rotary pairs (i, i + half), then the dims beyond rot_dim unchanged
+            AT* dst = nullptr;
+            if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
+            else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
+            if (!dst) continue;
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {
+                const int c0 = head * d + i, c1 = c0 + half;
+                float x0 = row[c0], x1 = row[c1];
+                if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
+                float y0 = x0, y1 = x1;
+                if (inv_freq) {
+                    const float ang = pos * inv_freq[i];
+                    const float c = cosf(ang), s = sinf(ang);
+                    y0 = x0 * c - x1 * s;
+                    y1 = x1 * c + x0 * s;
+                }
+                dst[i] = from_float<AT>(y0);
+                dst[i + half] = from_float<AT>(y1);
+            }
+            for (int i = rot_dim + threadIdx.x; i < rot_dim + rest; i += blockDim.x) {
+                float x = row[head * d + i];
+                if (bias) x += to_float(bias[head * d + i]);
+                dst[i] = from_float<AT>(x);
+            }
         } else if (kbase >= 0) {
-            AT* k = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
-            k[i] = from_float<AT>(y0);
-            k[i + half] = from_float<AT>(y1);
-        }
-    }
-    // dims beyond rot_dim of q and k heads pass through
-    const int rest = d - rot_dim;
-    if (rest > 0) {
-        for (int idx = threadIdx.x; idx < n_rot_heads * rest; idx += blockDim.x) {
-            const int head = idx / rest, i = rot_dim + (idx - head * rest);
-            const int c = head * d + i;
-            float x = row[c];
-            if (bias) x += to_float(bias[c]);
-            if (head < nh) q_out[((int64_t)t * nh + head) * d + i] = from_float<AT>(x);
-            else if (kbase >= 0) k_cache[kbase + (int64_t)(head - nh) * page_size * d + i] = from_float<AT>(x);
-        }
-    }
-    // v heads
-    if (kbase >= 0) {
-        for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
-            const int head = idx / d, i = idx - head * d;
-            const int c = (nh + nkv) * d + idx;
-            float x = row[c];
-            if (bias) x += to_float(bias[c]);
-            v_cache[kbase + (int64_t)head * page_size * d + i] = from_float<AT>(x);
+            AT* dst = v_cache + kbase + (int64_t)(head - nh - nkv) * page_size * d;
+            for (int i = threadIdx.x; i < d; i += blockDim.x) {
+                float x = row[head * d + i];
+                if (bias) x += to_float(bias[head * d + i]);
+                dst[i] = from_float<AT>(x);
+            }
         }
     }
 }
@@ -183,18 +178,32 @@ __global__ void swiglu_kernel(const AT* __restrict__ gu, AT* __restrict__ out, i
 // out[t, :] = sum_k w[t, k] * y[inv_perm[t*K + k], :]   (k ascending: slot order)
 //           + gate[t] * shared[t, :]                     (if shared)
 // ---------------------------------------------------------------------------
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv_perm,
-                                   const float* __restrict__ w, const float* __restrict__ shared,
-                                   const float* __restrict__ gate, float* __restrict__ out, int H, int K) {
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv_perm,
+                   const float* __restrict__ w, const float* __restrict__ shared,
+                   const float* __restrict__ gate, float* __restrict__ out, int H, int K) {
     const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float acc = 0.f;
-        for (int k = 0; k < K; ++k) {
-            const int r = inv_perm[t * K + k];
-            acc += w[t * K + k] * y[(int64_t)r * H + i];
+    const int i0 = blockIdx.y * 512 + threadIdx.x;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < K; ++k) {
+        const int r = inv_perm[t * K + k];
+        const float wk = w[t * K + k];
+        const float* yr = y + (int64_t)r * H;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = i0 + 128 * j;
+            if (i < H) acc[j] += wk * yr[i];
         }
-        if (shared) acc += gate[t] * shared[(int64_t)t * H + i];
-        out[(int64_t)t * H + i] = acc;
+    }
+    const float gt = shared ? gate[t] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = i0 + 128 * j;
+        if (i < H) {
+            float v = acc[j];
+            if (shared) v += gt * shared[(int64_t)t * H + i];
+            out[(int64_t)t * H + i] = v;
+        }
     }
 }
 
@@ -240,8 +249,9 @@ int mi_qkv_post(const float* qkv, const void* bias, int wdtype, const int* posit
         set_last_error("qkv_post: head_dim %d must be even", d);
         return kBadShape;
     }
+    const dim3 grid(T, (nh + 2 * nkv + QKV_HEADS_PER_BLOCK - 1) / QKV_HEADS_PER_BLOCK);
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
-        qkv_post_kernel<AT, WT><<<T, 256, 0, stream>>>(
+        qkv_post_kernel<AT, WT><<<grid, 128, 0, stream>>>(
             qkv, (const WT*)bias, positions, inv_freq, slot_mapping, (AT*)q_out, (AT*)k_cache,
             (AT*)v_cache, nh, nkv, d, rot_dim, page_size));
     return finish_launch("qkv_post");
@@ -260,7 +270,7 @@ int mi_swiglu(const void* gu, void* out, int adtype, int64_t T, int I, cudaStrea
 int mi_moe_combine(const float* y, const int* inv_perm, const float* w, const float* shared,
                    const float* gate, float* out, int T, int H, int K, cudaStream_t stream) {
     if (T <= 0) return kOk;
-    moe_combine_kernel<<<T, 256, 0, stream>>>(y, inv_perm, w, shared, gate, out, H, K);
+    moe_combine_kernel<<<dim3(T, (H + 511) / 512), 128, 0, stream>>>(y, inv_perm, w, shared, gate, out, H, K);
     return finish_launch("moe_combine");
 }
 

@@ -187,6 +187,36 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     return out
 
 
+def prefill_attention_supported(d: int) -> bool:
+    return bool(library().mi_attn_prefill_supported(int(d)))
+
+
+def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                      q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int, window: int = 0,
+                      scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Same contract as :func:`attention`, on tensor cores: bfloat16, head sizes 64 and 128."""
+    _chk(q, "prefill_attention q", BF16)
+    T, nh, d = q.shape
+    _chk(k_cache, "prefill_attention k_cache", BF16)
+    _, nkv, page_size, d2 = k_cache.shape
+    _chk(v_cache, "prefill_attention v_cache", BF16, tuple(k_cache.shape))
+    if d2 != d:
+        raise ValueError(f"prefill_attention: head_dim of q ({d}) and of the cache ({d2}) differ")
+    _chk(block_table, "prefill_attention block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "prefill_attention q_start", I32, (B + 1,))
+    _chk(kv_len, "prefill_attention kv_len", I32, (B,))
+    if out is None:
+        out = torch.empty_like(q)
+    _chk(out, "prefill_attention out", BF16, (T, nh, d))
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    check(library().mi_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(q_start),
+                                    _ptr(kv_len), _ptr(out), B, int(max_q_len), nh, nkv, d, page_size, max_pages,
+                                    int(window), float(scale), _stream()), "prefill_attention")
+    return out
+
+
 def decode_attention_supported(d: int) -> bool:
     return bool(library().mi_attn_decode_supported(int(d)))
 

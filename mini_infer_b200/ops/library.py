@@ -33,6 +33,7 @@ _SIGNATURES = {
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
     "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],
     "mi_gather_rows_bf16": [P, P, P, I, I, P],
+    "mi_attn_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, P],
 }
 
@@ -58,6 +59,8 @@ def library() -> ctypes.CDLL:
     lib.mi_launch_count.argtypes = []
     lib.mi_attn_decode_supported.argtypes = [I]
     lib.mi_attn_decode_supported.restype = c_int
+    lib.mi_attn_prefill_supported.argtypes = [I]
+    lib.mi_attn_prefill_supported.restype = c_int
     lib.mi_grouped_gemm_tc_supported.argtypes = [I]
     lib.mi_grouped_gemm_tc_supported.restype = c_int
     lib.mi_grouped_gemm_skinny_supported.argtypes = [I]

@@ -77,6 +77,7 @@ class GQAttention(Mixer):
         self.w_o = prec.matrix(tensors[f"{self.prefix}o_proj.weight"], dev)
         self.inv_freq = self.position.table(dev)
         self.rot_dim = self.position.rot_dim if self.inv_freq is not None else self.d
+        self._tensor_core_prefill = rt.act == torch.bfloat16 and F.prefill_attention_supported(self.d)
 
     # -- cache ------------------------------------------------------------- #
     def cache_need(self):
@@ -103,6 +104,8 @@ class GQAttention(Mixer):
             splits = -(-ctx.max_kv_len // F.decode_split_size())
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
                                    ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window)
+        elif self._tensor_core_prefill:
+            a = F.prefill_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
         else:
             a = F.attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
         return linear(a.view(ctx.num_tokens, self.nh * self.d), self.w_o, torch.float32)

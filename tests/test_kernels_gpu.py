@@ -255,6 +255,41 @@ def test_decode_attention(adt, nh, nkv, d, window):
     close(out, tiled, 3e-6 if adt == torch.float32 else 1e-2, "decode vs tiled")
 
 
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 64), (2, 2, 128), (6, 1, 128)])
+@pytest.mark.parametrize("ps,window", [(16, 0), (4, 0), (16, 70), (64, 130)])
+def test_prefill_attention_tensor_cores(nh, nkv, d, ps, window):
+    """The mma prefill kernel against the plain attention: portions with and without history, single
+    tokens in the same batch, lengths around the 64-query and 64-key tiles."""
+    kv = [1, 64, 65, 200, 333, 130, 17]
+    ql = [1, 64, 2, 200, 63, 1, 17]
+    case = paged_case(kv, ql, nh, nkv, d, ps, torch.bfloat16, seed=d + ps)
+    out = F().prefill_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],
+                                max(ql), window=window)
+    ref = plain_attention(case, window)
+    close(out, ref, 1e-2, "prefill attention")
+    tiled = F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], max(ql),
+                          window=window)
+    close(out, tiled, 1e-2, "prefill vs tiled")
+
+
+def test_prefill_attention_far_key():
+    n, d, ps = 700, 128, 16
+    for far, window, visible in ((5, 0, True), (440, 250, True), (439, 250, False)):
+        case = paged_case([n], [60], 2, 1, d, ps, torch.bfloat16, seed=far)
+        q, k, v = case["seqs"][0]
+        k[far] = q[n - 11, 0] * 4.0                             # aligned with the query at position n - 11
+        v[far] = 50.0
+        page, off = int(case["table"][0, far // ps]), far % ps
+        case["kc"][page, :, off] = k[far].to(DEV)
+        case["vc"][page, :, off] = v[far].to(DEV)
+        out = F().prefill_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],
+                                    60, window=window)
+        close(out, plain_attention(case, window), 1e-2, f"far key {far} window {window}")
+        row = 60 - 11                                            # the query at position n - 11
+        want_visible = visible and (window == 0 or far > (n - 11) - window)
+        assert (float(out[row, 0].float().mean()) > 40.0) == want_visible
+
+
 def test_attention_refuses_bad_shapes():
     from mini_infer_b200.ops.library import KernelError
     case = paged_case([5], [1], 3, 2, 16, 16, torch.float32)

@@ -197,7 +197,7 @@ def run_ours(args):
         if sampler_clock:
             sampler_clock.start()
         torch.cuda.synchronize()
-        launches0 = launch_count()
+        launches0 = launch_count() + runner.graph_kernel_launches
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.perf_counter()
         a.record()
@@ -208,7 +208,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         wall = time.perf_counter() - w0
         dev_ms = a.elapsed_time(b)
-        launches = launch_count() - launches0
+        launches = launch_count() + runner.graph_kernel_launches - launches0   # eager + replayed in graphs
         clock = sampler_clock.stop() if sampler_clock else None
         kv_tokens = sum(r.num_computed for r in sched.running)
         for r in list(sched.running):

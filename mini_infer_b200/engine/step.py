@@ -88,9 +88,10 @@ class ModelRunner:
         # keep host-side state per step, or were not written with replay in mind, switch this off.
         self.cuda_graphs = bool(cuda_graphs) and not model.state_needs and \
             all(getattr(p, "graph_safe", False) for p in model.all_parts())
-        self._graphs: Dict[int, Tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._graphs: Dict[int, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_pool = None
         self.graph_replays = 0
+        self.graph_kernel_launches = 0      # kernels of this library launched through graph replays
 
     # ------------------------------------------------------------------ #
     # staging: one pinned buffer, one copy per step
@@ -273,13 +274,16 @@ class ModelRunner:
             torch.cuda.synchronize(self.rt.device)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
+            from ..ops.library import launch_count
+            before = launch_count()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=self._graph_pool):
                 out = self.model.forward(ctx, logit_rows)
-            self._graphs[B] = (g, out)
-        g, out = self._graphs[B]
+            self._graphs[B] = (g, out, launch_count() - before)
+        g, out, kernels = self._graphs[B]
         g.replay()
         self.graph_replays += 1
+        self.graph_kernel_launches += kernels
         return out
 
     @torch.no_grad()

@@ -460,3 +460,70 @@ int mi_attn_decode(const void* q, const void* k_cache, const void* v_cache, int 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate (see attention_noalloc.h): the
+// split partials live in an array that is part of the library image instead of caller scratch.
+// ---------------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+namespace mi {
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MI_ATTN_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+// Device address of g_noalloc_scratch per device.  In host code the array's name is only a
+// handle for cudaGetSymbolAddress, never a pointer a kernel could use.
+static float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Looks the address up once per device, with that device current.  Returns nullptr on failure.
+static float* noalloc_scratch_for_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_last_error("decode attention (no allocation): cannot identify the current device");
+        return nullptr;
+    }
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            set_last_error("decode attention (no allocation): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    return g_noalloc_ptr[dev];
+}
+
+}  // namespace mi
+
+extern "C" {
+
+unsigned int mi_attn_decode_noalloc_capacity(void) { return MI_ATTN_NOALLOC_SCRATCH_BYTES; }
+
+int mi_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, int adtype,
+                           const int* block_table, const int* q_start, const int* kv_len, void* out, int B,
+                           int nh, int nkv, int d, int page_size, int max_pages, int max_splits, int window,
+                           float scale, cudaStream_t stream) {
+    if (B <= 0) return kOk;
+    if (max_splits < 1 || nh < 1 || d < 1) {
+        set_last_error("decode attention (no allocation): bad sizes (nh=%d, d=%d, max_splits=%d)", nh, d, max_splits);
+        return kBadShape;
+    }
+    const unsigned long long n_part = (unsigned long long)B * nh * max_splits;
+    const unsigned long long need = n_part * ((unsigned long long)d + 2ull) * sizeof(float);
+    if (need > MI_ATTN_NOALLOC_SCRATCH_BYTES) {
+        set_last_error("decode attention (no allocation): B=%d, heads=%d, splits=%d, head_dim=%d need %llu bytes of "
+                       "scratch, the built-in array holds %u", B, nh, max_splits, d, need,
+                       (unsigned)MI_ATTN_NOALLOC_SCRATCH_BYTES);
+        return kBadShape;
+    }
+    float* scratch = noalloc_scratch_for_current_device();
+    if (!scratch) return kLaunchFailed;
+    float* part_o = scratch;                       // [B, nh, max_splits, d]
+    float* part_ml = scratch + n_part * d;         // [B, nh, max_splits, 2]
+    return mi_attn_decode(q, k_cache, v_cache, adtype, block_table, q_start, kv_len, out, part_o, part_ml, B, nh,
+                          nkv, d, page_size, max_pages, max_splits, window, scale, stream);
+}
+
+}  // extern "C"

@@ -90,6 +90,55 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const float* __re
     }
 }
 
+// The same for rows of H = 4 * VPT * 256 floats at most: a thread keeps its float4s in registers
+// between the two passes.  Threads take interleaved float4s, so the order of the additions of a
+// row's sum of squares differs from the scalar kernel's but depends on H only.
+template <typename AT, typename WT, int VPT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
+                       const int* __restrict__ rows, const WT* __restrict__ weight,
+                       AT* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float4* h = reinterpret_cast<float4*>(hidden + (int64_t)src * H);
+    const float4* d = delta ? reinterpret_cast<const float4*>(delta + (int64_t)src * H) : nullptr;
+    const int nv = H >> 2;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nv) {
+            v[j] = h[i];
+            if (d) {
+                const float4 dv = d[i];
+                v[j].x += dv.x; v[j].y += dv.y; v[j].z += dv.z; v[j].w += dv.w;
+                if (!rows) h[i] = v[j];
+            }
+            ss += v[j].x * v[j].x;
+            ss += v[j].y * v[j].y;
+            ss += v[j].z * v[j].z;
+            ss += v[j].w * v[j].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rrms = rsqrtf(ss / (float)H + eps);
+    AT* o = out + (int64_t)r * H;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < nv) {
+            const int c = 4 * i;
+            o[c] = from_float<AT>(v[j].x * rrms * to_float(weight[c]));
+            o[c + 1] = from_float<AT>(v[j].y * rrms * to_float(weight[c + 1]));
+            o[c + 2] = from_float<AT>(v[j].z * rrms * to_float(weight[c + 2]));
+            o[c + 3] = from_float<AT>(v[j].w * rrms * to_float(weight[c + 3]));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // q/k/v post-processing for one token per block:
 //   add bias; rotate the first rot_dim dims of every q and k head by
@@ -97,7 +146,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const float* __re
 //   q -> q_out[t, head, :]; k, v -> cache slot slot_mapping[t]
 // cache layout per layer: [page, kv_head, page_size, d]
 // ---------------------------------------------------------------------------
-constexpr int QKV_HEADS_PER_BLOCK = 4;
+constexpr int QKV_HEADS_PER_BLOCK = 8;
 
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(128)
@@ -122,28 +171,48 @@ qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
             kbase = (int64_t)page * nkv * page_size * d + (int64_t)off * d;
         }
     }
+    // work items: (head of this block, pair index i < half); with half dividing the block size a
+    // thread keeps the same i for all its heads and computes the angle's cosine and sine once
+    const int n_heads = h_hi - h_lo;
+    const bool same_i = half > 0 && (blockDim.x % half) == 0;
+    float c_keep = 1.f, s_keep = 0.f;
+    if (same_i && inv_freq) {
+        const float ang = pos * inv_freq[threadIdx.x % half];
+        c_keep = cosf(ang);
+        s_keep = sinf(ang);
+    }
+    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+        const int head = h_lo + idx / half, i = idx % half;
+        if (head >= nh + nkv) break;                         // v heads follow the q and k heads
+        AT* dst = nullptr;
+        if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
+        else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
+        if (!dst) continue;
+        const int c0 = head * d + i, c1 = c0 + half;
+        float x0 = row[c0], x1 = row[c1];
+        if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
+        float y0 = x0, y1 = x1;
+        if (inv_freq) {
+            float c = c_keep, sn = s_keep;
+            if (!same_i) {
+                const float ang = pos * inv_freq[i];
+                c = cosf(ang);
+                sn = sinf(ang);
+            }
+            y0 = x0 * c - x1 * sn;
+            y1 = x1 * c + x0 * sn;
+        }
+        dst[i] = from_float<AT>(y0);
+        dst[i + half] = from_float<AT>(y1);
+    }
     for (int head = h_lo; head < h_hi; ++head) {
         if (head < nh + nkv) {
-            // a q or k head: rotary pairs (i, i + half), then the dims beyond rot_dim unchanged
+            if (rest <= 0) continue;
             AT* dst = nullptr;
             if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
             else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
             if (!dst) continue;
-            for (int i = threadIdx.x; i < half; i += blockDim.x) {
-                const int c0 = head * d + i, c1 = c0 + half;
-                float x0 = row[c0], x1 = row[c1];
-                if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
-                float y0 = x0, y1 = x1;
-                if (inv_freq) {
-                    const float ang = pos * inv_freq[i];
-                    const float c = cosf(ang), s = sinf(ang);
-                    y0 = x0 * c - x1 * s;
-                    y1 = x1 * c + x0 * s;
-                }
-                dst[i] = from_float<AT>(y0);
-                dst[i + half] = from_float<AT>(y1);
-            }
-            for (int i = rot_dim + threadIdx.x; i < rot_dim + rest; i += blockDim.x) {
+            for (int i = rot_dim + threadIdx.x; i < d; i += blockDim.x) {
                 float x = row[head * d + i];
                 if (bias) x += to_float(bias[head * d + i]);
                 dst[i] = from_float<AT>(x);
@@ -171,6 +240,28 @@ __global__ void swiglu_kernel(const AT* __restrict__ gu, AT* __restrict__ out, i
         const float g = to_float(gu[t * 2 * I + i]);
         const float u = to_float(gu[t * 2 * I + I + i]);
         out[idx] = from_float<AT>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// bfloat16 rows with I a multiple of 8: 16 bytes per load and store
+__global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, int64_t total_vec,
+                                     int Iv) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / Iv;
+        const int i = (int)(idx - t * Iv);
+        const uint4 gv = __ldg(gu + t * 2 * Iv + i);
+        const uint4 uv = __ldg(gu + t * 2 * Iv + Iv + i);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 r;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            r2[j] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        }
+        out[idx] = r;
     }
 }
 
@@ -230,6 +321,23 @@ int mi_add_rmsnorm(float* hidden, const float* delta, const int* rows, const voi
                    void* out, int adtype, int n_rows, int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return kOk;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0;
+    if (H % 4 == 0 && H >= 1024 && H <= 8192 && aligned) {
+        if (H <= 2048) {
+            MI_DISPATCH_2(adtype, AT, wdtype, WT,
+                add_rmsnorm_vec_kernel<AT, WT, 2><<<n_rows, 256, 0, stream>>>(
+                    hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+        } else if (H <= 4096) {
+            MI_DISPATCH_2(adtype, AT, wdtype, WT,
+                add_rmsnorm_vec_kernel<AT, WT, 4><<<n_rows, 256, 0, stream>>>(
+                    hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+        } else {
+            MI_DISPATCH_2(adtype, AT, wdtype, WT,
+                add_rmsnorm_vec_kernel<AT, WT, 8><<<n_rows, 256, 0, stream>>>(
+                    hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+        }
+        return finish_launch("add_rmsnorm");
+    }
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         add_rmsnorm_kernel<AT, WT><<<n_rows, threads, 0, stream>>>(
             hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
@@ -260,6 +368,14 @@ int mi_qkv_post(const float* qkv, const void* bias, int wdtype, const int* posit
 int mi_swiglu(const void* gu, void* out, int adtype, int64_t T, int I, cudaStream_t stream) {
     const int64_t total = T * I;
     if (total <= 0) return kOk;
+    if (adtype == kBF16 && I % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int64_t total_vec = total / 8;
+        int64_t vblocks = (total_vec + 255) / 256;
+        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        swiglu_bf16x8_kernel<<<(int)vblocks, 256, 0, stream>>>((const uint4*)gu, (uint4*)out, total_vec, I / 8);
+        return finish_launch("swiglu");
+    }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     MI_DISPATCH_1(adtype, AT,

@@ -14,83 +14,104 @@
 namespace mi {
 
 // ---------------------------------------------------------------------------
-// Router: one block per token.
-//   z_e = x . Wr[e]              (float, one warp per expert: lane-strided, then butterfly sum)
-//   p = softmax(z) over all experts
-//   K rounds of arg-max over p, lowest index wins ties (moe_kernel.cu:28-47)
-//   w_k = p[idx_k]  (divided by their sum when norm_topk)
-//   gate = sigmoid(x . Wsg)      (moe_kernel.cu:137-139)
+// Router, in two kernels.
+//   logits:  z[t, e] = x[t] . Wr[e]   (and the shared-expert gate row as column E)
+//            block = 8 tokens x 8 weight rows (one warp per row): a weight row is read once for
+//            the block's tokens, the tokens' rows sit in shared memory as float.  Each lane
+//            takes interleaved 16-byte chunks of the row, then a butterfly sum: the order of a
+//            dot product's additions depends on H only.
+//   select:  one warp per token: p = softmax(z) over all experts; K rounds of arg-max over p,
+//            lowest index wins ties (moe_kernel.cu:28-47); w_k = p[idx_k] (divided by their sum
+//            when norm_topk); gate = sigmoid(z[E]) (moe_kernel.cu:137-139)
 // ---------------------------------------------------------------------------
-// Dot product of a float row in shared memory with a weight row in global memory; the lanes of a
-// warp take interleaved chunks of 8 (one 16-byte load of bfloat16) and a scalar tail.
-template <typename WT>
-__device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const WT* __restrict__ w, int H, int lane);
+constexpr int RT_TOK = 8;    // tokens per block
+constexpr int RT_ROWS = 8;   // weight rows per block (warps)
 
-template <>
-__device__ __forceinline__ float warp_dot<__nv_bfloat16>(const float* __restrict__ xs, const __nv_bfloat16* __restrict__ w,
-                                                         int H, int lane) {
-    float acc = 0.f;
-    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-    const int main = aligned ? (H & ~7) : 0;
-    for (int i = lane * 8; i < main; i += 256) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(w + i));
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+template <typename WT> struct RowChunk;
+template <> struct RowChunk<__nv_bfloat16> {
+    static constexpr int N = 8;
+    float v[8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        const uint4 x = __ldg(reinterpret_cast<const uint4*>(p));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h[j]);
-            acc += xs[i + 2 * j] * f.x;
-            acc += xs[i + 2 * j + 1] * f.y;
-        }
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
     }
-    for (int i = main + lane; i < H; i += 32) acc += xs[i] * __bfloat162float(w[i]);
-    return warp_sum(acc);
-}
-
-template <>
-__device__ __forceinline__ float warp_dot<float>(const float* __restrict__ xs, const float* __restrict__ w, int H, int lane) {
-    float acc = 0.f;
-    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-    const int main = aligned ? (H & ~3) : 0;
-    for (int i = lane * 4; i < main; i += 128) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(w + i));
-        acc += xs[i] * v.x;
-        acc += xs[i + 1] * v.y;
-        acc += xs[i + 2] * v.z;
-        acc += xs[i + 3] * v.w;
+};
+template <> struct RowChunk<float> {
+    static constexpr int N = 4;
+    float v[4];
+    __device__ __forceinline__ void load(const float* p) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(p));
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
     }
-    for (int i = main + lane; i < H; i += 32) acc += xs[i] * w[i];
-    return warp_sum(acc);
-}
+};
 
-// One block (8 warps) per token: the token's row goes to shared memory as float, the warps share
-// out the experts' dot products, warp 0 does softmax, top-k and the weights.  The order of the
-// additions of a dot product depends on H only.
 template <typename AT, typename WT>
-__global__ void __launch_bounds__(256)
-moe_router_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
-                  int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ gate,
-                  float* __restrict__ probs_out, int T, int H, int E, int K, int norm_topk) {
-    extern __shared__ float smem[];  // [H] token row, [E] logits / probabilities
-    float* xs = smem;
-    float* p = smem + H;
+__global__ void __launch_bounds__(32 * RT_ROWS)
+moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                         float* __restrict__ z, int T, int H, int E) {
+    extern __shared__ __align__(16) float xs[];   // [RT_TOK][H]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x;
-    const AT* xr = x + (int64_t)t * H;
-    for (int i = threadIdx.x; i < H; i += 256) xs[i] = to_float(xr[i]);
-    __syncthreads();
-    for (int e = warp; e < E + (wsg ? 1 : 0); e += 8) {
-        if (e < E) {
-            const float z = warp_dot<WT>(xs, wr + (int64_t)e * H, H, lane);
-            if (lane == 0) p[e] = z;
-        } else {
-            const float z = warp_dot<WT>(xs, wsg, H, lane);
-            if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-z));
-        }
+    const int t0 = blockIdx.x * RT_TOK;
+    const int nt = min(RT_TOK, T - t0);
+    for (int idx = threadIdx.x; idx < RT_TOK * H; idx += 32 * RT_ROWS) {
+        const int j = idx / H, i = idx - j * H;
+        xs[idx] = j < nt ? to_float(x[(int64_t)(t0 + j) * H + i]) : 0.f;
     }
     __syncthreads();
-    if (warp != 0) return;
+    const int ncols = E + (wsg ? 1 : 0);
+    const int e = blockIdx.y * RT_ROWS + warp;
+    if (e >= ncols) return;
+    const WT* w = e < E ? wr + (int64_t)e * H : wsg;
+    constexpr int CN = RowChunk<WT>::N;
+    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    const int main = (aligned && H % 4 == 0) ? (H / CN) * CN : 0;   // rows of xs stay 16-byte aligned
+    float acc[RT_TOK];
+#pragma unroll
+    for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
+    for (int i = lane * CN; i < main; i += 32 * CN) {
+        RowChunk<WT> c;
+        c.load(w + i);
+#pragma unroll
+        for (int j = 0; j < RT_TOK; ++j) {
+            const float4* xr = reinterpret_cast<const float4*>(xs + j * H + i);   // H % CN == 0 here
+#pragma unroll
+            for (int u = 0; u < CN / 4; ++u) {
+                const float4 xv = xr[u];
+                acc[j] += xv.x * c.v[4 * u];
+                acc[j] += xv.y * c.v[4 * u + 1];
+                acc[j] += xv.z * c.v[4 * u + 2];
+                acc[j] += xv.w * c.v[4 * u + 3];
+            }
+        }
+    }
+    for (int i = main + lane; i < H; i += 32) {
+        const float wv = to_float(w[i]);
+#pragma unroll
+        for (int j = 0; j < RT_TOK; ++j) acc[j] += xs[j * H + i] * wv;
+    }
+#pragma unroll
+    for (int j = 0; j < RT_TOK; ++j) {
+        const float v = warp_sum(acc[j]);
+        if (lane == 0 && j < nt) z[(int64_t)(t0 + j) * ncols + e] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restrict__ topk_idx,
+                         float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
+                         int T, int E, int K, int norm_topk) {
+    extern __shared__ float smem[];  // [8][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    float* p = smem + warp * E;
+    const int ncols = E + (has_gate ? 1 : 0);
+    const float* zr = z + (int64_t)t * ncols;
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
+    for (int e = lane; e < E; e += 32) { const float v = zr[e]; p[e] = v; mx = fmaxf(mx, v); }
+    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zr[E]));
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
@@ -138,13 +159,15 @@ moe_router_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT*
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, int* __restrict__ sorted_token,
-                   int* __restrict__ inv_perm, int N, int E, int K) {
-    extern __shared__ int sh[];  // [E+1]
+                   int* __restrict__ inv_perm, int N, int E, int K, int idx_in_smem) {
+    extern __shared__ int sh[];  // [E+1] starts, then (if it fits) a copy of topk_idx
+    int* sidx = sh + E + 1;
     const int tid = threadIdx.x;
     for (int e = tid; e <= E; e += blockDim.x) sh[e] = 0;
     __syncthreads();
     for (int i = tid; i < N; i += blockDim.x) {
         const int e = topk_idx[i];
+        if (idx_in_smem) sidx[i] = e;
         if (e >= 0 && e < E) atomicAdd(&sh[e + 1], 1);
     }
     __syncthreads();
@@ -154,12 +177,14 @@ moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, 
     }
     __syncthreads();
     for (int e = tid; e <= E; e += blockDim.x) offsets[e] = sh[e];
+    const int* src = idx_in_smem ? sidx : topk_idx;
     const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
     for (int e = warp; e < E; e += nwarps) {
         int run = sh[e];
-        for (int base = 0; base < N; base += 32) {
+        const int end = sh[e + 1];
+        for (int base = 0; base < N && run < end; base += 32) {
             const int i = base + lane;
-            const bool mine = (i < N) && (topk_idx[i] == e);
+            const bool mine = (i < N) && (src[i] == e);
             const unsigned bal = __ballot_sync(0xffffffffu, mine);
             if (mine) {
                 const int pos = run + __popc(bal & ((1u << lane) - 1u));
@@ -256,32 +281,38 @@ using namespace mi;
 
 extern "C" {
 
-int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, int* topk_idx,
-                  float* topk_w, float* gate, float* probs_out, int T, int H, int E, int K, int norm_topk,
-                  cudaStream_t stream) {
+// `z_scratch` holds T * (E + 1) floats (router logits and the shared gate's logit).
+int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
+                  int* topk_idx, float* topk_w, float* gate, float* probs_out, int T, int H, int E, int K,
+                  int norm_topk, cudaStream_t stream) {
     if (T <= 0) return kOk;
     if (K < 1 || K > 32 || K > E) {
         set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
         return kBadShape;
     }
-    const size_t smem = sizeof(float) * ((size_t)H + (size_t)E);
-    if (smem > 200 * 1024) {
-        set_last_error("router: hidden size %d plus %d experts exceed the shared memory of a block", H, E);
+    const size_t smem_x = sizeof(float) * RT_TOK * (size_t)H;
+    const size_t smem_p = sizeof(float) * 8 * (size_t)E;
+    if (smem_x > 200 * 1024 || smem_p > 48 * 1024) {
+        set_last_error("router: hidden size %d or %d experts exceed the shared memory of a block", H, E);
         return kBadShape;
     }
-    if (T > 0x7fffffff / 2) {
-        set_last_error("router: too many tokens");
+    const int ncols = E + (wsg ? 1 : 0);
+    const dim3 grid((T + RT_TOK - 1) / RT_TOK, (ncols + RT_ROWS - 1) / RT_ROWS);
+    if (grid.y > 65535) {
+        set_last_error("router: %d experts exceed the grid limit", E);
         return kBadShape;
     }
-#define MI_ROUTER_ATTR(AT, WT)                                                                         \
-    if (smem > 48 * 1024)                                                                              \
-        cudaFuncSetAttribute(moe_router_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+#define MI_ROUTER_ATTR(AT, WT)                                                                              \
+    if (smem_x > 48 * 1024)                                                                                 \
+        cudaFuncSetAttribute(moe_router_logits_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                             (int)smem_x)
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         MI_ROUTER_ATTR(AT, WT);
-        moe_router_kernel<AT, WT><<<T, 256, smem, stream>>>(
-            (const AT*)x, (const WT*)wr, (const WT*)wsg, topk_idx, topk_w, gate, probs_out, T, H, E, K,
-            norm_topk));
-    return finish_launch("moe_router");
+        moe_router_logits_kernel<AT, WT><<<grid, 32 * RT_ROWS, smem_x, stream>>>(
+            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, T, H, E));
+    moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w, gate,
+                                                                    probs_out, T, E, K, norm_topk);
+    return finish_launch("moe_router", 2);
 }
 
 int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int T, int E, int K,
@@ -290,8 +321,14 @@ int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* in
         set_last_error("permute: %d experts exceed the shared-memory table", E);
         return kBadShape;
     }
-    moe_permute_kernel<<<1, 1024, sizeof(int) * (E + 1), stream>>>(topk_idx, offsets, sorted_token, inv_perm,
-                                                                   T * K, E, K);
+    const int64_t N = (int64_t)T * K;
+    size_t smem = sizeof(int) * (E + 1);
+    const int idx_in_smem = (smem + sizeof(int) * N <= 160 * 1024) ? 1 : 0;
+    if (idx_in_smem) smem += sizeof(int) * N;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(moe_permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    moe_permute_kernel<<<1, 1024, smem, stream>>>(topk_idx, offsets, sorted_token, inv_perm, (int)N, E, K,
+                                                  idx_in_smem);
     return finish_launch("moe_permute");
 }
 

@@ -3,12 +3,18 @@
 // accumulators in tensor memory, read back with tcgen05.ld for the epilogue.
 //
 // Rows are the (token, slot) pairs sorted by expert and gathered into a contiguous matrix, so
-// an expert's rows are the contiguous range offsets[e] .. offsets[e+1].  One block computes a
-// tile of 128 rows x 128 features of one expert:
-//   warp 0    TMA producer: A tile (rows x 64 k) and the weight tile(s) per pipeline stage
+// an expert's rows are the contiguous range offsets[e] .. offsets[e+1].  The product is computed
+// transposed: the expert's weights are the M operand (128 features per tile) and the rows are the
+// N operand, whose size follows the expert's row count (a multiple of 16 up to 256).  An expert
+// with 137 rows is one tile with N = 144 instead of two row tiles of 128, and its weights - the
+// bytes that bound this product - are read once.  One block computes one (expert, row tile,
+// feature tile):
+//   warp 0    TMA producer: weight tile(s) (128 features x 64 k) and row tile (rows x 64 k)
 //   warp 1    allocates tensor memory, issues the MMAs, commits stages back to the producer
 //   warps 2-5 epilogue: accumulators -> registers -> SwiGLU / store, one TMEM lane quarter each
-// A tile that crosses the end of its expert's range computes rows of the next expert too; they
+//             (a lane is a feature, a column is a row of the expert: for each row a warp stores 32
+//             consecutive features)
+// A row tile that crosses the end of its expert's range computes rows of the next expert too; they
 // are simply not stored.  The k loop runs in ascending order whatever the number of rows.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error status that the host
@@ -24,11 +30,14 @@
 namespace mi {
 namespace tc {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4;
-constexpr int TILE_BYTES = BM * BK * 2;        // one operand tile of one stage: 16 KiB
+constexpr int BF = 128;                        // features per tile (MMA M)
+constexpr int BK = 64;                         // k per pipeline stage (one 128-byte swizzle row)
+constexpr int MAXN = 256;                      // rows per tile at most (MMA N)
+constexpr int W_TILE_BYTES = BF * BK * 2;      // one weight tile of one stage: 16 KiB
+constexpr int R_TILE_BYTES = MAXN * BK * 2;    // room for the row tile of one stage: 32 KiB
 constexpr uint32_t WAIT_LIMIT = 400000;        // try_wait rounds before a wait gives up
-// instruction descriptor: D float32, A and B bfloat16, both K-major, N = 128, M = 128
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// instruction descriptor without N: D float32, A and B bfloat16, both K-major, M = 128
+constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BF >> 4) << 24);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -71,12 +80,13 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
     const uint32_t zero = 0;
     asm volatile(
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
         " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate), "r"(zero) : "memory");
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -93,15 +103,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
 }
 
+// The four row-tile maps differ in their box height only (32, 64, 128, 256 rows).
+struct RowMaps {
+    CUtensorMap m[4];
+};
+
 // MODE 1: C[r, n] = silu(a_r . W[e, n]) * (a_r . W[e, Nout + n])  (bfloat16); MODE 0: C[r, n] = a_r . W[e, n] (float)
 template <int MODE>
 __global__ void __launch_bounds__(192, 1)
-grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
                        int* __restrict__ status) {
     constexpr int NB = MODE == 1 ? 2 : 1;                 // weight tiles per stage (gate and up, or one)
-    constexpr int STAGE_BYTES = (1 + NB) * TILE_BYTES;
-    constexpr uint32_t TMEM_COLS = NB * BN;               // 256 or 128: a power of two >= 32
+    constexpr int STAGES = MODE == 1 ? 3 : 4;
+    constexpr int STAGE_BYTES = NB * W_TILE_BYTES + R_TILE_BYTES;
+    constexpr uint32_t TMEM_COLS = NB * MAXN;             // 512 or 256: a power of two >= 32
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
     __shared__ uint32_t tmem_base_s;
@@ -112,14 +128,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     bool found = false;
     for (e = 0; e < E; ++e) {
         const int b0 = offsets[e], cnt = offsets[e + 1] - b0;
-        const int tiles = (cnt + BM - 1) / BM;
-        if (slot < tiles) { row0 = b0 + slot * BM; rows = min(BM, cnt - slot * BM); found = true; break; }
+        const int tiles = (cnt + MAXN - 1) / MAXN;
+        if (slot < tiles) { row0 = b0 + slot * MAXN; rows = min(MAXN, cnt - slot * MAXN); found = true; break; }
         slot -= tiles;
     }
     if (!found) return;                                   // uniform for the whole block
-    const int n0 = blockIdx.x * BN;
+    const int n0 = blockIdx.x * BF;
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     const int num_kb = Kd / BK;
+    const int n_mma = (rows + 15) & ~15;                  // MMA N: a multiple of 16 for M = 128
+    const int box = rows <= 32 ? 0 : (rows <= 64 ? 1 : (rows <= 128 ? 2 : 3));
+    const uint32_t row_bytes = (32u << box) * BK * 2;     // bytes the row-tile copy delivers
+    const uint32_t idesc = IDESC_BASE | ((uint32_t)(n_mma >> 3) << 17);
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -149,10 +169,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
                 if (!mbar_wait(&empty_bar[s], parity, abort_flag, 1)) break;
                 uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(st, &map_a, kb * BK, row0, &full_bar[s]);
-                tma_load_2d(st + TILE_BYTES, &map_w, kb * BK, e * wrows + n0, &full_bar[s]);
-                if (MODE == 1) tma_load_2d(st + 2 * TILE_BYTES, &map_w, kb * BK, e * wrows + Nout + n0, &full_bar[s]);
+                mbar_expect_tx(&full_bar[s], NB * W_TILE_BYTES + row_bytes);
+                tma_load_2d(st, &map_w, kb * BK, e * wrows + n0, &full_bar[s]);
+                if (MODE == 1) tma_load_2d(st + W_TILE_BYTES, &map_w, kb * BK, e * wrows + Nout + n0, &full_bar[s]);
+                tma_load_2d(st + NB * W_TILE_BYTES, &maps_a.m[box], kb * BK, row0, &full_bar[s]);
             }
         }
     } else if (warp == 1) {
@@ -164,56 +184,53 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 ok = mbar_wait(&full_bar[s], parity, abort_flag, 2);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t w_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t r_addr = w_addr + NB * W_TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k) {
                     const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    const uint64_t ad = umma_desc(a_addr + k * 32);
-                    umma_bf16(tmem_base, ad, umma_desc(a_addr + TILE_BYTES + k * 32), acc);
-                    if (MODE == 1) umma_bf16(tmem_base + BN, ad, umma_desc(a_addr + 2 * TILE_BYTES + k * 32), acc);
+                    const uint64_t rd = umma_desc(r_addr + k * 32);
+                    umma_bf16(tmem_base, umma_desc(w_addr + k * 32), rd, idesc, acc);
+                    if (MODE == 1) umma_bf16(tmem_base + MAXN, umma_desc(w_addr + W_TILE_BYTES + k * 32), rd, idesc, acc);
                 }
                 umma_commit(&empty_bar[s]);               // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(&accum_bar);              // accumulators complete
         }
     } else {
-        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
+        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; a lane is a feature of the tile
         const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;                // row of the tile held by this thread
+        const int f = n0 + quarter * 32 + lane;
         bool ok = mbar_wait(&accum_bar, 0, abort_flag, 3);
         ok = __all_sync(0xffffffffu, ok);                 // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < rows; c0 += 32) {      // columns beyond n_mma hold nothing; they are not stored
                 uint32_t g[32];
                 tmem_ld32(lane_addr + c0, g);
                 if (MODE == 1) {
                     uint32_t u[32];
-                    tmem_ld32(lane_addr + BN + c0, u);
+                    tmem_ld32(lane_addr + MAXN + c0, u);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (r < rows) {
-                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + r) * Nout + n0 + c0;
+                    if (f < Nout) {
+                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float g0 = __uint_as_float(g[i]), g1 = __uint_as_float(g[i + 1]);
-                            const float v0 = g0 / (1.0f + expf(-g0)) * __uint_as_float(u[i]);
-                            const float v1 = g1 / (1.0f + expf(-g1)) * __uint_as_float(u[i + 1]);
-                            if (n0 + c0 + i + 1 < Nout) {
-                                *reinterpret_cast<__nv_bfloat162*>(out + i) = __floats2bfloat162_rn(v0, v1);
-                            } else if (n0 + c0 + i < Nout) {
-                                out[i] = __float2bfloat16_rn(v0);
+                        for (int i = 0; i < 32; ++i) {
+                            if (c0 + i < rows) {
+                                const float gv = __uint_as_float(g[i]);
+                                out[(int64_t)i * Nout] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * __uint_as_float(u[i]));
                             }
                         }
                     }
                 } else {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (r < rows) {
-                        float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + r) * Nout + n0 + c0;
+                    if (f < Nout) {
+                        float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + c0) * Nout + f;
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (n0 + c0 + i < Nout) out[i] = __uint_as_float(g[i]);
+                            if (c0 + i < rows) out[(int64_t)i * Nout] = __uint_as_float(g[i]);
                     }
                 }
             }
@@ -258,7 +275,7 @@ static bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
     if (!fn) return false;
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {BK, box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -296,12 +313,8 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
         set_last_error("grouped product (tensor cores): inner size %d is not a multiple of %d", Kd, tc::BK);
         return kBadShape;
     }
-    if (mode == 1 && (Nout & 1)) {
-        set_last_error("grouped product (tensor cores): an odd feature count %d is not supported", Nout);
-        return kBadShape;
-    }
     const int wrows = mode == 1 ? 2 * Nout : Nout;
-    const int max_tiles = (n_rows + tc::BM - 1) / tc::BM + E;
+    const int max_tiles = (n_rows + tc::MAXN - 1) / tc::MAXN + E;
     if (max_tiles > 65535) {
         set_last_error("grouped product (tensor cores): %d row tiles exceed the grid limit", max_tiles);
         return kBadShape;
@@ -310,23 +323,25 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
         set_last_error("grouped product (tensor cores): operands must be 16-byte aligned");
         return kBadShape;
     }
-    CUtensorMap map_a, map_w;
-    if (!tc::make_map(&map_a, A, (uint64_t)n_rows, (uint64_t)Kd, tc::BM) ||
-        !tc::make_map(&map_w, W, (uint64_t)E * wrows, (uint64_t)Kd, tc::BN)) {
+    tc::RowMaps maps_a;
+    CUtensorMap map_w;
+    bool ok = tc::make_map(&map_w, W, (uint64_t)E * wrows, (uint64_t)Kd, tc::BF);
+    for (int i = 0; i < 4 && ok; ++i) ok = tc::make_map(&maps_a.m[i], A, (uint64_t)n_rows, (uint64_t)Kd, 32u << i);
+    if (!ok) {
         set_last_error("grouped product (tensor cores): cuTensorMapEncodeTiled failed");
         return kLaunchFailed;
     }
-    const dim3 grid((Nout + tc::BN - 1) / tc::BN, max_tiles);
-    const int nb = mode == 1 ? 2 : 1;
-    const size_t smem = (size_t)tc::STAGES * (1 + nb) * tc::TILE_BYTES + 1024;
+    const dim3 grid((Nout + tc::BF - 1) / tc::BF, max_tiles);
     if (mode == 1) {
+        const size_t smem = 3 * (size_t)(2 * tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
         auto kern = tc::grouped_gemm_tc_kernel<1>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<grid, 192, smem, stream>>>(map_a, map_w, offsets, C, E, Nout, Kd, status);
+        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);
     } else {
+        const size_t smem = 4 * (size_t)(tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
         auto kern = tc::grouped_gemm_tc_kernel<0>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<grid, 192, smem, stream>>>(map_a, map_w, offsets, C, E, Nout, Kd, status);
+        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);
     }
     return finish_launch("grouped_gemm_tc");
 }

@@ -280,8 +280,9 @@ def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[
     w = torch.empty(T, top_k, dtype=F32, device=dev)
     gate = torch.empty(T, dtype=F32, device=dev) if shared_gate_w is not None else None
     probs = torch.empty(T, E, dtype=F32, device=dev) if want_probs else None
+    z = torch.empty(T, E + 1, dtype=F32, device=dev)
     check(library().mi_moe_router(_ptr(x), _code(x, "moe_router x"), _ptr(router_w), _ptr(shared_gate_w),
-                                  _code(router_w, "moe_router weight"), _ptr(idx), _ptr(w), _ptr(gate),
+                                  _code(router_w, "moe_router weight"), _ptr(z), _ptr(idx), _ptr(w), _ptr(gate),
                                   _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _stream()),
           "moe_router")
     return idx, w, gate, probs
@@ -351,7 +352,7 @@ def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torc
 
 
 def grouped_gemm_tc_supported(kd: int, nout: int) -> bool:
-    return bool(library().mi_grouped_gemm_tc_supported(int(kd))) and nout % 2 == 0
+    return bool(library().mi_grouped_gemm_tc_supported(int(kd)))
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -47,54 +47,81 @@ template <> struct RowChunk<float> {
     }
 };
 
+// 16 bytes of activations -> floats in shared memory
+__device__ __forceinline__ void stage_chunk(const __nv_bfloat16* src, float* dst) {
+    const uint4 x = __ldg(reinterpret_cast<const uint4*>(src));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); dst[2 * j] = f.x; dst[2 * j + 1] = f.y; }
+}
+__device__ __forceinline__ void stage_chunk(const float* src, float* dst) {
+    const float4 x = __ldg(reinterpret_cast<const float4*>(src));
+    dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
+}
+
+// Block = 8 warps, RT_TOK tokens, `rows_per_block` weight rows (a warp takes every 8th of them).
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(32 * RT_ROWS)
 moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
-                         float* __restrict__ z, int T, int H, int E) {
+                         float* __restrict__ z, int T, int H, int E, int rows_per_block) {
     extern __shared__ __align__(16) float xs[];   // [RT_TOK][H]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * RT_TOK;
     const int nt = min(RT_TOK, T - t0);
-    for (int idx = threadIdx.x; idx < RT_TOK * H; idx += 32 * RT_ROWS) {
-        const int j = idx / H, i = idx - j * H;
-        xs[idx] = j < nt ? to_float(x[(int64_t)(t0 + j) * H + i]) : 0.f;
+    constexpr int AV = 16 / sizeof(AT);           // activations per 16-byte load
+    if (H % AV == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const int per_row = H / AV;
+        for (int idx = threadIdx.x; idx < RT_TOK * per_row; idx += 32 * RT_ROWS) {
+            const int j = idx / per_row, c = idx - j * per_row;
+            float* dst = xs + j * H + c * AV;
+            if (j < nt) stage_chunk(x + (int64_t)(t0 + j) * H + c * AV, dst);
+            else
+#pragma unroll
+                for (int u = 0; u < AV; ++u) dst[u] = 0.f;
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < RT_TOK * H; idx += 32 * RT_ROWS) {
+            const int j = idx / H, i = idx - j * H;
+            xs[idx] = j < nt ? to_float(x[(int64_t)(t0 + j) * H + i]) : 0.f;
+        }
     }
     __syncthreads();
     const int ncols = E + (wsg ? 1 : 0);
-    const int e = blockIdx.y * RT_ROWS + warp;
-    if (e >= ncols) return;
-    const WT* w = e < E ? wr + (int64_t)e * H : wsg;
+    const int e_end = min(ncols, (int)(blockIdx.y + 1) * rows_per_block);
     constexpr int CN = RowChunk<WT>::N;
-    const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-    const int main = (aligned && H % 4 == 0) ? (H / CN) * CN : 0;   // rows of xs stay 16-byte aligned
-    float acc[RT_TOK];
+    for (int e = blockIdx.y * rows_per_block + warp; e < e_end; e += RT_ROWS) {
+        const WT* w = e < E ? wr + (int64_t)e * H : wsg;
+        const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+        const int main = (aligned && H % 4 == 0) ? (H / CN) * CN : 0;   // rows of xs stay 16-byte aligned
+        float acc[RT_TOK];
 #pragma unroll
-    for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
-    for (int i = lane * CN; i < main; i += 32 * CN) {
-        RowChunk<WT> c;
-        c.load(w + i);
+        for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
+        for (int i = lane * CN; i < main; i += 32 * CN) {
+            RowChunk<WT> c;
+            c.load(w + i);
 #pragma unroll
-        for (int j = 0; j < RT_TOK; ++j) {
-            const float4* xr = reinterpret_cast<const float4*>(xs + j * H + i);   // H % CN == 0 here
+            for (int j = 0; j < RT_TOK; ++j) {
+                const float4* xr = reinterpret_cast<const float4*>(xs + j * H + i);   // H % CN == 0 here
 #pragma unroll
-            for (int u = 0; u < CN / 4; ++u) {
-                const float4 xv = xr[u];
-                acc[j] += xv.x * c.v[4 * u];
-                acc[j] += xv.y * c.v[4 * u + 1];
-                acc[j] += xv.z * c.v[4 * u + 2];
-                acc[j] += xv.w * c.v[4 * u + 3];
+                for (int u = 0; u < CN / 4; ++u) {
+                    const float4 xv = xr[u];
+                    acc[j] += xv.x * c.v[4 * u];
+                    acc[j] += xv.y * c.v[4 * u + 1];
+                    acc[j] += xv.z * c.v[4 * u + 2];
+                    acc[j] += xv.w * c.v[4 * u + 3];
+                }
             }
         }
-    }
-    for (int i = main + lane; i < H; i += 32) {
-        const float wv = to_float(w[i]);
+        for (int i = main + lane; i < H; i += 32) {
+            const float wv = to_float(w[i]);
 #pragma unroll
-        for (int j = 0; j < RT_TOK; ++j) acc[j] += xs[j * H + i] * wv;
-    }
+            for (int j = 0; j < RT_TOK; ++j) acc[j] += xs[j * H + i] * wv;
+        }
 #pragma unroll
-    for (int j = 0; j < RT_TOK; ++j) {
-        const float v = warp_sum(acc[j]);
-        if (lane == 0 && j < nt) z[(int64_t)(t0 + j) * ncols + e] = v;
+        for (int j = 0; j < RT_TOK; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0 && j < nt) z[(int64_t)(t0 + j) * ncols + e] = v;
+        }
     }
 }
 
@@ -193,6 +220,67 @@ moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, 
             }
             run += __popc(bal);
         }
+    }
+}
+
+// For many rows: one block per expert, no atomics.
+//   counts:  counts[e] = number of (token, slot) pairs routed to e
+//   place:   offsets[e] = sum of counts below e; pairs of e placed in token order
+__global__ void __launch_bounds__(256)
+moe_permute_count_kernel(const int* __restrict__ topk_idx, int* __restrict__ counts, int N) {
+    __shared__ int warp_cnt[8];
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int c = 0;
+    for (int base = 0; base < N; base += 256) {
+        const int i = base + threadIdx.x;
+        c += __popc(__ballot_sync(0xffffffffu, i < N && topk_idx[i] == e));
+    }
+    if (lane == 0) warp_cnt[warp] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < 8; ++w) t += warp_cnt[w];
+        counts[e] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_permute_place_kernel(const int* __restrict__ topk_idx, const int* __restrict__ counts,
+                         int* __restrict__ offsets, int* __restrict__ sorted_token, int* __restrict__ inv_perm,
+                         int N, int E, int K) {
+    __shared__ int warp_cnt[8];
+    __shared__ int start_s;
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        int part = 0;
+        for (int i = lane; i < e; i += 32) part += counts[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) {
+            start_s = part;
+            offsets[e] = part;
+            if (e == E - 1) offsets[E] = part + counts[e];
+        }
+    }
+    __syncthreads();
+    int run = start_s;
+    const int end = run + counts[e];
+    for (int base = 0; base < N && run < end; base += 256) {
+        const int i = base + threadIdx.x;
+        const bool mine = i < N && topk_idx[i] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_cnt[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { const int c = warp_cnt[w]; total += c; if (w < warp) before += c; }
+        if (mine) {
+            const int pos = run + before + __popc(bal & ((1u << lane) - 1u));
+            sorted_token[pos] = i / K;
+            inv_perm[i] = pos;
+        }
+        run += total;
+        __syncthreads();
     }
 }
 
@@ -297,7 +385,11 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
         return kBadShape;
     }
     const int ncols = E + (wsg ? 1 : 0);
-    const dim3 grid((T + RT_TOK - 1) / RT_TOK, (ncols + RT_ROWS - 1) / RT_ROWS);
+    // few tokens: spread the weight rows over many blocks; many tokens: stage a token tile once
+    // and run all rows over it
+    const int token_tiles = (T + RT_TOK - 1) / RT_TOK;
+    const int rows_per_block = token_tiles >= 64 ? ((ncols + RT_ROWS - 1) / RT_ROWS) * RT_ROWS : RT_ROWS;
+    const dim3 grid(token_tiles, (ncols + rows_per_block - 1) / rows_per_block);
     if (grid.y > 65535) {
         set_last_error("router: %d experts exceed the grid limit", E);
         return kBadShape;
@@ -309,19 +401,26 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         MI_ROUTER_ATTR(AT, WT);
         moe_router_logits_kernel<AT, WT><<<grid, 32 * RT_ROWS, smem_x, stream>>>(
-            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, T, H, E));
+            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, T, H, E, rows_per_block));
     moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w, gate,
                                                                     probs_out, T, E, K, norm_topk);
     return finish_launch("moe_router", 2);
 }
 
-int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int T, int E, int K,
-                   cudaStream_t stream) {
+// `counts_scratch` holds E ints (used when there are many rows).
+int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int* counts_scratch, int T,
+                   int E, int K, cudaStream_t stream) {
     if (E + 1 > 12000) {
         set_last_error("permute: %d experts exceed the shared-memory table", E);
         return kBadShape;
     }
     const int64_t N = (int64_t)T * K;
+    if (N > 2048 && E <= 65535) {
+        moe_permute_count_kernel<<<E, 256, 0, stream>>>(topk_idx, counts_scratch, (int)N);
+        moe_permute_place_kernel<<<E, 256, 0, stream>>>(topk_idx, counts_scratch, offsets, sorted_token, inv_perm,
+                                                        (int)N, E, K);
+        return finish_launch("moe_permute", 2);
+    }
     size_t smem = sizeof(int) * (E + 1);
     const int idx_in_smem = (smem + sizeof(int) * N <= 160 * 1024) ? 1 : 0;
     if (idx_in_smem) smem += sizeof(int) * N;

@@ -299,7 +299,8 @@ def moe_permute(topk_idx: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor,
     offsets = torch.empty(num_experts + 1, dtype=I32, device=dev)
     sorted_token = torch.empty(T * K, dtype=I32, device=dev)
     inv_perm = torch.empty(T * K, dtype=I32, device=dev)
-    check(library().mi_moe_permute(_ptr(topk_idx), _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T,
+    counts = torch.empty(num_experts, dtype=I32, device=dev)
+    check(library().mi_moe_permute(_ptr(topk_idx), _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), _ptr(counts), T,
                                    int(num_experts), K, _stream()), "moe_permute")
     return offsets, sorted_token, inv_perm
 

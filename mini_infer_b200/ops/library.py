@@ -28,7 +28,7 @@ _SIGNATURES = {
     "mi_attn_tiled": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_moe_router": [P, I, P, P, I, P, P, P, P, P, I, I, I, I, I, P],
-    "mi_moe_permute": [P, P, P, P, I, I, I, P],
+    "mi_moe_permute": [P, P, P, P, P, I, I, I, P],
     "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
     "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],

@@ -63,6 +63,8 @@ class SparseMoE(FeedForward):
     graph_safe = True
     # up to this many rows per expert on average, the decode-sized grouped product is used
     SKINNY_ROWS_PER_EXPERT = 8
+    # up to this many tokens in a step, the shared expert runs on a second stream beside the routed path
+    OVERLAP_MAX_TOKENS = 64
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -77,6 +79,7 @@ class SparseMoE(FeedForward):
             raise ValueError(f"moe: top_k {self.K} must lie in [1, min(32, num_experts={self.E})]")
         self.last_routing = None
         self.keep_routing = False
+        self._side_stream = None
 
     def tensor_decls(self) -> List[TensorDecl]:
         p = self.prefix
@@ -119,8 +122,25 @@ class SparseMoE(FeedForward):
         self._skinny = (rt.act == torch.bfloat16 and F.grouped_gemm_skinny_supported(self.H)
                         and F.grouped_gemm_skinny_supported(self.mI))
 
+    def _shared_expert(self, x: torch.Tensor) -> torch.Tensor:
+        gu = linear(x, self.w_shared_gate_up, self.rt.act)
+        return linear(F.swiglu(gu), self.w_shared_down, torch.float32)
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = x.shape[0]
+        shared = None
+        side = None
+        if self.sI > 0 and T <= self.OVERLAP_MAX_TOKENS:
+            # decode-sized step: every kernel is short, so the shared expert runs beside the routed
+            # path on a second stream (fork here, join before the combine)
+            main = torch.cuda.current_stream()
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=x.device)
+            side = self._side_stream
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shared = self._shared_expert(x)
+            shared.record_stream(main)
         idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
                                            want_probs=self.keep_routing)
         if self.keep_routing:
@@ -139,10 +159,10 @@ class SparseMoE(FeedForward):
         else:
             act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
             y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
-        shared = None
-        if self.sI > 0:
-            gu = linear(x, self.w_shared_gate_up, self.rt.act)
-            shared = linear(F.swiglu(gu), self.w_shared_down, torch.float32)
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        elif self.sI > 0:
+            shared = self._shared_expert(x)
         return F.moe_combine(y, inv_perm, w, shared, gate)
 
 

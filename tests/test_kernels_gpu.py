@@ -354,10 +354,14 @@ def test_router_ties_go_to_the_lowest_index():
         F().moe_router(x, wr, None, 11, False)
 
 
-@pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8)])
+@pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8), (700, 9, 3),
+                                   (2100, 7, 1)])
 def test_permute(T, E, K):
     g = torch.Generator().manual_seed(T)
-    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    if K == 1:
+        idx[idx == 3] = 4                                        # an expert nobody is routed to
+    idx = idx.to(DEV)
     offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
     flat = idx.flatten().cpu().long()
     counts = torch.bincount(flat, minlength=E)

@@ -3,7 +3,7 @@
 //
 // Block = 4 warps = 64 queries of one head (16 per warp, held as MMA fragments); key tiles of 64,
 // aligned to absolute positions, are gathered page row by page row into shared memory with
-// cp.async (double buffered), S = Q K^T and O += P V run on mma.sync m16n8k16 with float
+// cp.async (three stages), S = Q K^T and O += P V run on mma.sync m16n8k16 with float
 // accumulators, the softmax runs online in float on the accumulator fragments.  Masking is
 // positional: key j is visible from the query at position p iff j <= p and (window == 0 or
 // j > p - window); rows of keys that are masked for the whole tile are zero-filled.
@@ -16,7 +16,7 @@
 namespace mi {
 namespace pf {
 
-constexpr int BQ = 64, BKEYS = 64, THREADS = 128;
+constexpr int BQ = 64, BKEYS = 64, THREADS = 128, NSTAGE = 3;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -64,7 +64,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     constexpr int DT = D / 8;          // n-tiles of O
     constexpr int TILE = BKEYS * D * 2;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ int64_t row_off[2][BKEYS];
+    __shared__ int64_t row_off[NSTAGE][BKEYS];
 
     const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
     const int q0 = q_start[b], q_len = q_start[b + 1] - q0;
@@ -77,8 +77,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int p_hi = p_lo + nq - 1;
 
     const uint32_t sQ = smem_u32(smem);
-    const uint32_t sK[2] = {sQ + BQ * D * 2, sQ + BQ * D * 2 + 2 * TILE};
-    const uint32_t sV[2] = {sK[0] + TILE, sK[1] + TILE};
+    auto sK = [&](int buf) { return sQ + (uint32_t)(BQ * D * 2 + 2 * buf * TILE); };
+    auto sV = [&](int buf) { return sQ + (uint32_t)(BQ * D * 2 + 2 * buf * TILE + TILE); };
 
     // ---- Q tile -> shared (rows beyond nq zero-filled) ---------------------------------------
     for (int idx = tid; idx < BQ * CH; idx += THREADS) {
@@ -113,14 +113,19 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
             const int64_t off = row_off[buf][r];
             const bool valid = off >= 0;
             const int64_t o = (valid ? off : 0) + c * 8;
-            cp_async16(tile_addr<D>(sK[buf], r, c), k_cache + o, valid);
-            cp_async16(tile_addr<D>(sV[buf], r, c), v_cache + o, valid);
+            cp_async16(tile_addr<D>(sK(buf), r, c), k_cache + o, valid);
+            cp_async16(tile_addr<D>(sV(buf), r, c), v_cache + o, valid);
         }
         cp_async_commit();
     };
 
-    load_tile(0, 0);
-    cp_async_wait<1>();            // the Q tile has landed (the first key tile may still be in flight)
+    // prefetch distance NSTAGE - 1: one commit group per tile (empty when there is no such tile)
+#pragma unroll
+    for (int i = 0; i < NSTAGE - 1; ++i) {
+        if (i < n_tiles) load_tile(i, i);
+        else cp_async_commit();
+    }
+    cp_async_wait<NSTAGE - 1>();   // the Q tile has landed (key tiles may still be in flight)
     __syncthreads();
 
     // ---- Q fragments ---------------------------------------------------------------------------
@@ -141,13 +146,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int pos_a = p_lo + row_a, pos_b = p_lo + row_b;
 
     for (int ti = 0; ti < n_tiles; ++ti) {
-        const int buf = ti & 1;
-        if (ti + 1 < n_tiles) {
-            load_tile(ti + 1, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int buf = ti % NSTAGE;
+        if (ti + NSTAGE - 1 < n_tiles) load_tile(ti + NSTAGE - 1, (ti + NSTAGE - 1) % NSTAGE);
+        else cp_async_commit();
+        cp_async_wait<NSTAGE - 1>();   // all but the newest NSTAGE-1 groups are done: tile ti is here
         __syncthreads();
         const int kt = k_begin + ti * BKEYS;
 
@@ -160,25 +162,41 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
             for (int ks = 0; ks < KS; ks += 2) {
                 uint32_t kb[4];   // b0,b1 of k-step ks, b0,b1 of k-step ks+1
-                ldmatrix_x4(kb, tile_addr<D>(sK[buf], nt * 8 + (lane & 7), ks * 2 + (lane >> 3)));
+                ldmatrix_x4(kb, tile_addr<D>(sK(buf), nt * 8 + (lane & 7), ks * 2 + (lane >> 3)));
                 mma16816(s[nt], qf[ks], kb[0], kb[1]);
                 mma16816(s[nt], qf[ks + 1], kb[2], kb[3]);
             }
         }
-        // mask, scale (log2 domain), running maximum
+        // mask, scale (log2 domain), running maximum; a tile wholly visible to every row of the
+        // block (all keys at or below the first query, inside every window, all rows real) skips the tests
         float mx[2] = {-INFINITY, -INFINITY};
+        const bool all_visible = nq == BQ && kt + BKEYS - 1 <= p_lo && kt + BKEYS <= k_end &&
+                                 (window == 0 || kt > p_hi - window) && row_off[buf][BKEYS - 1] >= 0 &&
+                                 row_off[buf][0] >= 0;
+        if (all_visible) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int kj = kt + nt * 8 + 2 * t + (j & 1);
-                const int pos = (j & 2) ? pos_b : pos_a;
-                const int row = (j & 2) ? row_b : row_a;
-                const bool vis = row < nq && kj <= pos && (window == 0 || kj > pos - window) &&
-                                 row_off[buf][kj - kt] >= 0;
-                const float v = vis ? s[nt][j] * scale_log2 : -INFINITY;
-                s[nt][j] = v;
-                mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                for (int j = 0; j < 4; ++j) {
+                    const float v = s[nt][j] * scale_log2;
+                    s[nt][j] = v;
+                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int kj = kt + nt * 8 + 2 * t + (j & 1);
+                    const int pos = (j & 2) ? pos_b : pos_a;
+                    const int row = (j & 2) ? row_b : row_a;
+                    const bool vis = row < nq && kj <= pos && (window == 0 || kj > pos - window) &&
+                                     row_off[buf][kj - kt] >= 0;
+                    const float v = vis ? s[nt][j] * scale_log2 : -INFINITY;
+                    s[nt][j] = v;
+                    mx[j >> 1] = fmaxf(mx[j >> 1], v);
+                }
             }
         }
         float alpha[2];
@@ -222,7 +240,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
             for (int dt = 0; dt < DT; dt += 2) {
                 uint32_t vb[4];   // b0,b1 for d-tile dt, b0,b1 for d-tile dt+1
                 const int row = 16 * j + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldmatrix_x4_trans(vb, tile_addr<D>(sV[buf], row, dt + (lane >> 4)));
+                ldmatrix_x4_trans(vb, tile_addr<D>(sV(buf), row, dt + (lane >> 4)));
                 mma16816(o_acc[dt], pa[j], vb[0], vb[1]);
                 mma16816(o_acc[dt + 1], pa[j], vb[2], vb[3]);
             }
@@ -275,7 +293,7 @@ int mi_attn_prefill(const void* q, const void* k_cache, const void* v_cache, con
     }
     const dim3 grid((max_q_len + pf::BQ - 1) / pf::BQ, nh, B);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)pf::BQ * d * 2 + 4 * (size_t)pf::BKEYS * d * 2;
+    const size_t smem = (size_t)pf::BQ * d * 2 + 2 * pf::NSTAGE * (size_t)pf::BKEYS * d * 2;
 #define MI_PF(DD)                                                                                          \
     do {                                                                                                   \
         auto kern = pf::attn_prefill_kernel<DD>;                                                           \

@@ -125,6 +125,70 @@ moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, co
     }
 }
 
+// Few tokens (decode): one block per weight row and group of RT_TOK tokens; the 8 warps split the
+// row, so every lane has a single round of loads in flight, and the warps' partial sums are added
+// in warp order.  The order of a dot product's additions depends on H only.
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(256)
+moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                               float* __restrict__ z, int T, int H, int E) {
+    __shared__ float part[8][RT_TOK];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x;
+    const int t0 = blockIdx.y * RT_TOK;
+    const int nt = min(RT_TOK, T - t0);
+    const int ncols = E + (wsg ? 1 : 0);
+    const WT* w = e < E ? wr + (int64_t)e * H : wsg;
+    constexpr int CN = RowChunk<WT>::N;
+    constexpr int AV = 16 / sizeof(AT);
+    constexpr int L = CN > AV ? CN : AV;          // elements per thread and round: whole 16-byte loads of both
+    const bool vec = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     H % L == 0;
+    const int main = vec ? H : 0;
+    float acc[RT_TOK];
+#pragma unroll
+    for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
+    for (int i = threadIdx.x * L; i < main; i += 256 * L) {
+        float wv[L];
+#pragma unroll
+        for (int u = 0; u < L; u += CN) {
+            RowChunk<WT> c;
+            c.load(w + i + u);
+#pragma unroll
+            for (int k = 0; k < CN; ++k) wv[u + k] = c.v[k];
+        }
+#pragma unroll
+        for (int j = 0; j < RT_TOK; ++j) {
+            if (j < nt) {
+                float xv[L];
+                const AT* xp = x + (int64_t)(t0 + j) * H + i;
+#pragma unroll
+                for (int u = 0; u < L; u += AV) stage_chunk(xp + u, xv + u);
+#pragma unroll
+                for (int u = 0; u < L; ++u) acc[j] += xv[u] * wv[u];
+            }
+        }
+    }
+    for (int i = main + threadIdx.x; i < H; i += 256) {
+        const float wv = to_float(w[i]);
+#pragma unroll
+        for (int j = 0; j < RT_TOK; ++j)
+            if (j < nt) acc[j] += to_float(x[(int64_t)(t0 + j) * H + i]) * wv;
+    }
+#pragma unroll
+    for (int j = 0; j < RT_TOK; ++j) {
+        const float v = warp_sum(acc[j]);
+        if (lane == 0) part[warp][j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < nt) {
+        float v = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) v += part[wv][threadIdx.x];
+        z[(int64_t)(t0 + threadIdx.x) * ncols + e] = v;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restrict__ topk_idx,
                          float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
@@ -393,6 +457,15 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
     if (grid.y > 65535) {
         set_last_error("router: %d experts exceed the grid limit", E);
         return kBadShape;
+    }
+    if (T <= 4 * RT_TOK) {
+        const dim3 sgrid(ncols, token_tiles);
+        MI_DISPATCH_2(adtype, AT, wdtype, WT,
+            moe_router_logits_small_kernel<AT, WT><<<sgrid, 256, 0, stream>>>(
+                (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, T, H, E));
+        moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w,
+                                                                        gate, probs_out, T, E, K, norm_topk);
+        return finish_launch("moe_router", 2);
     }
 #define MI_ROUTER_ATTR(AT, WT)                                                                              \
     if (smem_x > 48 * 1024)                                                                                 \

@@ -222,7 +222,7 @@ template <int E> struct RawVec<__nv_bfloat16, E> {
     }
 };
 
-constexpr int DEC_SPLIT = 256;
+constexpr int DEC_SPLIT = 512;
 constexpr int DEC_GROUPS = 16;
 
 template <typename AT, int D>

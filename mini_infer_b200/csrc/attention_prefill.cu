@@ -76,9 +76,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int p_lo = kvl - q_len + qt * BQ;            // position of the tile's first query
     const int p_hi = p_lo + nq - 1;
 
-    const uint32_t sQ = smem_u32(smem);
-    auto sK = [&](int buf) { return sQ + (uint32_t)(BQ * D * 2 + 2 * buf * TILE); };
-    auto sV = [&](int buf) { return sQ + (uint32_t)(BQ * D * 2 + 2 * buf * TILE + TILE); };
+    // The Q tile borrows the last pipeline stage: it is turned into register fragments before the
+    // first key tile that uses that stage is requested.
+    static_assert(BQ * D * 2 <= 2 * TILE, "the Q tile must fit a pipeline stage");
+    const uint32_t s0 = smem_u32(smem);
+    auto sK = [&](int buf) { return s0 + (uint32_t)(2 * buf * TILE); };
+    auto sV = [&](int buf) { return s0 + (uint32_t)(2 * buf * TILE + TILE); };
+    const uint32_t sQ = sK(NSTAGE - 1);
 
     // ---- Q tile -> shared (rows beyond nq zero-filled) ---------------------------------------
     for (int idx = tid; idx < BQ * CH; idx += THREADS) {
@@ -135,6 +139,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         ldmatrix_x4(qf[ks], tile_addr<D>(sQ, row, ks * 2 + (lane >> 4)));
     }
+
+    __syncthreads();               // every warp holds its Q fragments: the borrowed stage is free
 
     float o_acc[DT][4];
 #pragma unroll
@@ -293,7 +299,7 @@ int mi_attn_prefill(const void* q, const void* k_cache, const void* v_cache, con
     }
     const dim3 grid((max_q_len + pf::BQ - 1) / pf::BQ, nh, B);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)pf::BQ * d * 2 + 2 * pf::NSTAGE * (size_t)pf::BKEYS * d * 2;
+    const size_t smem = 2 * pf::NSTAGE * (size_t)pf::BKEYS * d * 2;
 #define MI_PF(DD)                                                                                          \
     do {                                                                                                   \
         auto kern = pf::attn_prefill_kernel<DD>;                                                           \

@@ -148,6 +148,11 @@ add_rmsnorm_vec_kernel(float* __restrict__ hidden, const float* __restrict__ del
 // ---------------------------------------------------------------------------
 constexpr int QKV_HEADS_PER_BLOCK = 8;
 
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(128)
 qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
@@ -171,39 +176,68 @@ qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
             kbase = (int64_t)page * nkv * page_size * d + (int64_t)off * d;
         }
     }
-    // work items: (head of this block, pair index i < half); with half dividing the block size a
-    // thread keeps the same i for all its heads and computes the angle's cosine and sine once
+    // work items: (head of this block, two neighbouring pair indices i, i+1 < half); when the number
+    // of items per head divides the block size a thread keeps the same i for all its heads and
+    // computes the angles' cosines and sines once.  Values travel in pairs (8-byte loads, 4- or
+    // 8-byte stores).
     const int n_heads = h_hi - h_lo;
-    const bool same_i = half > 0 && (blockDim.x % half) == 0;
-    float c_keep = 1.f, s_keep = 0.f;
-    if (same_i && inv_freq) {
-        const float ang = pos * inv_freq[threadIdx.x % half];
-        c_keep = cosf(ang);
-        s_keep = sinf(ang);
-    }
-    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-        const int head = h_lo + idx / half, i = idx % half;
-        if (head >= nh + nkv) break;                         // v heads follow the q and k heads
-        AT* dst = nullptr;
-        if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
-        else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
-        if (!dst) continue;
-        const int c0 = head * d + i, c1 = c0 + half;
-        float x0 = row[c0], x1 = row[c1];
-        if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
-        float y0 = x0, y1 = x1;
-        if (inv_freq) {
-            float c = c_keep, sn = s_keep;
-            if (!same_i) {
-                const float ang = pos * inv_freq[i];
-                c = cosf(ang);
-                sn = sinf(ang);
-            }
-            y0 = x0 * c - x1 * sn;
-            y1 = x1 * c + x0 * sn;
+    if ((half & 1) == 0 && half > 0) {
+        const int hp = half >> 1;
+        const bool same_i = (blockDim.x % hp) == 0;
+        float c0k = 1.f, s0k = 0.f, c1k = 1.f, s1k = 0.f;
+        if (same_i && inv_freq) {
+            const int i = 2 * (threadIdx.x % hp);
+            const float a0 = pos * inv_freq[i], a1 = pos * inv_freq[i + 1];
+            c0k = cosf(a0); s0k = sinf(a0); c1k = cosf(a1); s1k = sinf(a1);
         }
-        dst[i] = from_float<AT>(y0);
-        dst[i + half] = from_float<AT>(y1);
+        for (int idx = threadIdx.x; idx < n_heads * hp; idx += blockDim.x) {
+            const int head = h_lo + idx / hp, i = 2 * (idx % hp);
+            if (head >= nh + nkv) break;                     // v heads follow the q and k heads
+            AT* dst = nullptr;
+            if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
+            else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
+            if (!dst) continue;
+            const int c0 = head * d + i, c1 = c0 + half;
+            float2 lo = *reinterpret_cast<const float2*>(row + c0);
+            float2 hi = *reinterpret_cast<const float2*>(row + c1);
+            if (bias) {
+                lo.x += to_float(bias[c0]); lo.y += to_float(bias[c0 + 1]);
+                hi.x += to_float(bias[c1]); hi.y += to_float(bias[c1 + 1]);
+            }
+            float2 ylo = lo, yhi = hi;
+            if (inv_freq) {
+                float ca = c0k, sa = s0k, cb = c1k, sb = s1k;
+                if (!same_i) {
+                    const float a0 = pos * inv_freq[i], a1 = pos * inv_freq[i + 1];
+                    ca = cosf(a0); sa = sinf(a0); cb = cosf(a1); sb = sinf(a1);
+                }
+                ylo.x = lo.x * ca - hi.x * sa;  yhi.x = hi.x * ca + lo.x * sa;
+                ylo.y = lo.y * cb - hi.y * sb;  yhi.y = hi.y * cb + lo.y * sb;
+            }
+            store_pair(dst + i, ylo.x, ylo.y);
+            store_pair(dst + i + half, yhi.x, yhi.y);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+            const int head = h_lo + idx / half, i = idx % half;
+            if (head >= nh + nkv) break;
+            AT* dst = nullptr;
+            if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
+            else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
+            if (!dst) continue;
+            const int c0 = head * d + i, c1 = c0 + half;
+            float x0 = row[c0], x1 = row[c1];
+            if (bias) { x0 += to_float(bias[c0]); x1 += to_float(bias[c1]); }
+            float y0 = x0, y1 = x1;
+            if (inv_freq) {
+                const float ang = pos * inv_freq[i];
+                const float c = cosf(ang), sn = sinf(ang);
+                y0 = x0 * c - x1 * sn;
+                y1 = x1 * c + x0 * sn;
+            }
+            dst[i] = from_float<AT>(y0);
+            dst[i + half] = from_float<AT>(y1);
+        }
     }
     for (int head = h_lo; head < h_hi; ++head) {
         if (head < nh + nkv) {

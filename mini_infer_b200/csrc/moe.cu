@@ -96,6 +96,7 @@ moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, co
         float acc[RT_TOK];
 #pragma unroll
         for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
+#pragma unroll 4
         for (int i = lane * CN; i < main; i += 32 * CN) {
             RowChunk<WT> c;
             c.load(w + i);

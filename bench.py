@@ -8,8 +8,10 @@ The model has the layer sizes of Qwen1.5-MoE-A2.7B (24 layers, hidden 2048, 16 h
 bfloat16 weights and seeded uniform-random token ids.  The headline ``value`` is decoded tokens
 per second at batch 8 with 2,048-token prompts in a 4,096-token context: K timed decode steps,
 timed on the device with CUDA events after W warm-up steps.  ``e2e`` is the same metric through
-the scheduler that the Python entry point drives (host token ids in through pinned memory, sampled
-ids back to the host, every step).  ``prefill`` times one 2,048-token prompt; ``points`` holds
+the Python entry point ``LLM.generate`` (host token ids in, host token ids out; every step stages its
+inputs in pinned memory, copies them to the device and reads the sampled ids back): the wall time
+of generating K+1 tokens per prompt minus that of generating 1, so that the prompts' prefill
+cancels.  ``prefill`` times one 2,048-token prompt; ``points`` holds
 decode at batch 1 and 64; ``roofline`` divides the bytes a decode step must read (every weight it
 uses once, the cache of the live requests) by its time.  Every step reads far more than the
 126 MB of L2 (gigabytes of weights), so no separate flush is needed between timed iterations.
@@ -125,7 +127,7 @@ def prefill_flops(cfg, layers, T):
 
 def run_ours(args):
     import torch
-    from mini_infer_b200.engine.llm import GPUExecutor
+    from mini_infer_b200.engine.llm import LLM, GPUExecutor
     from mini_infer_b200.engine.loading import random_model
     from mini_infer_b200.engine.request import Request
     from mini_infer_b200.engine.scheduler import Scheduler, SchedulerConfig
@@ -145,12 +147,14 @@ def run_ours(args):
     load_s = time.time() - t0
     page = DEFAULT_PAGE_SIZE
     prompt_len, ctx_len = args.prompt_len, args.context
+    if args.only != "all":
+        args.points = False
     max_b = max(args.batch, 64 if args.points else args.batch, 1)
     per_req_tokens = prompt_len + args.steps + args.warmup + 2 * max_b + 16
     num_pages = max_b * (-(-per_req_tokens // page)) + 8
-    runner = ModelRunner(model, rt, page_size=page, num_pages=num_pages, max_requests=max_b,
-                         max_tokens_per_step=max(2048, max_b), max_context=ctx_len)
-    sampler = Sampler(rt.device, cfg["vocab_size"], max_b)
+    llm = LLM(model, runtime=rt, max_seq_len=ctx_len, page_size=page, num_pages=num_pages, max_running=max_b,
+              max_tokens_per_step=max(2048, max_b), prefill_chunk=2048, cuda_graphs=not args.eager)
+    runner, sampler = llm.runner, llm.sampler
     g = torch.Generator().manual_seed(args.seed)
 
     def random_prompt(n):
@@ -172,13 +176,22 @@ def run_ours(args):
         ms = time_events(lambda: runner.step([StepEntry("pf", toks, [prompt_len - 1])]))
         runner.release("pf")
         return ms
-    for _ in range(2):
-        prefill_once()
-    pf_ms = min(prefill_once() for _ in range(3))
-    pf_flops = prefill_flops(cfg, args.layers, prompt_len)
-    prefill = {"value": round(prompt_len / (pf_ms / 1e3), 1), "tokens": prompt_len, "ms": round(pf_ms, 3),
-               "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
-               "tflops": round(pf_flops / (pf_ms / 1e3) / 1e12, 2), "of": pk["source"]}
+    prefill = None
+    if args.only in ("all", "prefill"):
+        for _ in range(2):
+            prefill_once()
+        if args.profiler_range:
+            torch.cuda.profiler.start()
+        pf_ms = min(prefill_once() for _ in range(1 if args.profiler_range else 3))
+        if args.profiler_range:
+            torch.cuda.profiler.stop()
+        pf_flops = prefill_flops(cfg, args.layers, prompt_len)
+        prefill = {"value": round(prompt_len / (pf_ms / 1e3), 1), "tokens": prompt_len, "ms": round(pf_ms, 3),
+                   "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "tflops": round(pf_flops / (pf_ms / 1e3) / 1e12, 2), "of": pk["source"]}
+    if args.only == "prefill":
+        print(json.dumps({"impl": "ours", "only": "prefill", "layers": args.layers, "prefill": prefill}))
+        return 0
 
     # ---- decode through the scheduler (what the Python entry point drives) -------------------- #
     def decode_run(batch, steps, warmup, clocks=False):
@@ -197,6 +210,8 @@ def run_ours(args):
         if sampler_clock:
             sampler_clock.start()
         torch.cuda.synchronize()
+        if clocks and args.profiler_range:
+            torch.cuda.profiler.start()
         launches0 = launch_count() + runner.graph_kernel_launches
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.perf_counter()
@@ -208,6 +223,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         wall = time.perf_counter() - w0
         dev_ms = a.elapsed_time(b)
+        if clocks and args.profiler_range:
+            torch.cuda.profiler.stop()
         launches = launch_count() + runner.graph_kernel_launches - launches0   # eager + replayed in graphs
         clock = sampler_clock.stop() if sampler_clock else None
         kv_tokens = sum(r.num_computed for r in sched.running)
@@ -218,7 +235,25 @@ def run_ours(args):
     main = decode_run(args.batch, args.steps, args.warmup, clocks=True)
     ms_per_step = main["dev_ms"] / args.steps
     value = args.batch * args.steps / (main["dev_ms"] / 1e3)
-    e2e_value = args.batch * args.steps / main["wall_s"]
+    if args.only == "decode":
+        print(json.dumps({"impl": "ours", "only": "decode", "layers": args.layers, "batch": args.batch,
+                          "ms_per_step": round(ms_per_step, 4), "value": round(value, 1)}))
+        return 0
+
+    # ---- the same through the Python entry point: host token ids in, host token ids out ------- #
+    prompts = [random_prompt(prompt_len) for _ in range(args.batch)]
+
+    def generate_seconds(new_tokens):
+        torch.cuda.synchronize()
+        t = time.perf_counter()
+        outs = llm.generate(prompts, SamplingParams(greedy=True, max_new_tokens=new_tokens))
+        dt = time.perf_counter() - t
+        assert all(len(o.token_ids) == new_tokens for o in outs)
+        return dt
+    generate_seconds(2)                                            # warm-up of this path
+    t_short = min(generate_seconds(1) for _ in range(2))           # prefill and the first token
+    t_long = min(generate_seconds(args.steps + 1) for _ in range(2))
+    e2e_value = args.batch * args.steps / max(t_long - t_short, 1e-9)
 
     # ---- roofline of the decode step ----------------------------------------------------------- #
     E, K = cfg["num_experts"], cfg["num_experts_per_tok"]
@@ -285,6 +320,11 @@ def main():
                     help="fewer layers than the named configuration's 24 (same layer sizes) where memory or time needs it")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one workload and print a short line (used for profiling small cases)")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="wrap the timed region in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--eager", action="store_true", help="launch decode steps kernel by kernel, without CUDA graphs")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -69,7 +69,7 @@ class LLM:
     def __init__(self, model: Union[str, Model], dtype: str = "bfloat16", device: str = "cuda:0",
                  max_seq_len: int = 2048, page_size: Optional[int] = None, num_pages: Optional[int] = None,
                  max_running: int = 64, max_tokens_per_step: int = 2048, prefill_chunk: int = 0,
-                 memory_fraction: float = 0.85, runtime=None):
+                 memory_fraction: float = 0.85, runtime=None, cuda_graphs: bool = True):
         if isinstance(model, str):
             self.model, self.rt, self.config_json = load_model(model, dtype, device)
         else:
@@ -90,7 +90,7 @@ class LLM:
         max_tokens_per_step = max(max_tokens_per_step, max_running)
         self.runner = ModelRunner(self.model, self.rt, page_size=page_size, num_pages=num_pages,
                                   max_requests=max_running, max_tokens_per_step=max_tokens_per_step,
-                                  max_context=max_seq_len)
+                                  max_context=max_seq_len, cuda_graphs=cuda_graphs)
         self.sampler = Sampler(self.rt.device, self.model.spec.vocab_size, max_running)
         self.executor = GPUExecutor(self.runner, self.sampler)
         self.sched_cfg = SchedulerConfig(max_tokens_per_step=max_tokens_per_step, max_running=max_running,

@@ -89,39 +89,60 @@ moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, co
     const int ncols = E + (wsg ? 1 : 0);
     const int e_end = min(ncols, (int)(blockIdx.y + 1) * rows_per_block);
     constexpr int CN = RowChunk<WT>::N;
-    for (int e = blockIdx.y * rows_per_block + warp; e < e_end; e += RT_ROWS) {
-        const WT* w = e < E ? wr + (int64_t)e * H : wsg;
-        const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-        const int main = (aligned && H % 4 == 0) ? (H / CN) * CN : 0;   // rows of xs stay 16-byte aligned
-        float acc[RT_TOK];
+    constexpr int RR = 4;                          // weight rows per pass: a staged chunk of the tokens is
+                                                   // read from shared memory once for RR rows
+    const bool x_ok = H % 4 == 0;                  // rows of xs stay 16-byte aligned
+    for (int e0 = blockIdx.y * rows_per_block + warp; e0 < e_end; e0 += RT_ROWS * RR) {
+        const WT* w[RR];
+        bool aligned = x_ok;
 #pragma unroll
-        for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
-#pragma unroll 4
+        for (int r = 0; r < RR; ++r) {
+            const int e = min(e0 + r * RT_ROWS, e_end - 1);          // rows past the end repeat the last one
+            w[r] = e < E ? wr + (int64_t)e * H : wsg;
+            aligned = aligned && (reinterpret_cast<uintptr_t>(w[r]) & 15) == 0;
+        }
+        const int main = aligned ? (H / CN) * CN : 0;
+        float acc[RR][RT_TOK];
+#pragma unroll
+        for (int r = 0; r < RR; ++r)
+#pragma unroll
+            for (int j = 0; j < RT_TOK; ++j) acc[r][j] = 0.f;
         for (int i = lane * CN; i < main; i += 32 * CN) {
-            RowChunk<WT> c;
-            c.load(w + i);
+            RowChunk<WT> c[RR];
+#pragma unroll
+            for (int r = 0; r < RR; ++r) c[r].load(w[r] + i);
 #pragma unroll
             for (int j = 0; j < RT_TOK; ++j) {
-                const float4* xr = reinterpret_cast<const float4*>(xs + j * H + i);   // H % CN == 0 here
+                const float4* xr = reinterpret_cast<const float4*>(xs + j * H + i);
 #pragma unroll
                 for (int u = 0; u < CN / 4; ++u) {
                     const float4 xv = xr[u];
-                    acc[j] += xv.x * c.v[4 * u];
-                    acc[j] += xv.y * c.v[4 * u + 1];
-                    acc[j] += xv.z * c.v[4 * u + 2];
-                    acc[j] += xv.w * c.v[4 * u + 3];
+#pragma unroll
+                    for (int r = 0; r < RR; ++r) {
+                        acc[r][j] += xv.x * c[r].v[4 * u];
+                        acc[r][j] += xv.y * c[r].v[4 * u + 1];
+                        acc[r][j] += xv.z * c[r].v[4 * u + 2];
+                        acc[r][j] += xv.w * c[r].v[4 * u + 3];
+                    }
                 }
             }
         }
         for (int i = main + lane; i < H; i += 32) {
-            const float wv = to_float(w[i]);
 #pragma unroll
-            for (int j = 0; j < RT_TOK; ++j) acc[j] += xs[j * H + i] * wv;
+            for (int r = 0; r < RR; ++r) {
+                const float wv = to_float(w[r][i]);
+#pragma unroll
+                for (int j = 0; j < RT_TOK; ++j) acc[r][j] += xs[j * H + i] * wv;
+            }
         }
 #pragma unroll
-        for (int j = 0; j < RT_TOK; ++j) {
-            const float v = warp_sum(acc[j]);
-            if (lane == 0 && j < nt) z[(int64_t)(t0 + j) * ncols + e] = v;
+        for (int r = 0; r < RR; ++r) {
+            const int e = e0 + r * RT_ROWS;
+#pragma unroll
+            for (int j = 0; j < RT_TOK; ++j) {
+                const float v = warp_sum(acc[r][j]);
+                if (lane == 0 && j < nt && e < e_end) z[(int64_t)(t0 + j) * ncols + e] = v;
+            }
         }
     }
 }

@@ -204,6 +204,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
         bool ok = mbar_wait(&accum_bar, 0, abort_flag, 3);
         ok = __all_sync(0xffffffffu, ok);                 // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // With whole 16-byte groups of features per row the tile is transposed through the (now
+        // idle) pipeline memory and leaves in 16-byte stores; otherwise element by element.
+        constexpr int OUT_BYTES = MODE == 1 ? 2 : 4;
+        constexpr int PER16 = 16 / OUT_BYTES;                         // features per 16-byte group
+        const bool staged = (Nout % PER16) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        uint8_t* stage = smem;                                        // [rows][BF] outputs, row pitch BF * OUT_BYTES
+        const int fl = quarter * 32 + lane;                           // feature of this thread inside the tile
         if (ok) {
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
@@ -214,24 +221,43 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
                     uint32_t u[32];
                     tmem_ld32(lane_addr + MAXN + c0, u);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (f < Nout) {
-                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
+                    __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage) + (size_t)c0 * BF + fl;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (c0 + i < rows) {
-                                const float gv = __uint_as_float(g[i]);
-                                out[(int64_t)i * Nout] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * __uint_as_float(u[i]));
-                            }
+                    for (int i = 0; i < 32; ++i) {
+                        if (c0 + i < rows) {
+                            const float gv = __uint_as_float(g[i]);
+                            const __nv_bfloat16 v = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * __uint_as_float(u[i]));
+                            if (staged) st[(size_t)i * BF] = v;
+                            else if (f < Nout) out[(int64_t)i * Nout] = v;
                         }
                     }
                 } else {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (f < Nout) {
-                        float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + c0) * Nout + f;
+                    float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + c0) * Nout + f;
+                    float* st = reinterpret_cast<float*>(stage) + (size_t)c0 * BF + fl;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c0 + i < rows) out[(int64_t)i * Nout] = __uint_as_float(g[i]);
+                    for (int i = 0; i < 32; ++i) {
+                        if (c0 + i < rows) {
+                            if (staged) st[(size_t)i * BF] = __uint_as_float(g[i]);
+                            else if (f < Nout) out[(int64_t)i * Nout] = __uint_as_float(g[i]);
+                        }
                     }
+                }
+            }
+        }
+        if (staged) {
+            asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps, whatever `ok`
+            if (ok && *abort_flag == 0) {
+                constexpr int GROUPS = BF / PER16;                    // 16-byte groups per row of the tile
+                const int et = threadIdx.x - 64;                      // 0..127 among the epilogue threads
+                const uint4* src = reinterpret_cast<const uint4*>(stage);
+                uint8_t* dst = reinterpret_cast<uint8_t*>(C);
+                for (int idx = et; idx < rows * GROUPS; idx += 128) {
+                    const int r = idx / GROUPS, gq = idx - r * GROUPS;
+                    const int feat = n0 + gq * PER16;
+                    if (feat < Nout)
+                        *reinterpret_cast<uint4*>(dst + ((int64_t)(row0 + r) * Nout + feat) * OUT_BYTES) = src[idx];
                 }
             }
         }

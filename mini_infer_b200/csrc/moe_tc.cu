@@ -8,7 +8,8 @@
 // N operand, whose size follows the expert's row count (a multiple of 16 up to 256).  An expert
 // with 137 rows is one tile with N = 144 instead of two row tiles of 128, and its weights - the
 // bytes that bound this product - are read once.  One block computes one (expert, row tile,
-// feature tile):
+// feature tile) with two accumulators: gate and up of 128 features (mode 1), or two neighbouring
+// tiles of 128 features that share the row tile (mode 0):
 //   warp 0    TMA producer: weight tile(s) (128 features x 64 k) and row tile (rows x 64 k)
 //   warp 1    allocates tensor memory, issues the MMAs, commits stages back to the producer
 //   warps 2-5 epilogue: accumulators -> registers -> SwiGLU / store, one TMEM lane quarter each
@@ -114,8 +115,10 @@ __global__ void __launch_bounds__(192, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
                        int* __restrict__ status) {
-    constexpr int NB = MODE == 1 ? 2 : 1;                 // weight tiles per stage (gate and up, or one)
-    constexpr int STAGES = MODE == 1 ? 3 : 4;
+    constexpr int NB = 2;                                 // weight tiles per stage: gate and up (MODE 1), or two
+                                                          // neighbouring feature tiles sharing the row tile (MODE 0)
+    constexpr int STAGES = 3;
+    constexpr int FEATS = MODE == 1 ? BF : 2 * BF;        // output features per block
     constexpr int STAGE_BYTES = NB * W_TILE_BYTES + R_TILE_BYTES;
     constexpr uint32_t TMEM_COLS = NB * MAXN;             // 512 or 256: a power of two >= 32
     extern __shared__ uint8_t smem_raw[];
@@ -133,7 +136,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
         slot -= tiles;
     }
     if (!found) return;                                   // uniform for the whole block
-    const int n0 = blockIdx.x * BF;
+    const int n0 = blockIdx.x * FEATS;
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     const int num_kb = Kd / BK;
     const int n_mma = (rows + 15) & ~15;                  // MMA N: a multiple of 16 for M = 128
@@ -171,7 +174,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
                 uint8_t* st = smem + (size_t)s * STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], NB * W_TILE_BYTES + row_bytes);
                 tma_load_2d(st, &map_w, kb * BK, e * wrows + n0, &full_bar[s]);
-                if (MODE == 1) tma_load_2d(st + W_TILE_BYTES, &map_w, kb * BK, e * wrows + Nout + n0, &full_bar[s]);
+                tma_load_2d(st + W_TILE_BYTES, &map_w, kb * BK, e * wrows + (MODE == 1 ? Nout + n0 : n0 + BF), &full_bar[s]);
                 tma_load_2d(st + NB * W_TILE_BYTES, &maps_a.m[box], kb * BK, row0, &full_bar[s]);
             }
         }
@@ -191,16 +194,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
                     const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
                     const uint64_t rd = umma_desc(r_addr + k * 32);
                     umma_bf16(tmem_base, umma_desc(w_addr + k * 32), rd, idesc, acc);
-                    if (MODE == 1) umma_bf16(tmem_base + MAXN, umma_desc(w_addr + W_TILE_BYTES + k * 32), rd, idesc, acc);
+                    umma_bf16(tmem_base + MAXN, umma_desc(w_addr + W_TILE_BYTES + k * 32), rd, idesc, acc);
                 }
                 umma_commit(&empty_bar[s]);               // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(&accum_bar);              // accumulators complete
         }
     } else {
-        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; a lane is a feature of the tile
+        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; a lane is a feature of a 128-feature tile
         const int quarter = warp & 3;
-        const int f = n0 + quarter * 32 + lane;
+        const int fl = quarter * 32 + lane;
         bool ok = mbar_wait(&accum_bar, 0, abort_flag, 3);
         ok = __all_sync(0xffffffffu, ok);                 // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -208,57 +211,65 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
         // idle) pipeline memory and leaves in 16-byte stores; otherwise element by element.
         constexpr int OUT_BYTES = MODE == 1 ? 2 : 4;
         constexpr int PER16 = 16 / OUT_BYTES;                         // features per 16-byte group
+        constexpr int HALVES = MODE == 1 ? 1 : 2;                     // accumulators that are outputs of their own
         const bool staged = (Nout % PER16) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         uint8_t* stage = smem;                                        // [rows][BF] outputs, row pitch BF * OUT_BYTES
-        const int fl = quarter * 32 + lane;                           // feature of this thread inside the tile
-        if (ok) {
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < rows; c0 += 32) {      // columns beyond n_mma hold nothing; they are not stored
-                uint32_t g[32];
-                tmem_ld32(lane_addr + c0, g);
-                if (MODE == 1) {
-                    uint32_t u[32];
-                    tmem_ld32(lane_addr + MAXN + c0, u);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
-                    __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage) + (size_t)c0 * BF + fl;
+        for (int half = 0; half < HALVES; ++half) {
+            const int fbase = n0 + half * BF;                         // first feature of this accumulator
+            const int f = fbase + fl;
+            if (ok && fbase < Nout) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < rows; c0 += 32) {  // columns beyond n_mma hold nothing; they are not stored
+                    uint32_t g[32];
+                    tmem_ld32(lane_addr + half * MAXN + c0, g);
+                    if (MODE == 1) {
+                        uint32_t u[32];
+                        tmem_ld32(lane_addr + MAXN + c0, u);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
+                        __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage) + (size_t)c0 * BF + fl;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (c0 + i < rows) {
-                            const float gv = __uint_as_float(g[i]);
-                            const __nv_bfloat16 v = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * __uint_as_float(u[i]));
-                            if (staged) st[(size_t)i * BF] = v;
-                            else if (f < Nout) out[(int64_t)i * Nout] = v;
+                        for (int i = 0; i < 32; ++i) {
+                            if (c0 + i < rows) {
+                                const float gv = __uint_as_float(g[i]);
+                                // the result is rounded to bfloat16: the fast exponential and division are exact enough
+                                const __nv_bfloat16 v =
+                                    __float2bfloat16_rn(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[i]));
+                                if (staged) st[(size_t)i * BF] = v;
+                                else if (f < Nout) out[(int64_t)i * Nout] = v;
+                            }
                         }
-                    }
-                } else {
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + c0) * Nout + f;
-                    float* st = reinterpret_cast<float*>(stage) + (size_t)c0 * BF + fl;
+                    } else {
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + c0) * Nout + f;
+                        float* st = reinterpret_cast<float*>(stage) + (size_t)c0 * BF + fl;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (c0 + i < rows) {
-                            if (staged) st[(size_t)i * BF] = __uint_as_float(g[i]);
-                            else if (f < Nout) out[(int64_t)i * Nout] = __uint_as_float(g[i]);
+                        for (int i = 0; i < 32; ++i) {
+                            if (c0 + i < rows) {
+                                if (staged) st[(size_t)i * BF] = __uint_as_float(g[i]);
+                                else if (f < Nout) out[(int64_t)i * Nout] = __uint_as_float(g[i]);
+                            }
                         }
                     }
                 }
             }
-        }
-        if (staged) {
-            asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps, whatever `ok`
-            if (ok && *abort_flag == 0) {
-                constexpr int GROUPS = BF / PER16;                    // 16-byte groups per row of the tile
-                const int et = threadIdx.x - 64;                      // 0..127 among the epilogue threads
-                const uint4* src = reinterpret_cast<const uint4*>(stage);
-                uint8_t* dst = reinterpret_cast<uint8_t*>(C);
-                for (int idx = et; idx < rows * GROUPS; idx += 128) {
-                    const int r = idx / GROUPS, gq = idx - r * GROUPS;
-                    const int feat = n0 + gq * PER16;
-                    if (feat < Nout)
-                        *reinterpret_cast<uint4*>(dst + ((int64_t)(row0 + r) * Nout + feat) * OUT_BYTES) = src[idx];
+            if (staged) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps, whatever `ok`
+                if (ok && *abort_flag == 0 && fbase < Nout) {
+                    constexpr int GROUPS = BF / PER16;                // 16-byte groups per row of the tile
+                    const int et = threadIdx.x - 64;                  // 0..127 among the epilogue threads
+                    const uint4* src = reinterpret_cast<const uint4*>(stage);
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(C);
+                    for (int idx = et; idx < rows * GROUPS; idx += 128) {
+                        const int r = idx / GROUPS, gq = idx - r * GROUPS;
+                        const int feat = fbase + gq * PER16;
+                        if (feat < Nout)
+                            *reinterpret_cast<uint4*>(dst + ((int64_t)(row0 + r) * Nout + feat) * OUT_BYTES) = src[idx];
+                    }
                 }
+                if (half + 1 < HALVES) asm volatile("bar.sync 1, 128;" ::: "memory");   // staging is reused
             }
         }
     }
@@ -357,14 +368,15 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
         set_last_error("grouped product (tensor cores): cuTensorMapEncodeTiled failed");
         return kLaunchFailed;
     }
-    const dim3 grid((Nout + tc::BF - 1) / tc::BF, max_tiles);
+    const int feats = mode == 1 ? tc::BF : 2 * tc::BF;
+    const dim3 grid((Nout + feats - 1) / feats, max_tiles);
     if (mode == 1) {
         const size_t smem = 3 * (size_t)(2 * tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
         auto kern = tc::grouped_gemm_tc_kernel<1>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);
     } else {
-        const size_t smem = 4 * (size_t)(tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
+        const size_t smem = 3 * (size_t)(2 * tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
         auto kern = tc::grouped_gemm_tc_kernel<0>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);

@@ -194,6 +194,29 @@ def moe_block(x: Tensor, w: Dict[str, Tensor], prefix: str, num_experts: int, to
     return out, idx, probs
 
 
+def moe_block_by_expert(x: Tensor, w: Dict[str, Tensor], prefix: str, num_experts: int, top_k: int,
+                        norm_topk_prob: bool, has_shared: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    """The same block as :func:`moe_block` with the loops turned inside out: for every expert, all
+    the tokens routed to it at once.  Sums per token run over slots in the order of the experts'
+    indices instead of the order of the slots, so results agree up to rounding; it exists because
+    the token-by-token form is too slow at real layer sizes."""
+    probs, idx, wts = route(x, w[prefix + "gate.weight"], top_k, norm_topk_prob)
+    out = torch.zeros_like(x)
+    for e in range(num_experts):
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        p = f"{prefix}experts.{e}."
+        y = swiglu_mlp(x[tok], w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+        out.index_add_(0, tok, wts[tok, slot][:, None] * y)
+    if has_shared:
+        p = prefix + "shared_expert."
+        sh = swiglu_mlp(x, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+        gamma = x @ w[prefix + "shared_expert_gate.weight"].T
+        out = out + (1.0 / (1.0 + torch.exp(-gamma))) * sh
+    return out, idx, probs
+
+
 # --------------------------------------------------------------------------- #
 # the model
 # --------------------------------------------------------------------------- #
@@ -219,7 +242,7 @@ def layer_window(cfg: dict, i: int) -> int:
 
 def forward(cfg: dict, weights: Dict[str, Tensor], token_ids: Sequence[int], dtype=torch.float32,
             forced_routing: Optional[Dict[int, Tensor]] = None,
-            record: Optional[dict] = None) -> Tensor:
+            record: Optional[dict] = None, by_expert: bool = False) -> Tensor:
     """Logits ``[S, V]`` of one whole sequence.
 
     Block: ``a = x + Attn(RMSNorm_in(x))``; ``y = a + FFN(RMSNorm_post(a))``
@@ -230,7 +253,7 @@ def forward(cfg: dict, weights: Dict[str, Tensor], token_ids: Sequence[int], dty
     ``record`` (a dict) receives per-layer routing (``idx``, ``probs``) and the
     hidden state after each layer.
     """
-    w = {k: v.to(dtype) for k, v in weights.items()}
+    w = weights if all(v.dtype == dtype for v in weights.values()) else {k: v.to(dtype) for k, v in weights.items()}
     dev = next(iter(w.values())).device
     ids = torch.as_tensor(list(token_ids), dtype=torch.long, device=dev)
     H = cfg["hidden_size"]
@@ -247,10 +270,16 @@ def forward(cfg: dict, weights: Dict[str, Tensor], token_ids: Sequence[int], dty
         x = rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
         if layer_is_sparse(cfg, i):
             forced = forced_routing.get(i) if forced_routing else None
-            y, idx, probs = moe_block(
-                x, w, p + "mlp.", cfg["num_experts"], cfg["num_experts_per_tok"],
-                bool(_cfg(cfg, "norm_topk_prob", False)),
-                _cfg(cfg, "shared_expert_intermediate_size", 0) > 0, forced)
+            if by_expert and forced is None:
+                y, idx, probs = moe_block_by_expert(
+                    x, w, p + "mlp.", cfg["num_experts"], cfg["num_experts_per_tok"],
+                    bool(_cfg(cfg, "norm_topk_prob", False)),
+                    _cfg(cfg, "shared_expert_intermediate_size", 0) > 0)
+            else:
+                y, idx, probs = moe_block(
+                    x, w, p + "mlp.", cfg["num_experts"], cfg["num_experts_per_tok"],
+                    bool(_cfg(cfg, "norm_topk_prob", False)),
+                    _cfg(cfg, "shared_expert_intermediate_size", 0) > 0, forced)
             if record is not None:
                 record.setdefault("routing", {})[i] = (idx, probs)
         else:

@@ -113,6 +113,14 @@ def test_moe_equals_dense_sum_over_chosen(model):
     assert not torch.allclose(out, out3)
 
 
+def test_by_expert_form_agrees_with_the_token_by_token_form(model):
+    cfg, w = model
+    toks = tiny.pick_tokens(cfg, w, 50, 9)
+    a = pm.forward(cfg, w, toks)
+    b = pm.forward(cfg, w, toks, by_expert=True)
+    assert float((a - b).abs().max()) < 1e-5 * float(a.abs().max())
+
+
 def test_sampling_rules():
     logits = torch.tensor([0.0, 3.0, 3.0, -1.0, 3.0])
     assert pm.greedy(logits) == 1

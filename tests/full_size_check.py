@@ -13,6 +13,13 @@ tokens once, and each kept row is compared with the plain row for the same posit
 causal, so the plain row does not depend on later tokens).  Prints the largest error relative to the
 largest logit, and how many of the engine's greedy tokens equal the plain model's arg-max.
 
+Expert routing is discontinuous: where two router probabilities differ by less than the engine's
+rounding, the engine may choose the other expert, and the logits then differ visibly although no
+kernel is wrong.  The script therefore records the experts the engine chose for every token and
+layer and prints a second figure, the error against the plain model made to follow that choice,
+together with the number of tokens whose choice differed and the largest amount by which a chosen
+expert's plain-model probability fell short of the K-th largest.
+
 The plain model holds a second copy of the weights, so both fit one 180 GB GPU only up to about
 70 GB of weights: use ``--layers`` to cut the 57B configuration down for the comparison.
 """
@@ -113,10 +120,21 @@ def main():
               prefill_chunk=args.chunk, num_pages=args.requests * (ctx // 16 + 1))
     # keep the logits the sampler saw, by wrapping the executor's run
     kept = {}
+    routing = {}
+    sparse = {i: l.feed_forward for i, l in enumerate(model.layers) if hasattr(l.feed_forward, "keep_routing")}
+    for part in sparse.values():
+        part.keep_routing = True          # (this also keeps decode steps out of CUDA graphs)
     inner_step = llm.runner.step
 
     def recording_step(entries):
         res = inner_step(entries)
+        t = 0
+        for e in entries:
+            start = llm.runner.num_tokens(e.rid) - len(e.tokens)
+            for li, part in sparse.items():
+                idx = part.last_routing[0][t:t + len(e.tokens)]
+                routing.setdefault(e.rid, {}).setdefault(li, {})[start] = idx.clone()
+            t += len(e.tokens)
         if res.logits is not None:
             rows = res.logits.float()
             for r, (rid, place) in enumerate(res.index):
@@ -134,21 +152,34 @@ def main():
           flush=True)
     llm.runner.step = inner_step
 
-    worst, agree, total = 0.0, 0, 0
+    worst, worst_f, agree, total, differ, short = 0.0, 0.0, 0, 0, 0, 0.0
+    K = cfg["num_experts_per_tok"]
     rids = sorted(kept, key=lambda r: r[1])
     for rid, prompt, out in zip(rids, prompts, outs):
         full = prompt + out.token_ids
-        ref = plain_model.forward(cfg, weights, full, dtype=plain_dtype, by_expert=True)
+        n_fed = len(full) - 1                                   # the last generated token was never fed
+        rec = {}
+        ref = plain_model.forward(cfg, weights, full[:n_fed], dtype=plain_dtype, by_expert=True, record=rec)
+        forced = {li: torch.cat([per[s] for s in sorted(per)]).long() for li, per in routing[rid].items()}
+        rec_f = {}
+        ref_f = plain_model.forward(cfg, weights, full[:n_fed], dtype=plain_dtype, by_expert=True,
+                                    forced_routing=forced, record=rec_f)
+        for li, eng in forced.items():
+            differ += int((torch.sort(eng, 1).values != torch.sort(rec["routing"][li][0], 1).values).any(1).sum())
+            probs = rec_f["routing"][li][1]
+            kth = torch.sort(probs, dim=1, descending=True).values[:, K - 1]
+            short = max(short, float((kth[:, None] - probs.gather(1, eng)).max()))
         scale = float(ref.abs().max())
         for pos, row in sorted(kept[rid].items()):
-            err = float((row - ref[pos]).abs().max()) / scale
-            worst = max(worst, err)
+            worst = max(worst, float((row - ref[pos]).abs().max()) / scale)
+            worst_f = max(worst_f, float((row - ref_f[pos]).abs().max()) / scale)
             agree += int(int(ref[pos].argmax()) == full[pos + 1])
             total += 1
-        print(f"request with {len(prompt):5d} prompt tokens: {len(kept[rid])} positions compared, "
-              f"largest error so far {worst:.3e} of the largest logit", flush=True)
-    print(f"RESULT config={args.config} dtype={args.dtype} layers={cfg['num_hidden_layers']} "
-          f"positions={total} max_rel_err={worst:.3e} greedy_agree={agree}/{total}")
+        print(f"request with {len(prompt):5d} prompt tokens: {len(kept[rid])} positions compared, largest error so far "
+              f"{worst:.3e} ({worst_f:.3e} with the engine's routing) of the largest logit", flush=True)
+    print(f"RESULT config={args.config} dtype={args.dtype} layers={cfg['num_hidden_layers']} positions={total} "
+          f"max_rel_err={worst:.3e} max_rel_err_with_engine_routing={worst_f:.3e} greedy_agree={agree}/{total} "
+          f"token_layers_routed_differently={differ} largest_probability_shortfall={short:.2e}")
     return 0
 
 

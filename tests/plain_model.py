@@ -195,12 +195,18 @@ def moe_block(x: Tensor, w: Dict[str, Tensor], prefix: str, num_experts: int, to
 
 
 def moe_block_by_expert(x: Tensor, w: Dict[str, Tensor], prefix: str, num_experts: int, top_k: int,
-                        norm_topk_prob: bool, has_shared: bool) -> Tuple[Tensor, Tensor, Tensor]:
+                        norm_topk_prob: bool, has_shared: bool,
+                        forced_idx: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Tensor]:
     """The same block as :func:`moe_block` with the loops turned inside out: for every expert, all
     the tokens routed to it at once.  Sums per token run over slots in the order of the experts'
     indices instead of the order of the slots, so results agree up to rounding; it exists because
     the token-by-token form is too slow at real layer sizes."""
     probs, idx, wts = route(x, w[prefix + "gate.weight"], top_k, norm_topk_prob)
+    if forced_idx is not None:
+        idx = forced_idx.to(idx.device).long()
+        wts = probs.gather(1, idx)
+        if norm_topk_prob:
+            wts = wts / wts.sum(dim=-1, keepdim=True)
     out = torch.zeros_like(x)
     for e in range(num_experts):
         tok, slot = (idx == e).nonzero(as_tuple=True)
@@ -270,11 +276,11 @@ def forward(cfg: dict, weights: Dict[str, Tensor], token_ids: Sequence[int], dty
         x = rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
         if layer_is_sparse(cfg, i):
             forced = forced_routing.get(i) if forced_routing else None
-            if by_expert and forced is None:
+            if by_expert:
                 y, idx, probs = moe_block_by_expert(
                     x, w, p + "mlp.", cfg["num_experts"], cfg["num_experts_per_tok"],
                     bool(_cfg(cfg, "norm_topk_prob", False)),
-                    _cfg(cfg, "shared_expert_intermediate_size", 0) > 0)
+                    _cfg(cfg, "shared_expert_intermediate_size", 0) > 0, forced)
             else:
                 y, idx, probs = moe_block(
                     x, w, p + "mlp.", cfg["num_experts"], cfg["num_experts_per_tok"],

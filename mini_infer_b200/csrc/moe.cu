@@ -151,13 +151,11 @@ moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, co
 // row, so every lane has a single round of loads in flight, and the warps' partial sums are added
 // in warp order.  The order of a dot product's additions depends on H only.
 template <typename AT, typename WT>
-__global__ void __launch_bounds__(256)
-moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
-                               float* __restrict__ z, int T, int H, int E) {
+__device__ __forceinline__ void router_logits_small_block(const AT* __restrict__ x, const WT* __restrict__ wr,
+                                                          const WT* __restrict__ wsg, float* __restrict__ z,
+                                                          int T, int H, int E, int e, int t0) {
     __shared__ float part[8][RT_TOK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x;
-    const int t0 = blockIdx.y * RT_TOK;
     const int nt = min(RT_TOK, T - t0);
     const int ncols = E + (wsg ? 1 : 0);
     const WT* w = e < E ? wr + (int64_t)e * H : wsg;
@@ -211,20 +209,27 @@ moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ 
     }
 }
 
+template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
-moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restrict__ topk_idx,
-                         float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
-                         int T, int E, int K, int norm_topk) {
-    extern __shared__ float smem[];  // [8][E]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 8 + warp;
-    if (t >= T) return;
-    float* p = smem + warp * E;
+moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                               float* __restrict__ z, int T, int H, int E) {
+    router_logits_small_block<AT, WT>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y * RT_TOK);
+}
+
+// Softmax over all experts, K rounds of arg-max (lowest index among equals), weights; one warp per
+// token.  `p` is the warp's E floats of shared memory; the logits are read around L1 (they may have
+// been written by other blocks of the same launch).
+__device__ __forceinline__ void router_select_token(const float* __restrict__ z, int has_gate,
+                                                    int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                    float* __restrict__ gate, float* __restrict__ probs_out,
+                                                    float* p, int* idx_copy, int t, int E, int K,
+                                                    int norm_topk) {
+    const int lane = threadIdx.x & 31;
     const int ncols = E + (has_gate ? 1 : 0);
     const float* zr = z + (int64_t)t * ncols;
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) { const float v = zr[e]; p[e] = v; mx = fmaxf(mx, v); }
-    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zr[E]));
+    for (int e = lane; e < E; e += 32) { const float v = __ldcg(zr + e); p[e] = v; mx = fmaxf(mx, v); }
+    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-__ldcg(zr + E)));
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
@@ -259,6 +264,7 @@ moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restr
         wsum += best;
         if (lane == 0) {
             topk_idx[(int64_t)t * K + k] = bi;
+            if (idx_copy) idx_copy[t * K + k] = bi;
             p[bi] = -INFINITY;
         }
         __syncwarp();
@@ -266,21 +272,34 @@ moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restr
     if (lane < K) topk_w[(int64_t)t * K + lane] = norm_topk ? my_w / wsum : my_w;
 }
 
+__global__ void __launch_bounds__(256)
+moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restrict__ topk_idx,
+                         float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
+                         int T, int E, int K, int norm_topk) {
+    extern __shared__ float smem[];  // [8][E]
+    const int warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    router_select_token(z, has_gate, topk_idx, topk_w, gate, probs_out, smem + warp * E, nullptr, t, E, K,
+                        norm_topk);
+}
+
 // ---------------------------------------------------------------------------
 // Permutation (one block): counts per expert, exclusive scan, stable placement.
 //   offsets[E+1]; sorted_token[N] = token of sorted row; inv_perm[t*K+k] = sorted row
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, int* __restrict__ sorted_token,
-                   int* __restrict__ inv_perm, int N, int E, int K, int idx_in_smem) {
-    extern __shared__ int sh[];  // [E+1] starts, then (if it fits) a copy of topk_idx
+__device__ __forceinline__ void permute_block(const int* __restrict__ topk_idx, int* __restrict__ offsets,
+                                              int* __restrict__ sorted_token, int* __restrict__ inv_perm,
+                                              int* sh, int N, int E, int K, int idx_in_smem) {
     int* sidx = sh + E + 1;
     const int tid = threadIdx.x;
     for (int e = tid; e <= E; e += blockDim.x) sh[e] = 0;
     __syncthreads();
+    // idx_in_smem: 0 read the indices from global memory, 1 copy them to shared memory first,
+    // 2 the caller has put them there already
     for (int i = tid; i < N; i += blockDim.x) {
-        const int e = topk_idx[i];
-        if (idx_in_smem) sidx[i] = e;
+        const int e = idx_in_smem == 2 ? sidx[i] : topk_idx[i];
+        if (idx_in_smem == 1) sidx[i] = e;
         if (e >= 0 && e < E) atomicAdd(&sh[e + 1], 1);
     }
     __syncthreads();
@@ -307,6 +326,46 @@ moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, 
             run += __popc(bal);
         }
     }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, int* __restrict__ sorted_token,
+                   int* __restrict__ inv_perm, int N, int E, int K, int idx_in_smem) {
+    extern __shared__ int sh[];  // [E+1] starts, then (if it fits) a copy of topk_idx
+    permute_block(topk_idx, offsets, sorted_token, inv_perm, sh, N, E, K, idx_in_smem);
+}
+
+// Routing of a few tokens (decode) in one launch: every block computes one weight row's logits; the
+// block that finishes last (a ticket counter, no block waits for another) selects the experts of
+// all tokens and builds the permutation.  `ticket` is zero before the launch and is zero again after.
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(256)
+moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                       float* __restrict__ z, unsigned* __restrict__ ticket, int* __restrict__ topk_idx,
+                       float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
+                       int* __restrict__ offsets, int* __restrict__ sorted_token, int* __restrict__ inv_perm,
+                       int T, int H, int E, int K, int norm_topk) {
+    extern __shared__ int route_sh[];  // select: [8][E] floats; then permute: [E+1] + [T*K] ints
+    __shared__ bool last;
+    router_logits_small_block<AT, WT>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y * RT_TOK);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned n = gridDim.x * gridDim.y;
+        last = atomicAdd(ticket, 1u) == n - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x == 0) *ticket = 0u;
+    const int warp = threadIdx.x >> 5;
+    float* p = reinterpret_cast<float*>(route_sh) + warp * E;
+    int* perm_sh = route_sh + 8 * E;
+    for (int t = warp; t < T; t += 8)
+        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, p, perm_sh + E + 1, t, E, K,
+                            norm_topk);
+    __syncthreads();
+    permute_block(nullptr, offsets, sorted_token, inv_perm, perm_sh, T * K, E, K, 2);
 }
 
 // For many rows: one block per expert, no atomics.
@@ -500,6 +559,43 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
     moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w, gate,
                                                                     probs_out, T, E, K, norm_topk);
     return finish_launch("moe_router", 2);
+}
+
+// Router and permutation of a step of at most mi_moe_route_small_max_tokens() tokens in one launch.
+// `ticket` is one unsigned that is zero before the first call; the kernel leaves it zero.
+int mi_moe_route_small_max_tokens() { return 4 * RT_TOK; }
+
+int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
+                       unsigned* ticket, int* topk_idx, float* topk_w, float* gate, float* probs_out,
+                       int* offsets, int* sorted_token, int* inv_perm, int T, int H, int E, int K, int norm_topk,
+                       cudaStream_t stream) {
+    if (T <= 0) return kOk;
+    if (T > mi_moe_route_small_max_tokens()) {
+        set_last_error("router (decode): %d tokens, takes at most %d", T, mi_moe_route_small_max_tokens());
+        return kBadShape;
+    }
+    if (K < 1 || K > 32 || K > E) {
+        set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
+        return kBadShape;
+    }
+    const size_t smem = sizeof(float) * 8 * (size_t)E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
+    if (smem > 160 * 1024 || E + 1 > 65535) {
+        set_last_error("router (decode): %d experts exceed the shared memory of a block", E);
+        return kBadShape;
+    }
+    const int ncols = E + (wsg ? 1 : 0);
+    const dim3 grid(ncols, (T + RT_TOK - 1) / RT_TOK);
+#define MI_ROUTE_ATTR(AT, WT)                                                                             \
+    if (smem > 48 * 1024)                                                                                 \
+        cudaFuncSetAttribute(moe_route_small_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                             (int)smem)
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        MI_ROUTE_ATTR(AT, WT);
+        moe_route_small_kernel<AT, WT><<<grid, 256, smem, stream>>>(
+            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, ticket, topk_idx, topk_w, gate, probs_out,
+            offsets, sorted_token, inv_perm, T, H, E, K, norm_topk));
+#undef MI_ROUTE_ATTR
+    return finish_launch("moe_route_small");
 }
 
 // `counts_scratch` holds E ints (used when there are many rows).

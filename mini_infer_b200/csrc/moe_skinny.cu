@@ -123,6 +123,186 @@ grouped_gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __res
     }
 }
 
+
+// Dense product for a step of a few tokens: C[r, n] = a_r . W[n, :] (+ bias[n]), all of W read once.
+// A block owns 16 output features; its 8 warps split the inner dimension into 8 contiguous ranges
+// (so a block keeps 8 x 2 KB x unroll of weight loads in flight) and their partial sums are added
+// in warp order through shared memory: the order of additions depends on K only.
+// MODE 0 writes float; MODE 1 holds gate and up rows (W has 2 * Nout rows) and writes
+// silu(gate) * up as bfloat16.  Tile j of NT holds rows 8j .. 8j+7.
+template <int MODE, int NT>
+__global__ void __launch_bounds__(256)
+dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                    const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
+    constexpr int H = MODE == 1 ? 2 : 1;
+    __shared__ float red[8][NT * H * 4][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int f0 = blockIdx.x * 16;
+    const int fa = min(f0 + g, Nout - 1), fb = min(f0 + g + 8, Nout - 1);
+    const uint4* wa = reinterpret_cast<const uint4*>(W + (int64_t)fa * Kd) + t;
+    const uint4* wb = reinterpret_cast<const uint4*>(W + (int64_t)fb * Kd) + t;
+    const uint4* ua = nullptr;
+    const uint4* ub = nullptr;
+    if (MODE == 1) {
+        ua = reinterpret_cast<const uint4*>(W + (int64_t)(Nout + fa) * Kd) + t;
+        ub = reinterpret_cast<const uint4*>(W + (int64_t)(Nout + fb) * Kd) + t;
+    }
+    const uint4* xr[NT];
+    bool xv[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int r = 8 * j + g;
+        xv[j] = r < rows;
+        xr[j] = reinterpret_cast<const uint4*>(A + (int64_t)(xv[j] ? r : 0) * Kd) + t;
+    }
+    float acc[NT][H][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int h = 0; h < H; ++h)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[j][h][i] = 0.f;
+
+    const int chunks = Kd >> 5;
+    const int per = (chunks + 7) >> 3;
+    const int c_begin = min(warp * per, chunks), c_end = min(c_begin + per, chunks);
+#pragma unroll 4
+    for (int c = c_begin; c < c_end; ++c) {
+        const uint4 va = ld_stream(wa + 4 * c), vb = ld_stream(wb + 4 * c);
+        uint4 pa, pb;
+        if (MODE == 1) { pa = ld_stream(ua + 4 * c); pb = ld_stream(ub + 4 * c); }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            uint4 x = make_uint4(0u, 0u, 0u, 0u);
+            if (xv[j]) x = __ldg(xr[j] + 4 * c);
+            mma_bf16_16816(acc[j][0], va.x, vb.x, va.y, vb.y, x.x, x.y);
+            mma_bf16_16816(acc[j][0], va.z, vb.z, va.w, vb.w, x.z, x.w);
+            if (MODE == 1) {
+                mma_bf16_16816(acc[j][H - 1], pa.x, pb.x, pa.y, pb.y, x.x, x.y);
+                mma_bf16_16816(acc[j][H - 1], pa.z, pb.z, pa.w, pb.w, x.z, x.w);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int h = 0; h < H; ++h)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) red[warp][(j * H + h) * 4 + i][lane] = acc[j][h][i];
+    __syncthreads();
+    // one thread per (tile, fragment element, lane); fragment element i of lane (g, t) is
+    // feature f0 + g + (i & 2 ? 8 : 0), row 8j + 2t + (i & 1)
+    for (int o = threadIdx.x; o < NT * 4 * 32; o += blockDim.x) {
+        const int l = o & 31, i = (o >> 5) & 3, j = o >> 7;
+        const int f = f0 + (l >> 2) + ((i & 2) ? 8 : 0);
+        const int r = 8 * j + 2 * (l & 3) + (i & 1);
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            s0 += red[w][(j * H) * 4 + i][l];
+            if (MODE == 1) s1 += red[w][(j * H + H - 1) * 4 + i][l];
+        }
+        if (f < Nout && r < rows) {
+            const int64_t at = (int64_t)r * Nout + f;
+            if (MODE == 1) {
+                if (bias) { s0 += bias[f]; s1 += bias[Nout + f]; }
+                reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(s0 / (1.0f + expf(-s0)) * s1);
+            } else {
+                if (bias) s0 += bias[f];
+                reinterpret_cast<float*>(C)[at] = s0;
+            }
+        }
+    }
+}
+
+// Query/key/value projection of a step of a few tokens with its whole epilogue: bias, rotary
+// position encoding of q and k (half-split pairing, angle = position * inv_freq in float), q
+// written as bfloat16 and k, v written into their cache pages.  A block owns 8 rotation pairs
+// (i, i + d/2) of one head: fragment rows g and g + 8 are the two members of pair g, so the thread
+// that sums the warps' partial sums holds both.  Split of the inner dimension as in
+// dense_skinny_kernel.  grid = (d / 16, nh + 2 * nkv).
+template <int NT>
+__global__ void __launch_bounds__(256)
+qkv_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                  const float* __restrict__ bias, const int* __restrict__ positions,
+                  const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
+                  __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                  __nv_bfloat16* __restrict__ v_cache, int rows, int Kd, int nh, int nkv, int d, int page_size) {
+    __shared__ float red[8][NT * 4][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int head = blockIdx.y, half = d >> 1;
+    const int p0 = blockIdx.x * 8;
+    const int fa = head * d + p0 + g, fb = fa + half;
+    const uint4* wa = reinterpret_cast<const uint4*>(W + (int64_t)fa * Kd) + t;
+    const uint4* wb = reinterpret_cast<const uint4*>(W + (int64_t)fb * Kd) + t;
+    const uint4* xr[NT];
+    bool xv[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int r = 8 * j + g;
+        xv[j] = r < rows;
+        xr[j] = reinterpret_cast<const uint4*>(A + (int64_t)(xv[j] ? r : 0) * Kd) + t;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+    const int chunks = Kd >> 5;
+    const int per = (chunks + 7) >> 3;
+    const int c_begin = min(warp * per, chunks), c_end = min(c_begin + per, chunks);
+#pragma unroll 4
+    for (int c = c_begin; c < c_end; ++c) {
+        const uint4 va = ld_stream(wa + 4 * c), vb = ld_stream(wb + 4 * c);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            uint4 x = make_uint4(0u, 0u, 0u, 0u);
+            if (xv[j]) x = __ldg(xr[j] + 4 * c);
+            mma_bf16_16816(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
+            mma_bf16_16816(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][j * 4 + i][lane] = acc[j][i];
+    __syncthreads();
+    // one thread per (tile j, token parity i, lane): pair p0 + (lane >> 2) of token 8j + 2(lane & 3) + i
+    for (int o = threadIdx.x; o < NT * 2 * 32; o += blockDim.x) {
+        const int l = o & 31, i = (o >> 5) & 1, j = o >> 6;
+        const int r = 8 * j + 2 * (l & 3) + i;
+        float lo = 0.f, hi = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { lo += red[w][j * 4 + i][l]; hi += red[w][j * 4 + i + 2][l]; }
+        if (r >= rows) continue;
+        const int pi = p0 + (l >> 2);
+        const int c0 = head * d + pi, c1 = c0 + half;
+        if (bias) { lo += bias[c0]; hi += bias[c1]; }
+        __nv_bfloat16* dst = nullptr;
+        if (head < nh) {
+            dst = q_out + ((int64_t)r * nh + head) * d;
+        } else {
+            const int slot = slot_mapping[r];
+            if (slot >= 0) {
+                const int page = slot / page_size, off = slot - page * page_size;
+                const int hk = head < nh + nkv ? head - nh : head - nh - nkv;
+                dst = (head < nh + nkv ? k_cache : v_cache) + ((int64_t)page * nkv + hk) * page_size * d +
+                      (int64_t)off * d;
+            }
+        }
+        if (!dst) continue;
+        float ylo = lo, yhi = hi;
+        if (inv_freq && head < nh + nkv) {
+            const float ang = (float)positions[r] * inv_freq[pi];
+            const float ca = cosf(ang), sa = sinf(ang);
+            ylo = lo * ca - hi * sa;
+            yhi = hi * ca + lo * sa;
+        }
+        dst[pi] = __float2bfloat16_rn(ylo);
+        dst[pi + half] = __float2bfloat16_rn(yhi);
+    }
+}
+
 }  // namespace mi
 
 using namespace mi;
@@ -151,6 +331,80 @@ int mi_grouped_gemm_skinny(const void* A, const int* gather, const void* W, cons
         grouped_gemm_skinny_kernel<0><<<grid, 128, 0, stream>>>(
             (const __nv_bfloat16*)A, gather, (const __nv_bfloat16*)W, offsets, C, Nout, Kd);
     return finish_launch("grouped_gemm_skinny");
+}
+
+
+// Largest step (in rows) that the dense decode-sized product takes.
+int mi_dense_skinny_max_rows() { return 32; }
+
+// C = A @ W^T (+ bias) for rows <= 32.  A [rows, Kd], W [Nout (mode 0) or 2*Nout (mode 1), Kd] bfloat16;
+// bias float or null; C float [rows, Nout] (mode 0) or bfloat16 silu(gate)*up (mode 1).
+int mi_dense_skinny(const void* A, const void* W, const float* bias, void* C, int rows, int Nout, int Kd,
+                    int mode, cudaStream_t stream) {
+    if (Kd <= 0 || Kd % 32 != 0) {
+        set_last_error("dense product (decode): inner size %d is not a multiple of 32", Kd);
+        return kBadShape;
+    }
+    if (rows < 1 || rows > mi_dense_skinny_max_rows()) {
+        set_last_error("dense product (decode): %d rows, takes 1..%d", rows, mi_dense_skinny_max_rows());
+        return kBadShape;
+    }
+    if (Nout < 1) {
+        set_last_error("dense product (decode): %d output features", Nout);
+        return kBadShape;
+    }
+    const dim3 grid((Nout + 15) / 16), block(256);
+    const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+#define MI_DENSE_SKINNY(MODE, NT) dense_skinny_kernel<MODE, NT><<<grid, block, 0, stream>>>(a, w, bias, C, rows, Nout, Kd)
+    if (mode == 1) {
+        if (rows <= 8) MI_DENSE_SKINNY(1, 1);
+        else if (rows <= 16) MI_DENSE_SKINNY(1, 2);
+        else MI_DENSE_SKINNY(1, 4);
+    } else {
+        if (rows <= 8) MI_DENSE_SKINNY(0, 1);
+        else if (rows <= 16) MI_DENSE_SKINNY(0, 2);
+        else MI_DENSE_SKINNY(0, 4);
+    }
+#undef MI_DENSE_SKINNY
+    return finish_launch("dense_skinny");
+}
+
+// 1 if the fused projection takes this geometry: whole pairs tiles (d a multiple of 16), rotation
+// over the whole head (or none), inner size a multiple of 32.
+int mi_qkv_skinny_supported(int Kd, int d, int rot_dim) {
+    return (Kd > 0 && Kd % 32 == 0 && d > 0 && d % 16 == 0 && (rot_dim == d || rot_dim == 0)) ? 1 : 0;
+}
+
+// q, k, v = A @ W^T + bias for rows <= mi_dense_skinny_max_rows(), rotated and stored:
+// A [rows, Kd], W [(nh + 2*nkv) * d, Kd] bfloat16; bias float [(nh + 2*nkv) * d] or null;
+// inv_freq float [d/2] or null (no rotation); q_out [rows, nh, d]; k_cache, v_cache one layer's
+// [pages, nkv, page_size, d]; slot_mapping[r] = page * page_size + offset of row r (or < 0: not stored).
+int mi_qkv_skinny(const void* A, const void* W, const float* bias, const int* positions, const float* inv_freq,
+                  const int* slot_mapping, void* q_out, void* k_cache, void* v_cache, int rows, int Kd, int nh,
+                  int nkv, int d, int page_size, cudaStream_t stream) {
+    if (!mi_qkv_skinny_supported(Kd, d, inv_freq ? d : 0)) {
+        set_last_error("fused q/k/v projection: inner size %d or head size %d not taken", Kd, d);
+        return kBadShape;
+    }
+    if (rows < 1 || rows > mi_dense_skinny_max_rows()) {
+        set_last_error("fused q/k/v projection: %d rows, takes 1..%d", rows, mi_dense_skinny_max_rows());
+        return kBadShape;
+    }
+    if (nh < 1 || nkv < 1 || nh + 2 * nkv > 65535) {
+        set_last_error("fused q/k/v projection: %d query and %d key/value heads", nh, nkv);
+        return kBadShape;
+    }
+    const dim3 grid(d / 16, nh + 2 * nkv), block(256);
+#define MI_QKV_SKINNY(NT)                                                                                  \
+    qkv_skinny_kernel<NT><<<grid, block, 0, stream>>>(                                                     \
+        (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, positions, inv_freq, slot_mapping,         \
+        (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, rows, Kd, nh, nkv, d, page_size)
+    if (rows <= 8) MI_QKV_SKINNY(1);
+    else if (rows <= 16) MI_QKV_SKINNY(2);
+    else MI_QKV_SKINNY(4);
+#undef MI_QKV_SKINNY
+    return finish_launch("qkv_skinny");
 }
 
 }  // extern "C"

@@ -305,6 +305,44 @@ def moe_permute(topk_idx: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor,
     return offsets, sorted_token, inv_perm
 
 
+def route_small_max_tokens() -> int:
+    return int(library().mi_moe_route_small_max_tokens())
+
+
+def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
+                    norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False):
+    """:func:`moe_router` and :func:`moe_permute` of a step of a few tokens in one launch.
+
+    ``ticket`` is one int32 that is zero before the first call and belongs to the caller (the
+    kernel leaves it zero); calls that share a ticket must not overlap.  Returns
+    ``(idx, w, gate, probs, offsets, sorted_token, inv_perm)``.
+    """
+    _chk(x, "moe_route_small x")
+    T, H = x.shape
+    _chk(router_w, "moe_route_small weight", None, (None, H))
+    E = router_w.shape[0]
+    if shared_gate_w is not None:
+        _chk(shared_gate_w, "moe_route_small shared gate", router_w.dtype)
+        if shared_gate_w.numel() != H:
+            raise ValueError("moe_route_small: the shared-expert gate must have hidden_size entries")
+    _chk(ticket, "moe_route_small ticket", I32, (1,))
+    dev = x.device
+    idx = torch.empty(T, top_k, dtype=I32, device=dev)
+    w = torch.empty(T, top_k, dtype=F32, device=dev)
+    gate = torch.empty(T, dtype=F32, device=dev) if shared_gate_w is not None else None
+    probs = torch.empty(T, E, dtype=F32, device=dev) if want_probs else None
+    z = torch.empty(T, E + 1, dtype=F32, device=dev)
+    offsets = torch.empty(E + 1, dtype=I32, device=dev)
+    sorted_token = torch.empty(T * top_k, dtype=I32, device=dev)
+    inv_perm = torch.empty(T * top_k, dtype=I32, device=dev)
+    check(library().mi_moe_route_small(
+        _ptr(x), _code(x, "moe_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
+        _code(router_w, "moe_route_small weight"), _ptr(z), _ptr(ticket), _ptr(idx), _ptr(w), _ptr(gate), _ptr(probs),
+        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), int(bool(norm_topk)), _stream()),
+        "moe_route_small")
+    return idx, w, gate, probs, offsets, sorted_token, inv_perm
+
+
 def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
                        n_rows: int, swiglu_pair: bool, out_dtype: torch.dtype) -> torch.Tensor:
     """Per-expert product of sorted rows (float arithmetic).
@@ -350,6 +388,70 @@ def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torc
     check(library().mi_grouped_gemm_skinny(_ptr(a), _ptr(gather), _ptr(w), _ptr(offsets), _ptr(out), E, nout, Kd,
                                            1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny")
     return out
+
+
+def dense_skinny_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether :func:`dense_skinny` takes this product: bfloat16, a few rows, inner size a multiple of 32."""
+    return (x.dtype == BF16 and w.dtype == BF16 and x.dim() == 2 and x.is_contiguous() and w.is_contiguous()
+            and 1 <= x.shape[0] <= library().mi_dense_skinny_max_rows() and x.shape[1] % 32 == 0)
+
+
+def dense_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 swiglu_pair: bool = False) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for a step of a few tokens (decode), every weight read once.
+
+    ``x`` [T, K] and ``w`` [N, K] bfloat16, ``bias`` float32 [N] or None.  Returns float32
+    [T, N]; with ``swiglu_pair`` the rows of ``w`` are N/2 gate rows then N/2 up rows and the
+    result is ``silu(gate) * up`` as bfloat16 [T, N/2].
+    """
+    _chk(x, "dense_skinny x", BF16)
+    T, Kd = x.shape
+    _chk(w, "dense_skinny w", BF16, (None, Kd))
+    wrows = w.shape[0]
+    if swiglu_pair and wrows % 2:
+        raise KernelError(f"dense_skinny: {wrows} weight rows cannot hold gate and up halves")
+    nout = wrows // 2 if swiglu_pair else wrows
+    if bias is not None:
+        _chk(bias, "dense_skinny bias", F32, (wrows,))
+    out = torch.empty(T, nout, dtype=BF16 if swiglu_pair else F32, device=x.device)
+    check(library().mi_dense_skinny(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), T, nout, Kd,
+                                    1 if swiglu_pair else 0, _stream()), "dense_skinny")
+    return out
+
+
+def qkv_skinny_supported(kd: int, d: int, rot_dim: int) -> bool:
+    """Whether :func:`qkv_skinny` takes this geometry (``rot_dim`` 0: no rotation)."""
+    return bool(library().mi_qkv_skinny_supported(int(kd), int(d), int(rot_dim)))
+
+
+def qkv_skinny_max_rows() -> int:
+    return int(library().mi_dense_skinny_max_rows())
+
+
+def qkv_skinny(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+               inv_freq: Optional[torch.Tensor], slot_mapping: torch.Tensor, k_cache: torch.Tensor,
+               v_cache: torch.Tensor, nh: int, nkv: int, d: int, page_size: int) -> torch.Tensor:
+    """The q/k/v projection of a step of a few tokens with bias, rotary encoding and cache write
+    in the same kernel (what a library product followed by :func:`qkv_post` does).
+
+    ``x`` [T, K] and ``w_qkv`` [(nh + 2*nkv) * d, K] bfloat16, ``bias`` float32 or None.  Returns
+    ``q [T, nh, d]`` bfloat16; k and v of row ``t`` go to ``slot_mapping[t]`` of the caches.
+    """
+    _chk(x, "qkv_skinny x", BF16)
+    T, Kd = x.shape
+    width = (nh + 2 * nkv) * d
+    _chk(w_qkv, "qkv_skinny weight", BF16, (width, Kd))
+    _chk(bias, "qkv_skinny bias", F32, (width,))
+    _chk(positions, "qkv_skinny positions", I32, (T,))
+    _chk(inv_freq, "qkv_skinny inv_freq", F32, (d // 2,))
+    _chk(slot_mapping, "qkv_skinny slot_mapping", I32, (T,))
+    _chk(k_cache, "qkv_skinny k_cache", BF16, (None, nkv, page_size, d))
+    _chk(v_cache, "qkv_skinny v_cache", BF16, tuple(k_cache.shape))
+    q = torch.empty(T, nh, d, dtype=BF16, device=x.device)
+    check(library().mi_qkv_skinny(_ptr(x), _ptr(w_qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq),
+                                  _ptr(slot_mapping), _ptr(q), _ptr(k_cache), _ptr(v_cache), T, Kd, nh, nkv, d,
+                                  page_size, _stream()), "qkv_skinny")
+    return q
 
 
 def grouped_gemm_tc_supported(kd: int, nout: int) -> bool:

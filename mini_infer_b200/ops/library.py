@@ -32,6 +32,9 @@ _SIGNATURES = {
     "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
     "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],
+    "mi_moe_route_small": [P, I, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "mi_qkv_skinny": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "mi_dense_skinny": [P, P, P, P, I, I, I, I, P],
     "mi_gather_rows_bf16": [P, P, P, I, I, P],
     "mi_attn_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, P],
@@ -65,6 +68,12 @@ def library() -> ctypes.CDLL:
     lib.mi_grouped_gemm_tc_supported.restype = c_int
     lib.mi_grouped_gemm_skinny_supported.argtypes = [I]
     lib.mi_grouped_gemm_skinny_supported.restype = c_int
+    lib.mi_moe_route_small_max_tokens.argtypes = []
+    lib.mi_moe_route_small_max_tokens.restype = c_int
+    lib.mi_qkv_skinny_supported.argtypes = [I, I, I]
+    lib.mi_qkv_skinny_supported.restype = c_int
+    lib.mi_dense_skinny_max_rows.argtypes = []
+    lib.mi_dense_skinny_max_rows.restype = c_int
     lib.mi_attn_decode_split_size.argtypes = []
     lib.mi_attn_decode_split_size.restype = c_int
     _lib = lib

@@ -78,6 +78,12 @@ class GQAttention(Mixer):
         self.inv_freq = self.position.table(dev)
         self.rot_dim = self.position.rot_dim if self.inv_freq is not None else self.d
         self._tensor_core_prefill = rt.act == torch.bfloat16 and F.prefill_attention_supported(self.d)
+        # decode-sized steps: projection, bias, rotation and cache write in one kernel
+        self._fused_qkv_rows = 0
+        if (rt.act == torch.bfloat16 and not self.shares_cache
+                and F.qkv_skinny_supported(self.H, self.d, self.rot_dim if self.inv_freq is not None else 0)):
+            self._fused_qkv_rows = F.qkv_skinny_max_rows()
+            self._b_qkv_f32 = None if self.b_qkv is None else self.b_qkv.float()
 
     # -- cache ------------------------------------------------------------- #
     def cache_need(self):
@@ -95,11 +101,15 @@ class GQAttention(Mixer):
         view = ctx.kv_groups[cache.group]
         kc = view.k[cache.layer_slot]
         vc = view.v[cache.layer_slot]
-        qkv = linear(x, self.w_qkv, torch.float32)
-        nkv_in = 0 if self.shares_cache else self.nkv
-        q = F.qkv_post(qkv, self.b_qkv, ctx.positions, self.inv_freq, self.rot_dim,
-                       view.slot_mapping if nkv_in else None, kc if nkv_in else None, vc if nkv_in else None,
-                       self.nh, nkv_in, self.d, view.page_size, self.rt.act)
+        if ctx.num_tokens <= self._fused_qkv_rows:
+            q = F.qkv_skinny(x, self.w_qkv, self._b_qkv_f32, ctx.positions, self.inv_freq, view.slot_mapping,
+                             kc, vc, self.nh, self.nkv, self.d, view.page_size)
+        else:
+            qkv = linear(x, self.w_qkv, torch.float32)
+            nkv_in = 0 if self.shares_cache else self.nkv
+            q = F.qkv_post(qkv, self.b_qkv, ctx.positions, self.inv_freq, self.rot_dim,
+                           view.slot_mapping if nkv_in else None, kc if nkv_in else None, vc if nkv_in else None,
+                           self.nh, nkv_in, self.d, view.page_size, self.rt.act)
         if ctx.all_decode and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d):
             splits = -(-ctx.max_kv_len // F.decode_split_size())
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,

@@ -276,6 +276,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
     """``x @ w.T`` through the library product the reference also uses for every dense
     projection (cuBLAS, src/layers/attention.cpp:45-55, src/layers/mlp.cpp:120-130),
     accumulating in float32; ``w`` is ``[out, in]`` as stored in checkpoints."""
+    if out_dtype == torch.float32 and x.is_cuda and x.shape[0] <= 8:
+        from ..ops import functional as F
+        if F.dense_skinny_takes(x, w):
+            return F.dense_skinny(x, w)
     if x.dtype == out_dtype:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

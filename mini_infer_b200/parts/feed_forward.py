@@ -117,6 +117,9 @@ class SparseMoE(FeedForward):
             self.w_shared_down = m(tensors[q + "down_proj.weight"], dev)
             g = rt.precision.small(tensors[p + "shared_expert_gate.weight"], dev).reshape(-1)
             self.w_shared_gate = g.to(self.w_router.dtype).contiguous()
+        # the one-launch routing of decode-sized steps counts its blocks in this word
+        self._route_ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._route_small_max = F.route_small_max_tokens()
         self._tc = (rt.act == torch.bfloat16 and F.grouped_gemm_tc_supported(self.H, self.mI)
                     and F.grouped_gemm_tc_supported(self.mI, self.H) and self.H % 8 == 0)
         self._skinny = (rt.act == torch.bfloat16 and F.grouped_gemm_skinny_supported(self.H)
@@ -141,11 +144,16 @@ class SparseMoE(FeedForward):
             with torch.cuda.stream(side):
                 shared = self._shared_expert(x)
             shared.record_stream(main)
-        idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
-                                           want_probs=self.keep_routing)
+        if T <= self._route_small_max:
+            idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
+                x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
+                want_probs=self.keep_routing)
+        else:
+            idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
+                                               want_probs=self.keep_routing)
+            offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
         if self.keep_routing:
             self.last_routing = (idx, w, probs)
-        offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
         n = T * self.K
         if self._skinny and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
             # a few rows per expert: bound by reading each used expert once

@@ -354,6 +354,96 @@ def test_router_ties_go_to_the_lowest_index():
         F().moe_router(x, wr, None, 11, False)
 
 
+@pytest.mark.parametrize("T", [1, 5, 9, 17, 32])
+@pytest.mark.parametrize("N,Kd", [(40, 96), (200, 64), (2048 + 24, 352), (6, 1024)])
+def test_dense_skinny(T, N, Kd):
+    x = rnd(T, Kd, dtype=torch.bfloat16, seed=T)
+    w = rnd(N, Kd, dtype=torch.bfloat16, scale=0.2, seed=N)
+    bias = rnd(N, seed=3)
+    ref = x.float() @ w.float().t()
+    close(F().dense_skinny(x, w), ref, 5e-6, "product")
+    close(F().dense_skinny(x, w, bias), ref + bias, 5e-6, "product with bias")
+    if N % 2 == 0:
+        g, u = ref[:, :N // 2], ref[:, N // 2:]
+        out = F().dense_skinny(x, w, swiglu_pair=True)
+        assert out.dtype == torch.bfloat16
+        close(out, g / (1 + torch.exp(-g)) * u, 8e-3, "SwiGLU pair")
+    # the same row gives the same bits whatever stands beside it
+    alone = F().dense_skinny(x[:1].contiguous(), w)
+    assert torch.equal(alone[0], F().dense_skinny(x, w)[0])
+
+
+def test_dense_skinny_refuses_what_it_cannot_take():
+    from mini_infer_b200.ops.library import KernelError
+    w = rnd(16, 40, dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="multiple of 32"):
+        F().dense_skinny(rnd(2, 40, dtype=torch.bfloat16), w)
+    w = rnd(16, 64, dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="rows"):
+        F().dense_skinny(rnd(33, 64, dtype=torch.bfloat16), w)
+    assert not F().dense_skinny_takes(rnd(33, 64, dtype=torch.bfloat16), w)
+    assert not F().dense_skinny_takes(rnd(3, 64), rnd(16, 64))
+
+
+@pytest.mark.parametrize("T", [1, 7, 12, 31])
+@pytest.mark.parametrize("nh,nkv,d,H,rope", [(4, 2, 16, 64, True), (3, 1, 48, 96, True), (2, 2, 128, 256, True),
+                                             (5, 1, 32, 160, False)])
+def test_qkv_skinny_equals_product_and_post(T, nh, nkv, d, H, rope):
+    ps, pages = 4, 12
+    width = (nh + 2 * nkv) * d
+    x = rnd(T, H, dtype=torch.bfloat16, seed=T)
+    w = rnd(width, H, dtype=torch.bfloat16, scale=0.2, seed=d)
+    bias = rnd(width, seed=5)
+    pos = torch.tensor([0, 1, 2, 3, 17, 18, 400, 4000, 5] * 4, dtype=torch.int32, device=DEV)[:T].contiguous()
+    inv = None
+    if rope:
+        inv = torch.pow(torch.tensor(1e6, dtype=torch.float64),
+                        -2.0 * torch.arange(d // 2, dtype=torch.float64) / d).float().to(DEV)
+    slots = torch.tensor(random.Random(1).sample(range(ps * pages), T), dtype=torch.int32, device=DEV)
+    if T > 2:
+        slots[2] = -1                                                          # a row that is not stored
+    assert F().qkv_skinny_supported(H, d, d if rope else 0)
+    kc = torch.zeros(pages, nkv, ps, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = F().qkv_skinny(x, w, bias, pos, inv, slots, kc, vc, nh, nkv, d, ps)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc)
+    qkv = x.float() @ w.float().t()
+    q2 = F().qkv_post(qkv, bias, pos, inv, d if rope else 0, slots, kc2, vc2, nh, nkv, d, ps, torch.bfloat16)
+    # float sums in another order, then one rounding to bfloat16: at most one step apart
+    close(q, q2, 8e-3, "q")
+    close(kc, kc2, 8e-3, "k cache")
+    close(vc, vc2, 8e-3, "v cache")
+    assert torch.equal(kc == 0, kc2 == 0) and torch.equal(vc == 0, vc2 == 0)   # the same places written
+
+
+def test_qkv_skinny_refuses_partial_rotation():
+    assert not F().qkv_skinny_supported(64, 32, 16)
+    assert not F().qkv_skinny_supported(64, 24, 24)
+    assert not F().qkv_skinny_supported(40, 32, 32)
+
+
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("T,E,K,norm", [(1, 6, 3, False), (8, 60, 4, False), (19, 8, 2, True), (32, 130, 8, True)])
+def test_route_small_equals_router_and_permute(adt, wdt, T, E, K, norm):
+    H = 200
+    x = rnd(T, H, dtype=adt, seed=E)
+    wr = rnd(E, H, dtype=wdt, scale=0.3, seed=K)
+    wsg = rnd(H, dtype=wdt, scale=0.2, seed=9)
+    ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+    idx, w, gate, probs = F().moe_router(x, wr, wsg, K, norm, want_probs=True)
+    offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
+    for _ in range(3):                                                         # the ticket is left at zero
+        got = F().moe_route_small(x, wr, wsg, K, norm, ticket, want_probs=True)
+        for a, b in zip(got, (idx, w, gate, probs, offsets, sorted_token, inv_perm)):
+            assert torch.equal(a, b)
+        assert int(ticket.item()) == 0
+    got = F().moe_route_small(x, wr, None, K, norm, ticket)
+    assert got[2] is None and torch.equal(got[0], idx) and torch.equal(got[6], inv_perm)
+    from mini_infer_b200.ops.library import KernelError
+    with pytest.raises(KernelError, match="tokens"):
+        F().moe_route_small(rnd(F().route_small_max_tokens() + 1, H, dtype=adt), wr, wsg, K, norm, ticket)
+
+
 @pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8), (700, 9, 3),
                                    (2100, 7, 1)])
 def test_permute(T, E, K):

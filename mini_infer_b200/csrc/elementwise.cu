@@ -311,7 +311,7 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv_perm
     const int i0 = blockIdx.y * 512 + threadIdx.x;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < K; ++k) {
-        const int r = inv_perm[t * K + k];
+        const int r = inv_perm ? inv_perm[t * K + k] : t * K + k;
         const float wk = w[t * K + k];
         const float* yr = y + (int64_t)r * H;
 #pragma unroll

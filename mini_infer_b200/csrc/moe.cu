@@ -150,13 +150,13 @@ moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, co
 // Few tokens (decode): one block per weight row and group of RT_TOK tokens; the 8 warps split the
 // row, so every lane has a single round of loads in flight, and the warps' partial sums are added
 // in warp order.  The order of a dot product's additions depends on H only.
-template <typename AT, typename WT>
+template <typename AT, typename WT, int TOK>
 __device__ __forceinline__ void router_logits_small_block(const AT* __restrict__ x, const WT* __restrict__ wr,
                                                           const WT* __restrict__ wsg, float* __restrict__ z,
                                                           int T, int H, int E, int e, int t0) {
-    __shared__ float part[8][RT_TOK];
+    __shared__ float part[8][TOK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nt = min(RT_TOK, T - t0);
+    const int nt = min(TOK, T - t0);
     const int ncols = E + (wsg ? 1 : 0);
     const WT* w = e < E ? wr + (int64_t)e * H : wsg;
     constexpr int CN = RowChunk<WT>::N;
@@ -165,9 +165,9 @@ __device__ __forceinline__ void router_logits_small_block(const AT* __restrict__
     const bool vec = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                      H % L == 0;
     const int main = vec ? H : 0;
-    float acc[RT_TOK];
+    float acc[TOK];
 #pragma unroll
-    for (int j = 0; j < RT_TOK; ++j) acc[j] = 0.f;
+    for (int j = 0; j < TOK; ++j) acc[j] = 0.f;
     for (int i = threadIdx.x * L; i < main; i += 256 * L) {
         float wv[L];
 #pragma unroll
@@ -178,7 +178,7 @@ __device__ __forceinline__ void router_logits_small_block(const AT* __restrict__
             for (int k = 0; k < CN; ++k) wv[u + k] = c.v[k];
         }
 #pragma unroll
-        for (int j = 0; j < RT_TOK; ++j) {
+        for (int j = 0; j < TOK; ++j) {
             if (j < nt) {
                 float xv[L];
                 const AT* xp = x + (int64_t)(t0 + j) * H + i;
@@ -192,11 +192,11 @@ __device__ __forceinline__ void router_logits_small_block(const AT* __restrict__
     for (int i = main + threadIdx.x; i < H; i += 256) {
         const float wv = to_float(w[i]);
 #pragma unroll
-        for (int j = 0; j < RT_TOK; ++j)
+        for (int j = 0; j < TOK; ++j)
             if (j < nt) acc[j] += to_float(x[(int64_t)(t0 + j) * H + i]) * wv;
     }
 #pragma unroll
-    for (int j = 0; j < RT_TOK; ++j) {
+    for (int j = 0; j < TOK; ++j) {
         const float v = warp_sum(acc[j]);
         if (lane == 0) part[warp][j] = v;
     }
@@ -213,7 +213,7 @@ template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
 moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
                                float* __restrict__ z, int T, int H, int E) {
-    router_logits_small_block<AT, WT>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y * RT_TOK);
+    router_logits_small_block<AT, WT, RT_TOK>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y * RT_TOK);
 }
 
 // Softmax over all experts, K rounds of arg-max (lowest index among equals), weights; one warp per
@@ -335,9 +335,10 @@ moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, 
     permute_block(topk_idx, offsets, sorted_token, inv_perm, sh, N, E, K, idx_in_smem);
 }
 
-// Routing of a few tokens (decode) in one launch: every block computes one weight row's logits; the
-// block that finishes last (a ticket counter, no block waits for another) selects the experts of
-// all tokens and builds the permutation.  `ticket` is zero before the launch and is zero again after.
+// Routing of a few tokens (decode) in one launch: every block computes one logit (weight row, token);
+// the block that finishes last (a ticket counter, no block waits for another) selects the experts of
+// all tokens and, if `offsets` is given, builds the permutation.  `ticket` is zero before the launch
+// and is zero again after.
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
 moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
@@ -347,7 +348,7 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
                        int T, int H, int E, int K, int norm_topk) {
     extern __shared__ int route_sh[];  // select: [8][E] floats; then permute: [E+1] + [T*K] ints
     __shared__ bool last;
-    router_logits_small_block<AT, WT>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y * RT_TOK);
+    router_logits_small_block<AT, WT, 1>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -362,8 +363,9 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
     float* p = reinterpret_cast<float*>(route_sh) + warp * E;
     int* perm_sh = route_sh + 8 * E;
     for (int t = warp; t < T; t += 8)
-        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, p, perm_sh + E + 1, t, E, K,
-                            norm_topk);
+        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, p, offsets ? perm_sh + E + 1 : nullptr,
+                            t, E, K, norm_topk);
+    if (!offsets) return;
     __syncthreads();
     permute_block(nullptr, offsets, sorted_token, inv_perm, perm_sh, T * K, E, K, 2);
 }
@@ -561,7 +563,8 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
     return finish_launch("moe_router", 2);
 }
 
-// Router and permutation of a step of at most mi_moe_route_small_max_tokens() tokens in one launch.
+// Router and (unless `offsets` is null) permutation of a step of at most
+// mi_moe_route_small_max_tokens() tokens in one launch.
 // `ticket` is one unsigned that is zero before the first call; the kernel leaves it zero.
 int mi_moe_route_small_max_tokens() { return 4 * RT_TOK; }
 
@@ -584,7 +587,7 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
         return kBadShape;
     }
     const int ncols = E + (wsg ? 1 : 0);
-    const dim3 grid(ncols, (T + RT_TOK - 1) / RT_TOK);
+    const dim3 grid(ncols, T);
 #define MI_ROUTE_ATTR(AT, WT)                                                                             \
     if (smem > 48 * 1024)                                                                                 \
         cudaFuncSetAttribute(moe_route_small_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \

@@ -33,8 +33,10 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 // MODE 0: C[r, n] = a_r . W[e, n, :]                       (C float)
 // MODE 1: C[r, n] = silu(a_r . W[e, n, :]) * (a_r . W[e, Nout + n, :])   (C bfloat16)
 // Block = 4 warps x 16 features; grid = (ceil(Nout / 64), E).
+// Rows r < rows of this pass: source row src[r] (row0 + r without src), result row dst[r] (row0 + r
+// without dst).
 template <int MODE, int NT>
-__device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A, const int* __restrict__ gather,
+__device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A, const int* src, const int* dst,
                                             const __nv_bfloat16* __restrict__ We, void* __restrict__ C, int row0,
                                             int rows, int f0, int Nout, int Kd) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -55,8 +57,8 @@ __device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A,
     for (int j = 0; j < NT; ++j) {
         const int r = 8 * j + g;
         xv[j] = r < rows;
-        const int src = xv[j] ? (gather ? gather[row0 + r] : row0 + r) : 0;
-        xr[j] = reinterpret_cast<const uint4*>(A + (int64_t)src * Kd) + t;
+        const int from = xv[j] ? (src ? src[r] : row0 + r) : 0;
+        xr[j] = reinterpret_cast<const uint4*>(A + (int64_t)from * Kd) + t;
     }
     float acc[NT][2][4];   // [tile][gate|up][fragment]
 #pragma unroll
@@ -92,7 +94,7 @@ __device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A,
             const int f = f0 + g + ((i & 2) ? 8 : 0);
             const int r = 8 * j + 2 * t + (i & 1);
             if (f < Nout && r < rows) {
-                const int64_t o = (int64_t)(row0 + r) * Nout + f;
+                const int64_t o = (int64_t)(dst ? dst[r] : row0 + r) * Nout + f;
                 if (MODE == 1) {
                     const float gv = acc[j][0][i];
                     reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * acc[j][1][i]);
@@ -116,10 +118,56 @@ grouped_gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __res
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     const __nv_bfloat16* We = W + (int64_t)e * wrows * Kd;
     if (cnt <= 8) {
-        skinny_pass<MODE, 1>(A, gather, We, C, b0, cnt, f0, Nout, Kd);
+        skinny_pass<MODE, 1>(A, gather ? gather + b0 : nullptr, nullptr, We, C, b0, cnt, f0, Nout, Kd);
     } else {
         for (int r0 = 0; r0 < cnt; r0 += 16)
-            skinny_pass<MODE, 2>(A, gather, We, C, b0 + r0, min(16, cnt - r0), f0, Nout, Kd);
+            skinny_pass<MODE, 2>(A, gather ? gather + b0 + r0 : nullptr, nullptr, We, C, b0 + r0,
+                                 min(16, cnt - r0), f0, Nout, Kd);
+    }
+}
+
+// The same product without a permutation, for a step of at most PAIR_MAX_TOKENS tokens: the rows of
+// expert e are the (token, slot) pairs i = t * K + k with topk_idx[i] == e, found by one warp with
+// ballots, in ascending i.  Result rows are indexed by pair.  src_is_token: the source row of pair i
+// is token i / K (first product); otherwise it is row i (second product).
+constexpr int PAIR_MAX_TOKENS = 32;
+
+template <int MODE>
+__global__ void __launch_bounds__(128)
+grouped_gemm_skinny_pairs_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ topk_idx,
+                                 const __nv_bfloat16* __restrict__ W, void* __restrict__ C, int n_pairs, int K,
+                                 int src_is_token, int Nout, int Kd) {
+    __shared__ int pair_sh[PAIR_MAX_TOKENS], from_sh[PAIR_MAX_TOKENS];
+    __shared__ int cnt_sh;
+    const int e = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        int run = 0;
+        for (int base = 0; base < n_pairs; base += 32) {
+            const int i = base + lane;
+            const bool mine = i < n_pairs && topk_idx[i] == e;
+            const unsigned bal = __ballot_sync(0xffffffffu, mine);
+            const int at = run + __popc(bal & ((1u << lane) - 1u));
+            if (mine && at < PAIR_MAX_TOKENS) {
+                pair_sh[at] = i;
+                from_sh[at] = src_is_token ? i / K : i;
+            }
+            run += __popc(bal);
+        }
+        if (lane == 0) cnt_sh = min(run, PAIR_MAX_TOKENS);
+    }
+    __syncthreads();
+    const int cnt = cnt_sh;
+    if (cnt <= 0) return;
+    const int f0 = blockIdx.x * 64 + warp * 16;
+    if (f0 >= Nout) return;
+    const int wrows = MODE == 1 ? 2 * Nout : Nout;
+    const __nv_bfloat16* We = W + (int64_t)e * wrows * Kd;
+    if (cnt <= 8) {
+        skinny_pass<MODE, 1>(A, from_sh, pair_sh, We, C, 0, cnt, f0, Nout, Kd);
+    } else {
+        for (int r0 = 0; r0 < cnt; r0 += 16)
+            skinny_pass<MODE, 2>(A, from_sh + r0, pair_sh + r0, We, C, 0, min(16, cnt - r0), f0, Nout, Kd);
     }
 }
 
@@ -333,6 +381,36 @@ int mi_grouped_gemm_skinny(const void* A, const int* gather, const void* W, cons
     return finish_launch("grouped_gemm_skinny");
 }
 
+
+// Largest step (in tokens) of the pair-indexed grouped product.
+int mi_grouped_gemm_skinny_pairs_max_tokens() { return PAIR_MAX_TOKENS; }
+
+// The decode-sized grouped product without a permutation.  topk_idx [T*K]: expert of pair t*K+k (each
+// token names an expert at most once).  mode 1: A [T, Kd], C bfloat16 [T*K, Nout] = SwiGLU pair of
+// token t's row under the pair's expert; mode 0: A [T*K, Kd] indexed by pair, C float [T*K, Nout].
+int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void* W, void* C, int T, int K, int E,
+                                 int Nout, int Kd, int mode, cudaStream_t stream) {
+    if (!mi_grouped_gemm_skinny_supported(Kd)) {
+        set_last_error("grouped product (decode): inner size %d is not a multiple of 32", Kd);
+        return kBadShape;
+    }
+    if (T < 1 || T > PAIR_MAX_TOKENS || K < 1) {
+        set_last_error("grouped product (decode, by pair): %d tokens, takes 1..%d", T, PAIR_MAX_TOKENS);
+        return kBadShape;
+    }
+    if (E < 1 || E > 65535) {
+        set_last_error("grouped product (decode): %d experts exceed the grid limit", E);
+        return kBadShape;
+    }
+    const dim3 grid((Nout + 63) / 64, E);
+    if (mode == 1)
+        grouped_gemm_skinny_pairs_kernel<1><<<grid, 128, 0, stream>>>(
+            (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 1, Nout, Kd);
+    else
+        grouped_gemm_skinny_pairs_kernel<0><<<grid, 128, 0, stream>>>(
+            (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 0, Nout, Kd);
+    return finish_launch("grouped_gemm_skinny_pairs");
+}
 
 // Largest step (in rows) that the dense decode-sized product takes.
 int mi_dense_skinny_max_rows() { return 32; }

@@ -139,10 +139,11 @@ def swiglu(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor
     return out
 
 
-def moe_combine(y: torch.Tensor, inv_perm: torch.Tensor, weights: torch.Tensor,
+def moe_combine(y: torch.Tensor, inv_perm: Optional[torch.Tensor], weights: torch.Tensor,
                 shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out[t] = sum_k weights[t,k] * y[inv_perm[t,k]] + gate[t] * shared[t]`` (float32)."""
+    """``out[t] = sum_k weights[t,k] * y[inv_perm[t,k]] + gate[t] * shared[t]`` (float32);
+    without ``inv_perm`` the rows of ``y`` are indexed by pair, ``y[t*K + k]``."""
     T, K = weights.shape
     _chk(y, "moe_combine y", F32, (T * K, None))
     H = y.shape[1]
@@ -310,12 +311,14 @@ def route_small_max_tokens() -> int:
 
 
 def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
-                    norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False):
-    """:func:`moe_router` and :func:`moe_permute` of a step of a few tokens in one launch.
+                    norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False, permute: bool = True):
+    """:func:`moe_router` and (with ``permute``) :func:`moe_permute` of a step of a few tokens in
+    one launch.
 
     ``ticket`` is one int32 that is zero before the first call and belongs to the caller (the
     kernel leaves it zero); calls that share a ticket must not overlap.  Returns
-    ``(idx, w, gate, probs, offsets, sorted_token, inv_perm)``.
+    ``(idx, w, gate, probs, offsets, sorted_token, inv_perm)``, the last three None without
+    ``permute``.
     """
     _chk(x, "moe_route_small x")
     T, H = x.shape
@@ -332,9 +335,11 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
     gate = torch.empty(T, dtype=F32, device=dev) if shared_gate_w is not None else None
     probs = torch.empty(T, E, dtype=F32, device=dev) if want_probs else None
     z = torch.empty(T, E + 1, dtype=F32, device=dev)
-    offsets = torch.empty(E + 1, dtype=I32, device=dev)
-    sorted_token = torch.empty(T * top_k, dtype=I32, device=dev)
-    inv_perm = torch.empty(T * top_k, dtype=I32, device=dev)
+    offsets = sorted_token = inv_perm = None
+    if permute:
+        offsets = torch.empty(E + 1, dtype=I32, device=dev)
+        sorted_token = torch.empty(T * top_k, dtype=I32, device=dev)
+        inv_perm = torch.empty(T * top_k, dtype=I32, device=dev)
     check(library().mi_moe_route_small(
         _ptr(x), _code(x, "moe_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
         _code(router_w, "moe_route_small weight"), _ptr(z), _ptr(ticket), _ptr(idx), _ptr(w), _ptr(gate), _ptr(probs),
@@ -452,6 +457,32 @@ def qkv_skinny(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor
                                   _ptr(slot_mapping), _ptr(q), _ptr(k_cache), _ptr(v_cache), T, Kd, nh, nkv, d,
                                   page_size, _stream()), "qkv_skinny")
     return q
+
+
+def skinny_pairs_max_tokens() -> int:
+    return int(library().mi_grouped_gemm_skinny_pairs_max_tokens())
+
+
+def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.Tensor,
+                              swiglu_pair: bool) -> torch.Tensor:
+    """The decode-sized grouped product without a permutation: row ``t*K + k`` of the result
+    belongs to the pair (token t, slot k) and is computed under expert ``topk_idx[t, k]``.
+
+    With ``swiglu_pair`` ``a`` is ``[T, Kd]`` (a token's row serves its K pairs) and the result is
+    the bfloat16 activation ``[T*K, Nout]``; without, ``a`` is ``[T*K, Kd]`` indexed by pair and
+    the result float32.
+    """
+    _chk(topk_idx, "grouped_gemm_skinny_pairs idx", I32)
+    T, K = topk_idx.shape
+    _chk(a, "grouped_gemm_skinny_pairs a", BF16, (T if swiglu_pair else T * K, None))
+    Kd = a.shape[1]
+    _chk(w, "grouped_gemm_skinny_pairs w", BF16, (None, None, Kd))
+    E, wrows, _ = w.shape
+    nout = wrows // 2 if swiglu_pair else wrows
+    out = torch.empty(T * K, nout, dtype=BF16 if swiglu_pair else F32, device=a.device)
+    check(library().mi_grouped_gemm_skinny_pairs(_ptr(a), _ptr(topk_idx), _ptr(w), _ptr(out), T, K, E, nout, Kd,
+                                                 1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny_pairs")
+    return out
 
 
 def grouped_gemm_tc_supported(kd: int, nout: int) -> bool:

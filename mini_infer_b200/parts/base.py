@@ -272,11 +272,23 @@ class BuiltLayer:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.block]
 
 
+SKINNY_MAX_TOKENS = 8   # steps up to this size run the dense products on the engine's own decode kernel
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+    """``silu(x @ w_gate.T) * (x @ w_up.T)`` in the activation dtype; ``w_gate_up`` holds the gate
+    rows then the up rows (src/layers/mlp.cpp:255-279 runs two products and an elementwise kernel)."""
+    from ..ops import functional as F
+    if x.is_cuda and x.shape[0] <= SKINNY_MAX_TOKENS and F.dense_skinny_takes(x, w_gate_up):
+        return F.dense_skinny(x, w_gate_up, swiglu_pair=True)
+    return F.swiglu(linear(x, w_gate_up, act_dtype))
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """``x @ w.T`` through the library product the reference also uses for every dense
     projection (cuBLAS, src/layers/attention.cpp:45-55, src/layers/mlp.cpp:120-130),
     accumulating in float32; ``w`` is ``[out, in]`` as stored in checkpoints."""
-    if out_dtype == torch.float32 and x.is_cuda and x.shape[0] <= 8:
+    if out_dtype == torch.float32 and x.is_cuda and x.shape[0] <= SKINNY_MAX_TOKENS:
         from ..ops import functional as F
         if F.dense_skinny_takes(x, w):
             return F.dense_skinny(x, w)

@@ -15,7 +15,7 @@ import torch
 
 from ..config.registry import register_part
 from ..ops import functional as F
-from .base import FeedForward, Runtime, StepContext, TensorDecl, linear
+from .base import FeedForward, Runtime, StepContext, TensorDecl, linear, linear_swiglu
 
 
 class SwiGLUMLP(FeedForward):
@@ -45,8 +45,7 @@ class SwiGLUMLP(FeedForward):
         self.w_down = m(tensors[p + "down_proj.weight"], dev)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = linear(x, self.w_gate_up, self.rt.act)
-        return linear(F.swiglu(gu), self.w_down, torch.float32)
+        return linear(linear_swiglu(x, self.w_gate_up, self.rt.act), self.w_down, torch.float32)
 
 
 class SparseMoE(FeedForward):
@@ -120,53 +119,70 @@ class SparseMoE(FeedForward):
         # the one-launch routing of decode-sized steps counts its blocks in this word
         self._route_ticket = torch.zeros(1, dtype=torch.int32, device=dev)
         self._route_small_max = F.route_small_max_tokens()
+        self._pairs_max = min(self._route_small_max, F.skinny_pairs_max_tokens())
         self._tc = (rt.act == torch.bfloat16 and F.grouped_gemm_tc_supported(self.H, self.mI)
                     and F.grouped_gemm_tc_supported(self.mI, self.H) and self.H % 8 == 0)
         self._skinny = (rt.act == torch.bfloat16 and F.grouped_gemm_skinny_supported(self.H)
                         and F.grouped_gemm_skinny_supported(self.mI))
 
     def _shared_expert(self, x: torch.Tensor) -> torch.Tensor:
-        gu = linear(x, self.w_shared_gate_up, self.rt.act)
-        return linear(F.swiglu(gu), self.w_shared_down, torch.float32)
+        return linear(linear_swiglu(x, self.w_shared_gate_up, self.rt.act), self.w_shared_down, torch.float32)
+
+    def _fork_shared_expert(self, x: torch.Tensor):
+        """Start the shared expert on a second stream (decode-sized steps: every kernel is short, so it
+        runs beside the routed experts).  The one-launch routing of the smallest steps is a chain
+        of short dependent loads that a concurrent weight stream slows down, so there the fork
+        comes after it; larger steps fork first."""
+        main = torch.cuda.current_stream()
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=x.device)
+        side = self._side_stream
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            shared = self._shared_expert(x)
+        shared.record_stream(main)
+        return side, shared
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = x.shape[0]
-        shared = None
-        side = None
-        if self.sI > 0 and T <= self.OVERLAP_MAX_TOKENS:
-            # decode-sized step: every kernel is short, so the shared expert runs beside the routed
-            # path on a second stream (fork here, join before the combine)
-            main = torch.cuda.current_stream()
-            if self._side_stream is None:
-                self._side_stream = torch.cuda.Stream(device=x.device)
-            side = self._side_stream
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                shared = self._shared_expert(x)
-            shared.record_stream(main)
-        if T <= self._route_small_max:
-            idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
+        shared = side = inv_perm = None
+        overlap = self.sI > 0 and T <= self.OVERLAP_MAX_TOKENS
+        n = T * self.K
+        if self._skinny and T <= self._pairs_max:
+            # decode-sized step: routing in one launch, no permutation; every used expert's weights
+            # are read once and result rows are indexed by (token, slot) pair
+            idx, w, gate, probs, _, _, _ = F.moe_route_small(
                 x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                want_probs=self.keep_routing)
+                want_probs=self.keep_routing, permute=False)
+            if overlap:
+                side, shared = self._fork_shared_expert(x)
+            act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True)
+            y = F.grouped_gemm_skinny_pairs(act, idx, self.w_down, False)
         else:
-            idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
-                                               want_probs=self.keep_routing)
-            offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
+            if overlap:
+                side, shared = self._fork_shared_expert(x)
+            if T <= self._route_small_max:
+                idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
+                    x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
+                    want_probs=self.keep_routing)
+            else:
+                idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
+                                                   want_probs=self.keep_routing)
+                offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
+            if self._skinny and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
+                # a few rows per expert: bound by reading each used expert once
+                act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
+                y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
+            elif self._tc:
+                # many rows per expert: tensor-core tiles over the rows gathered into expert order
+                xs = F.gather_rows(x, sorted_token)
+                act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True)
+                y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
+            else:
+                act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
+                y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         if self.keep_routing:
             self.last_routing = (idx, w, probs)
-        n = T * self.K
-        if self._skinny and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
-            # a few rows per expert: bound by reading each used expert once
-            act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
-            y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
-        elif self._tc:
-            # many rows per expert: tensor-core tiles over the rows gathered into expert order
-            xs = F.gather_rows(x, sorted_token)
-            act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True)
-            y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
-        else:
-            act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
-            y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         elif self.sI > 0:

@@ -439,6 +439,9 @@ def test_route_small_equals_router_and_permute(adt, wdt, T, E, K, norm):
         assert int(ticket.item()) == 0
     got = F().moe_route_small(x, wr, None, K, norm, ticket)
     assert got[2] is None and torch.equal(got[0], idx) and torch.equal(got[6], inv_perm)
+    got = F().moe_route_small(x, wr, wsg, K, norm, ticket, permute=False)
+    assert got[4] is None and torch.equal(got[0], idx) and torch.equal(got[1], w) and torch.equal(got[2], gate)
+    assert int(ticket.item()) == 0
     from mini_infer_b200.ops.library import KernelError
     with pytest.raises(KernelError, match="tokens"):
         F().moe_route_small(rnd(F().route_small_max_tokens() + 1, H, dtype=adt), wr, wsg, K, norm, ticket)
@@ -509,6 +512,31 @@ def test_grouped_gemm_skinny_equals_plain(T, E, K, H, I):
     from mini_infer_b200.ops.library import KernelError
     with pytest.raises(KernelError, match="multiple of 32"):
         F().grouped_gemm_skinny(x[:, :48].contiguous(), sorted_token, wgu[:, :, :48].contiguous(), offsets, T * K, True)
+
+
+@pytest.mark.parametrize("T,E,K,H,I", [(1, 8, 2, 64, 32), (8, 60, 4, 256, 96), (32, 12, 4, 128, 160), (19, 6, 3, 96, 64),
+                                       (32, 5, 5, 64, 64)])
+def test_grouped_gemm_skinny_by_pair_equals_sorted(T, E, K, H, I):
+    g = torch.Generator().manual_seed(E + T)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
+    x = rnd(T, H, dtype=torch.bfloat16, seed=1)
+    w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.2, seed=2)
+    w2 = rnd(E, H, I, dtype=torch.bfloat16, scale=0.2, seed=3)
+    act_sorted = F().grouped_gemm_skinny(x, sorted_token, w1, offsets, T * K, True)
+    y_sorted = F().grouped_gemm_skinny(act_sorted, None, w2, offsets, T * K, False)
+    act = F().grouped_gemm_skinny_pairs(x, idx, w1, True)
+    y = F().grouped_gemm_skinny_pairs(act, idx, w2, False)
+    # the same sums in the same order, only the rows stand elsewhere
+    assert torch.equal(act, act_sorted[inv_perm.long()])
+    assert torch.equal(y, y_sorted[inv_perm.long()])
+    wts = rnd(T, K, seed=4).abs()
+    assert torch.equal(F().moe_combine(y, None, wts, None, None),
+                       F().moe_combine(y_sorted, inv_perm, wts, None, None))
+    from mini_infer_b200.ops.library import KernelError
+    with pytest.raises(KernelError, match="tokens"):
+        F().grouped_gemm_skinny_pairs(rnd(33, H, dtype=torch.bfloat16), torch.zeros(33, K, dtype=torch.int32, device=DEV),
+                                      w1, True)
 
 
 @pytest.mark.parametrize("T,E,K,H,I", [(300, 6, 3, 128, 64), (2048, 60, 4, 256, 192), (1000, 12, 2, 192, 320),

@@ -47,6 +47,7 @@ class _Request:
     slot: int
     num_tokens: int = 0                       # tokens whose keys are in the cache
     reserved: int = 0                         # tokens reserved beyond num_tokens for the running step
+    ahead: int = 0                            # tokens reserved for a step launched before it was decided
     tables: List[List[int]] = field(default_factory=list)   # per group: page id by logical index
 
 
@@ -114,6 +115,8 @@ class CacheManager:
         if n_new < 1:
             raise ValueError("CacheManager.reserve: a portion has at least one token")
         r = self._req[rid]
+        if r.ahead:
+            raise ValueError("CacheManager.reserve: a step launched ahead is unsettled (adopt or cancel it)")
         need = self.pages_needed(rid, n_new)
         for g, n in enumerate(need):
             if n > self.pools[g].num_free:
@@ -125,8 +128,29 @@ class CacheManager:
         r.reserved += n_new
         return start
 
+    def reserve_ahead(self, rid: Hashable, n_new: int) -> int:
+        """:meth:`reserve` for a step that is launched before the scheduler has decided it (its
+        tokens are still being sampled).  The pages are held, but :meth:`pages_needed` keeps
+        answering for the committed tokens, so planning the very same step finds its pages in
+        place.  Settled by :meth:`adopt_ahead` (then :meth:`commit`) or :meth:`cancel`."""
+        r = self._req[rid]
+        if r.reserved or r.ahead:
+            raise ValueError("CacheManager.reserve_ahead: another step of this request is unsettled")
+        start = self.reserve(rid, n_new)
+        r.reserved, r.ahead = 0, n_new
+        return start
+
+    def adopt_ahead(self, rid: Hashable) -> None:
+        """The step launched ahead is the one that was decided: its tokens count as reserved."""
+        r = self._req[rid]
+        r.reserved, r.ahead = r.ahead, 0
+
+    def has_ahead(self, rid: Hashable) -> bool:
+        return rid in self._req and self._req[rid].ahead > 0
+
     def cancel(self, rid: Hashable) -> None:
-        """Undo :meth:`reserve` calls that no step followed: pages beyond the cached tokens go back."""
+        """Undo :meth:`reserve` calls that no step followed (and a step launched ahead that was not
+        adopted): pages beyond the cached tokens go back."""
         r = self._req[rid]
         keep = -(-r.num_tokens // self.page_size)
         for g, table in enumerate(r.tables):
@@ -135,6 +159,7 @@ class CacheManager:
                 if p >= 0:
                     self.pools[g].free(p)
         r.reserved = 0
+        r.ahead = 0
 
     def commit(self, rid: Hashable) -> None:
         """The step that wrote the reserved tokens is done: count them, and give back the
@@ -156,7 +181,7 @@ class CacheManager:
         """Forget the tokens beyond ``num_tokens`` (pages past the new end are given back).
         Counterpart of the reference's ``rollback`` (src/scheduler/paged_kv_cache.cpp:82-107)."""
         r = self._req[rid]
-        if r.reserved:
+        if r.reserved or r.ahead:
             raise ValueError("CacheManager.truncate: a step is in flight")
         if not 0 <= num_tokens <= r.num_tokens:
             raise ValueError("CacheManager.truncate: cannot grow")

@@ -21,6 +21,7 @@ from .loading import load_model
 from .model import Model
 from .request import Request
 from .scheduler import IterationStats, Scheduler, SchedulerConfig
+from ..cache.pages import OutOfPages
 from .step import ModelRunner, StepEntry
 
 
@@ -35,26 +36,70 @@ class GenerationOutput:
 
 
 class GPUExecutor:
-    """What the scheduler drives: the model runner and the sampler."""
+    """What the scheduler drives: the model runner and the sampler.
+
+    When the scheduler says that the next step will decode one token for exactly the requests
+    sampled now (unless a stop token ends one), that step is launched *ahead*: it takes its token
+    ids from the sampler's device buffer, so the device goes on while the host fetches the tokens
+    and plans.  If the next call asks for that very step, it is adopted; anything else (a request
+    ended, was added or preempted) drops it, and the step decided instead overwrites what it wrote.
+    """
+
+    lookahead_capable = True
 
     def __init__(self, runner: ModelRunner, sampler: Sampler):
         self.runner = runner
         self.sampler = sampler
         self.cache = runner.cache
+        self._ahead = None          # (request ids, sampler handle, token ids the step was fed | None)
+        self.steps_adopted = 0
+        self.steps_dropped = 0
+
+    def _drop_ahead(self) -> None:
+        if self._ahead is not None:
+            self.runner.drop_ahead(self._ahead[0])
+            self._ahead = None
+            self.steps_dropped += 1
 
     def add_request(self, rid: Hashable) -> None:
+        self._drop_ahead()
         self.runner.add_request(rid)
 
     def release(self, rid: Hashable) -> None:
+        self._drop_ahead()
         self.runner.release(rid)
 
-    def run(self, entries: Sequence[StepEntry], sample_for: Sequence[Request]) -> Dict[Hashable, int]:
-        res = self.runner.step(entries)
-        if not sample_for:
-            return {}
-        assert [rid for rid, _ in res.index] == [r.rid for r in sample_for]
-        toks = self.sampler.sample(res.logits, [r.params for r in sample_for], [r.stream for r in sample_for],
-                                   [len(r.generated) for r in sample_for])
+    def run(self, entries: Sequence[StepEntry], sample_for: Sequence[Request],
+            lookahead: bool = False) -> Dict[Hashable, int]:
+        rids = [r.rid for r in sample_for]
+        ahead = self._ahead
+        if ahead is not None and ahead[0] == rids and len(entries) == len(rids) and all(
+                e.rid == rid and list(e.tokens) == [tok] and list(e.want) == [0]
+                for e, rid, tok in zip(entries, rids, ahead[2])):
+            self._ahead = None
+            self.runner.adopt_ahead(rids)
+            self.steps_adopted += 1
+            handle = ahead[1]
+        else:
+            self._drop_ahead()
+            res = self.runner.step(entries)
+            if not sample_for:
+                return {}
+            assert [rid for rid, _ in res.index] == rids
+            handle = self.sampler.launch(res.logits, [r.params for r in sample_for],
+                                         [r.stream for r in sample_for], [len(r.generated) for r in sample_for])
+        if lookahead and self.runner.can_step_ahead(rids):
+            try:
+                logits = self.runner.step_ahead(rids, self.sampler.device_tokens(handle))
+            except OutOfPages:
+                pass                # the scheduler decides what makes room
+            else:
+                nxt = self.sampler.launch(logits, [r.params for r in sample_for], [r.stream for r in sample_for],
+                                          [len(r.generated) + 1 for r in sample_for])
+                self._ahead = (rids, nxt, None)
+        toks = self.sampler.fetch(handle)
+        if self._ahead is not None:
+            self._ahead = (rids, self._ahead[1], toks)
         return {r.rid: t for r, t in zip(sample_for, toks)}
 
 

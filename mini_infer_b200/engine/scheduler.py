@@ -220,8 +220,15 @@ class Scheduler:
                     stats.decode_tokens += 1
                 else:
                     stats.prefill_tokens += n
+            # If nothing but a stop token can change the batch, the next step decodes one token for
+            # exactly these requests: an executor that can do so launches it ahead.
+            ahead = (getattr(self.ex, "lookahead_capable", False) and len(sample_for) == len(self.running)
+                     and not self.waiting
+                     and all(len(r.generated) + 1 < r.params.max_new_tokens
+                             and r.num_tokens + 1 < self.cfg.max_context for r in sample_for))
             try:
-                tokens = self.ex.run(entries, sample_for)
+                tokens = self.ex.run(entries, sample_for, lookahead=True) if ahead \
+                    else self.ex.run(entries, sample_for)
             except OutOfPages:
                 # cannot happen if plan() counted right; treat as capacity failure of the newest request
                 victim = max((r for r, _ in plan), key=lambda r: r.admit_order)

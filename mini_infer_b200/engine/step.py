@@ -176,14 +176,20 @@ class ModelRunner:
         if total > self.max_tokens:
             raise StepError(f"step: {total} tokens exceed the budget {self.max_tokens}")
 
-    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, Optional[torch.Tensor], List]:
-        """Validate, reserve pages (all entries or none), stage and upload the metadata."""
+    def prepare(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+                ahead: bool = False) -> Tuple[StepContext, Optional[torch.Tensor], List]:
+        """Validate, reserve pages (all entries or none), stage and upload the metadata.
+
+        With ``device_tokens`` (int32, one per row, on the device) the token ids of ``entries`` are
+        placeholders and the step reads the given ones; ``ahead`` reserves through
+        :meth:`CacheManager.reserve_ahead`."""
         self.validate(entries)
         starts = []
         done = []
         try:
             for e in entries:
-                starts.append(self.cache.reserve(e.rid, len(e.tokens)))
+                starts.append(self.cache.reserve_ahead(e.rid, len(e.tokens)) if ahead
+                              else self.cache.reserve(e.rid, len(e.tokens)))
                 done.append(e.rid)
         except OutOfPages:
             for rid in done:
@@ -237,6 +243,8 @@ class ModelRunner:
         self._dev.copy_(self._host, non_blocking=True)
         self._copied.record()
         d = self._dview
+        if device_tokens is not None:
+            d("token_ids", T).copy_(device_tokens[:T], non_blocking=True)
         views = []
         for g in range(len(self.model.kv_groups)):
             k, v = self.kv_tensors[g]
@@ -303,3 +311,38 @@ class ModelRunner:
         for e in entries:
             self.cache.commit(e.rid)
         return StepResult(logits, index, ctx.num_tokens)
+
+    # ------------------------------------------------------------------ #
+    # a decode step launched ahead of the scheduler's decision
+    # ------------------------------------------------------------------ #
+    def can_step_ahead(self, rids: Sequence[Hashable]) -> bool:
+        """A step of one token per request can be launched ahead only as a graph replay."""
+        return self._graph_eligible([StepEntry(r, [0], [0]) for r in rids])
+
+    @torch.no_grad()
+    def step_ahead(self, rids: Sequence[Hashable], device_tokens: torch.Tensor) -> torch.Tensor:
+        """Launch the decode step that feeds request ``rids[b]`` the token ``device_tokens[b]``
+        (still being computed on the device) and return its logits ``[B, V]``.  Pages are held
+        through :meth:`CacheManager.reserve_ahead`; the caller settles the step with
+        :meth:`adopt_ahead` or :meth:`drop_ahead`.  Raises :class:`OutOfPages` and changes nothing
+        if a request cannot grow."""
+        entries = [StepEntry(r, [0], [0]) for r in rids]
+        ctx, logit_rows, _ = self.prepare(entries, device_tokens=device_tokens, ahead=True)
+        try:
+            return self._decode_with_graph(ctx, logit_rows)
+        except Exception:
+            self.drop_ahead(rids)
+            raise
+
+    def adopt_ahead(self, rids: Sequence[Hashable]) -> None:
+        """The step launched ahead was the one decided: its tokens are in the cache."""
+        for r in rids:
+            self.cache.adopt_ahead(r)
+            self.cache.commit(r)
+
+    def drop_ahead(self, rids: Sequence[Hashable]) -> None:
+        """The step launched ahead is void (what it wrote lies beyond every request's cached tokens
+        and is overwritten by the step that is decided instead)."""
+        for r in rids:
+            if self.cache.has_ahead(r):
+                self.cache.cancel(r)

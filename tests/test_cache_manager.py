@@ -117,6 +117,48 @@ def test_window_gives_pages_back():
     assert m.free_pages() == [16, 4]
 
 
+def test_a_step_launched_ahead_holds_pages_without_changing_what_planning_sees():
+    m = CacheManager([KVGroupSpec(1, 8, 0, (0,))], [3], 4, 2)
+    m.add_request("a")
+    assert m.reserve("a", 4) == 0
+    m.commit("a")                                   # 4 tokens: one full page
+    assert m.reserve_ahead("a", 1) == 4             # the next token needs a second page
+    assert m.free_pages() == [1] and m.has_ahead("a")
+    assert m.pages_needed("a", 1) == [0]            # planning the same token finds its page in place
+    with pytest.raises(ValueError, match="unsettled"):
+        m.reserve("a", 1)
+    with pytest.raises(ValueError, match="unsettled"):
+        m.reserve_ahead("a", 1)
+    with pytest.raises(ValueError, match="in flight"):
+        m.truncate("a", 2)
+    m.check_invariants()
+    m.adopt_ahead("a")
+    m.commit("a")
+    assert m.num_tokens("a") == 5 and not m.has_ahead("a") and m.free_pages() == [1]
+    assert m.reserve_ahead("a", 1) == 5             # same page, nothing taken
+    assert m.free_pages() == [1]
+    m.cancel("a")                                   # dropped: nothing lost, nothing counted
+    assert m.num_tokens("a") == 5 and not m.has_ahead("a") and m.free_pages() == [1]
+    for _ in range(3):
+        m.reserve("a", 1)
+        m.commit("a")                               # 8 tokens: two full pages
+    m.reserve_ahead("a", 1)
+    assert m.free_pages() == [0]
+    m.cancel("a")                                   # the page taken ahead goes back
+    assert m.free_pages() == [1]
+    m.reserve_ahead("a", 1)
+    m.release("a")                                  # a request that ends gives back that page too
+    assert m.free_pages() == [3]
+    m.check_invariants()
+    m.add_request("b")
+    m.reserve("b", 12)
+    m.commit("b")
+    with pytest.raises(OutOfPages):
+        m.reserve_ahead("b", 1)
+    assert not m.has_ahead("b") and m.free_pages() == [0]
+    m.check_invariants()
+
+
 def test_errors():
     m = _mgr()
     m.add_request("a")

@@ -91,6 +91,39 @@ def test_top_p_and_stop_token(folders):
     assert o.token_ids == gen[:first + 1] and o.finish_reason == "stop"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(folders, dtype):
+    """The executor launches the next decode step before the host has the tokens of this one; with
+    that switched off the tokens are the same, bit for bit, for greedy and sampled requests, and a
+    stop token drops the step launched beside it."""
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    folder, cfg, w = folders["A"]
+    prompts = [tiny.pick_tokens(cfg, w, n, 3 * n) for n in (6, 19, 11)]
+    params = [SamplingParams(greedy=True, max_new_tokens=14),
+              SamplingParams(greedy=False, temperature=0.9, top_p=0.8, seed=5, max_new_tokens=9),
+              SamplingParams(greedy=False, temperature=1.3, top_p=1.0, seed=6, max_new_tokens=17)]
+    llm = LLM(folder, dtype=dtype, max_seq_len=128, max_running=4, page_size=4)
+    ahead = llm.generate(prompts, params)
+    assert llm.executor.steps_adopted >= 10
+    llm.executor.lookahead_capable = False
+    adopted = llm.executor.steps_adopted
+    plain = llm.generate(prompts, params)
+    assert llm.executor.steps_adopted == adopted
+    assert [o.token_ids for o in ahead] == [o.token_ids for o in plain]
+    llm.executor.lookahead_capable = True
+    stop = ahead[0].token_ids[5]
+    first = ahead[0].token_ids.index(stop)
+    params[0] = SamplingParams(greedy=True, max_new_tokens=14, stop_token_ids=(stop,))
+    dropped = llm.executor.steps_dropped
+    outs = llm.generate(prompts, params)
+    assert outs[0].token_ids == ahead[0].token_ids[:first + 1] and outs[0].finish_reason == "stop"
+    assert [o.token_ids for o in outs[1:]] == [o.token_ids for o in ahead[1:]]
+    assert llm.executor.steps_dropped > dropped
+    assert llm.runner.cache.used_pages() == [0]
+    llm.runner.cache.check_invariants()
+
+
 @pytest.mark.parametrize("dtype,new_tokens,margin", [("float32", 20, 1e-4), ("bfloat16", 6, 0.02)])
 def test_preemption_recomputes_the_same_tokens(folders, dtype, new_tokens, margin):
     """So few pages that decoding requests are preempted and recomputed; tokens must not change.

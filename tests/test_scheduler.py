@@ -3,7 +3,7 @@ portions, decode first, finishing, exact max_new_tokens, and what happens when p
 
 import pytest
 
-from mini_infer_b200.cache import CacheManager, KVGroupSpec
+from mini_infer_b200.cache import CacheManager, KVGroupSpec, OutOfPages
 from mini_infer_b200.engine.request import Request
 from mini_infer_b200.engine.scheduler import Scheduler, SchedulerConfig
 from mini_infer_b200.sampling import SamplingParams
@@ -155,3 +155,100 @@ def test_empty_prompt_is_refused():
         Request("x", [], SamplingParams())
     with pytest.raises(ValueError):
         SamplingParams(max_new_tokens=0)
+
+
+class AheadExecutor(ScriptedExecutor):
+    """The scripted executor with the look-ahead protocol of the real one: when told so, it
+    'launches' the next decode step before returning (reserving its pages ahead) and adopts or drops
+    it at the next call."""
+
+    lookahead_capable = True
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.ahead = None
+        self.adopted = self.dropped = self.hints = 0
+
+    def _drop(self):
+        if self.ahead is not None:
+            for rid in self.ahead[0]:
+                if self.cache.has_ahead(rid):
+                    self.cache.cancel(rid)
+            self.ahead = None
+            self.dropped += 1
+
+    def add_request(self, rid):
+        self._drop()
+        super().add_request(rid)
+
+    def release(self, rid):
+        self._drop()
+        super().release(rid)
+
+    def _token(self, rid):
+        return (sum(self.history[rid]) * 7 + len(self.history[rid])) % self.vocab
+
+    def run(self, entries, sample_for, lookahead=False):
+        rids = [r.rid for r in sample_for]
+        self.hints += bool(lookahead)
+        if self.ahead is not None and self.ahead[0] == rids and len(entries) == len(rids) and all(
+                e.rid == rid and list(e.tokens) == [t] and list(e.want) == [0]
+                for e, rid, t in zip(entries, rids, self.ahead[1])):
+            self.batches.append([(e.rid, 1, [0]) for e in entries])
+            for e in entries:
+                self.cache.adopt_ahead(e.rid)
+                self.cache.commit(e.rid)
+                self.history[e.rid].extend(e.tokens)
+            self.ahead = None
+            self.adopted += 1
+            out = {rid: self._token(rid) for rid in rids}
+        else:
+            self._drop()
+            out = super().run(entries, sample_for)
+        if lookahead:
+            try:
+                done = []
+                for rid in rids:
+                    self.cache.reserve_ahead(rid, 1)
+                    done.append(rid)
+                self.ahead = (rids, [out[rid] for rid in rids])
+            except OutOfPages:
+                for rid in done:
+                    self.cache.cancel(rid)
+        self.cache.check_invariants()
+        return out
+
+
+def test_steps_launched_ahead_are_adopted_until_a_request_ends():
+    ex = AheadExecutor(num_pages=32)
+    a = Request("a", [1, 2, 3], SamplingParams(max_new_tokens=9))
+    b = Request("b", [4, 5], SamplingParams(max_new_tokens=5))
+    s, done = run(ex, SchedulerConfig(max_tokens_per_step=64, max_context=64), [a, b])
+    assert done["a"].generated == expected_tokens([1, 2, 3], 9)
+    assert done["b"].generated == expected_tokens([4, 5], 5)
+    # steps 1..4 hint (both go on), so steps 2..5 are adopted; step 5 is b's last and its end is known,
+    # so step 6 (a alone) is decided the ordinary way; it and steps 7, 8 hint, steps 7..9 are adopted
+    assert ex.adopted == 4 + 3 and ex.dropped == 0 and ex.hints == 4 + 3
+    assert ex.cache.free_pages() == [32]
+
+
+def test_a_stop_token_drops_the_step_launched_ahead():
+    ex = AheadExecutor(num_pages=32)
+    stop = expected_tokens([1, 2, 3], 3)[2]
+    a = Request("a", [1, 2, 3], SamplingParams(max_new_tokens=20, stop_token_ids=(stop,)))
+    b = Request("b", [4, 5], SamplingParams(max_new_tokens=6))
+    s, done = run(ex, SchedulerConfig(max_tokens_per_step=64, max_context=64), [a, b])
+    assert done["a"].finish_reason == "stop" and done["a"].generated == expected_tokens([1, 2, 3], 3)
+    assert done["b"].generated == expected_tokens([4, 5], 6)
+    assert ex.dropped == 1                           # the step launched beside a's stop token
+    assert ex.cache.free_pages() == [32]
+
+
+def test_look_ahead_with_a_pool_that_runs_out_still_finishes_right():
+    ex = AheadExecutor(num_pages=6, page_size=4, slots=4)
+    reqs = [Request(i, list(range(1, 6 + i)), SamplingParams(max_new_tokens=7)) for i in range(3)]
+    s, done = run(ex, SchedulerConfig(max_tokens_per_step=64, max_context=64), reqs)
+    for i in range(3):
+        assert done[i].generated == expected_tokens(range(1, 6 + i), 7)
+    assert s.num_preemptions >= 1
+    assert ex.cache.free_pages() == [6]

@@ -131,6 +131,7 @@ grouped_gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __res
 // ballots, in ascending i.  Result rows are indexed by pair.  src_is_token: the source row of pair i
 // is token i / K (first product); otherwise it is row i (second product).
 constexpr int PAIR_MAX_TOKENS = 32;
+constexpr int PAIR_SPLITK_MAX_TOKENS = 8;   // steps up to this size use the split-inner-dimension kernel
 
 template <int MODE>
 __global__ void __launch_bounds__(128)
@@ -179,13 +180,12 @@ grouped_gemm_skinny_pairs_kernel(const __nv_bfloat16* __restrict__ A, const int*
 // MODE 0 writes float; MODE 1 holds gate and up rows (W has 2 * Nout rows) and writes
 // silu(gate) * up as bfloat16.  Tile j of NT holds rows 8j .. 8j+7.
 template <int MODE, int NT>
-__global__ void __launch_bounds__(256)
-dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
-                    const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
+__device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A, const int* src, const int* dst,
+                                            const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
+                                            void* __restrict__ C, int rows, int f0, int Nout, int Kd) {
     constexpr int H = MODE == 1 ? 2 : 1;
     __shared__ float red[8][NT * H * 4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int f0 = blockIdx.x * 16;
     const int fa = min(f0 + g, Nout - 1), fb = min(f0 + g + 8, Nout - 1);
     const uint4* wa = reinterpret_cast<const uint4*>(W + (int64_t)fa * Kd) + t;
     const uint4* wb = reinterpret_cast<const uint4*>(W + (int64_t)fb * Kd) + t;
@@ -201,7 +201,8 @@ dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __
     for (int j = 0; j < NT; ++j) {
         const int r = 8 * j + g;
         xv[j] = r < rows;
-        xr[j] = reinterpret_cast<const uint4*>(A + (int64_t)(xv[j] ? r : 0) * Kd) + t;
+        const int from = xv[j] ? (src ? src[r] : r) : 0;
+        xr[j] = reinterpret_cast<const uint4*>(A + (int64_t)from * Kd) + t;
     }
     float acc[NT][H][4];
 #pragma unroll
@@ -251,7 +252,7 @@ dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __
             if (MODE == 1) s1 += red[w][(j * H + H - 1) * 4 + i][l];
         }
         if (f < Nout && r < rows) {
-            const int64_t at = (int64_t)r * Nout + f;
+            const int64_t at = (int64_t)(dst ? dst[r] : r) * Nout + f;
             if (MODE == 1) {
                 if (bias) { s0 += bias[f]; s1 += bias[Nout + f]; }
                 reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(s0 / (1.0f + expf(-s0)) * s1);
@@ -261,6 +262,48 @@ dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __
             }
         }
     }
+}
+
+template <int MODE, int NT>
+__global__ void __launch_bounds__(256)
+dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                    const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
+    splitk_tile<MODE, NT>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
+}
+
+// The pair-indexed grouped product for the smallest steps (at most 8 tokens, so at most 8 rows per
+// expert): with few experts in use, blocks of 64 features leave most of the device idle, so here a
+// block owns 16 features and its 8 warps split the inner dimension, as in the dense kernel.
+// grid = (ceil(Nout / 16), E).
+template <int MODE>
+__global__ void __launch_bounds__(256)
+grouped_gemm_skinny_pairs_splitk_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ topk_idx,
+                                        const __nv_bfloat16* __restrict__ W, void* __restrict__ C, int n_pairs,
+                                        int K, int src_is_token, int Nout, int Kd) {
+    __shared__ int pair_sh[8], from_sh[8];
+    __shared__ int cnt_sh;
+    const int e = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        int run = 0;
+        for (int base = 0; base < n_pairs; base += 32) {
+            const int i = base + lane;
+            const bool mine = i < n_pairs && topk_idx[i] == e;
+            const unsigned bal = __ballot_sync(0xffffffffu, mine);
+            const int at = run + __popc(bal & ((1u << lane) - 1u));
+            if (mine && at < 8) {
+                pair_sh[at] = i;
+                from_sh[at] = src_is_token ? i / K : i;
+            }
+            run += __popc(bal);
+        }
+        if (lane == 0) cnt_sh = min(run, 8);
+    }
+    __syncthreads();
+    const int cnt = cnt_sh;
+    if (cnt <= 0) return;
+    const int wrows = MODE == 1 ? 2 * Nout : Nout;
+    splitk_tile<MODE, 1>(A, from_sh, pair_sh, W + (int64_t)e * wrows * Kd, nullptr, C, cnt, blockIdx.x * 16, Nout, Kd);
 }
 
 // Query/key/value projection of a step of a few tokens with its whole epilogue: bias, rotary
@@ -401,6 +444,16 @@ int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void*
     if (E < 1 || E > 65535) {
         set_last_error("grouped product (decode): %d experts exceed the grid limit", E);
         return kBadShape;
+    }
+    if (T <= PAIR_SPLITK_MAX_TOKENS) {
+        const dim3 sgrid((Nout + 15) / 16, E);
+        if (mode == 1)
+            grouped_gemm_skinny_pairs_splitk_kernel<1><<<sgrid, 256, 0, stream>>>(
+                (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 1, Nout, Kd);
+        else
+            grouped_gemm_skinny_pairs_splitk_kernel<0><<<sgrid, 256, 0, stream>>>(
+                (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 0, Nout, Kd);
+        return finish_launch("grouped_gemm_skinny_pairs");
     }
     const dim3 grid((Nout + 63) / 64, E);
     if (mode == 1)

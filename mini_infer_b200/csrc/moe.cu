@@ -296,10 +296,11 @@ __device__ __forceinline__ void permute_block(const int* __restrict__ topk_idx, 
     for (int e = tid; e <= E; e += blockDim.x) sh[e] = 0;
     __syncthreads();
     // idx_in_smem: 0 read the indices from global memory, 1 copy them to shared memory first,
-    // 2 the caller has put them there already
+    // 2 the caller has put them there already, 3 as 1 but other blocks of this launch wrote them
+    // (read around L1)
     for (int i = tid; i < N; i += blockDim.x) {
-        const int e = idx_in_smem == 2 ? sidx[i] : topk_idx[i];
-        if (idx_in_smem == 1) sidx[i] = e;
+        const int e = idx_in_smem == 2 ? sidx[i] : (idx_in_smem == 3 ? __ldcg(topk_idx + i) : topk_idx[i]);
+        if (idx_in_smem == 1 || idx_in_smem == 3) sidx[i] = e;
         if (e >= 0 && e < E) atomicAdd(&sh[e + 1], 1);
     }
     __syncthreads();
@@ -335,39 +336,41 @@ moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, 
     permute_block(topk_idx, offsets, sorted_token, inv_perm, sh, N, E, K, idx_in_smem);
 }
 
-// Routing of a few tokens (decode) in one launch: every block computes one logit (weight row, token);
-// the block that finishes last (a ticket counter, no block waits for another) selects the experts of
-// all tokens and, if `offsets` is given, builds the permutation.  `ticket` is zero before the launch
-// and is zero again after.
+// Routing of a decode-sized step in one launch: every block computes one logit (weight row, token).
+// No block waits for another: the block that finishes a token's row of logits last (a ticket
+// counter per token) selects that token's experts, and, if `offsets` is given, the block that
+// finishes the last token (one more counter) builds the permutation.  `tickets` holds 1 + T
+// counters that are zero before the launch and zero again after.
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
 moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
-                       float* __restrict__ z, unsigned* __restrict__ ticket, int* __restrict__ topk_idx,
+                       float* __restrict__ z, unsigned* __restrict__ tickets, int* __restrict__ topk_idx,
                        float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
                        int* __restrict__ offsets, int* __restrict__ sorted_token, int* __restrict__ inv_perm,
                        int T, int H, int E, int K, int norm_topk) {
-    extern __shared__ int route_sh[];  // select: [8][E] floats; then permute: [E+1] + [T*K] ints
+    extern __shared__ int route_sh[];  // select: [E] floats; then permute: [E+1] + [T*K] ints
     __shared__ bool last;
-    router_logits_small_block<AT, WT, 1>(x, wr, wsg, z, T, H, E, blockIdx.x, blockIdx.y);
+    const int t = blockIdx.y;
+    router_logits_small_block<AT, WT, 1>(x, wr, wsg, z, T, H, E, blockIdx.x, t);
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned n = gridDim.x * gridDim.y;
-        last = atomicAdd(ticket, 1u) == n - 1;
-    }
+    if (threadIdx.x == 0) last = atomicAdd(&tickets[1 + t], 1u) == gridDim.x - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
-    if (threadIdx.x == 0) *ticket = 0u;
-    const int warp = threadIdx.x >> 5;
-    float* p = reinterpret_cast<float*>(route_sh) + warp * E;
-    int* perm_sh = route_sh + 8 * E;
-    for (int t = warp; t < T; t += 8)
-        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, p, offsets ? perm_sh + E + 1 : nullptr,
-                            t, E, K, norm_topk);
+    if (threadIdx.x == 0) tickets[1 + t] = 0u;
+    if (threadIdx.x < 32)
+        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, reinterpret_cast<float*>(route_sh),
+                            nullptr, t, E, K, norm_topk);
     if (!offsets) return;
+    __threadfence();
     __syncthreads();
-    permute_block(nullptr, offsets, sorted_token, inv_perm, perm_sh, T * K, E, K, 2);
+    if (threadIdx.x == 0) last = atomicAdd(&tickets[0], 1u) == (unsigned)T - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x == 0) tickets[0] = 0u;
+    permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + E, T * K, E, K, 3);
 }
 
 // For many rows: one block per expert, no atomics.
@@ -565,11 +568,11 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
 
 // Router and (unless `offsets` is null) permutation of a step of at most
 // mi_moe_route_small_max_tokens() tokens in one launch.
-// `ticket` is one unsigned that is zero before the first call; the kernel leaves it zero.
-int mi_moe_route_small_max_tokens() { return 4 * RT_TOK; }
+// `tickets` holds 1 + T unsigned that are zero before the first call; the kernel leaves them zero.
+int mi_moe_route_small_max_tokens() { return 128; }
 
 int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
-                       unsigned* ticket, int* topk_idx, float* topk_w, float* gate, float* probs_out,
+                       unsigned* tickets, int* topk_idx, float* topk_w, float* gate, float* probs_out,
                        int* offsets, int* sorted_token, int* inv_perm, int T, int H, int E, int K, int norm_topk,
                        cudaStream_t stream) {
     if (T <= 0) return kOk;
@@ -581,7 +584,7 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
         set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
         return kBadShape;
     }
-    const size_t smem = sizeof(float) * 8 * (size_t)E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
+    const size_t smem = sizeof(float) * (size_t)E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
     if (smem > 160 * 1024 || E + 1 > 65535) {
         set_last_error("router (decode): %d experts exceed the shared memory of a block", E);
         return kBadShape;
@@ -595,7 +598,7 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         MI_ROUTE_ATTR(AT, WT);
         moe_route_small_kernel<AT, WT><<<grid, 256, smem, stream>>>(
-            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, ticket, topk_idx, topk_w, gate, probs_out,
+            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, tickets, topk_idx, topk_w, gate, probs_out,
             offsets, sorted_token, inv_perm, T, H, E, K, norm_topk));
 #undef MI_ROUTE_ATTR
     return finish_launch("moe_route_small");

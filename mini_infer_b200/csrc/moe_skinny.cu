@@ -130,7 +130,7 @@ grouped_gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __res
 // expert e are the (token, slot) pairs i = t * K + k with topk_idx[i] == e, found by one warp with
 // ballots, in ascending i.  Result rows are indexed by pair.  src_is_token: the source row of pair i
 // is token i / K (first product); otherwise it is row i (second product).
-constexpr int PAIR_MAX_TOKENS = 32;
+constexpr int PAIR_MAX_TOKENS = 128;
 constexpr int PAIR_SPLITK_MAX_TOKENS = 8;   // steps up to this size use the split-inner-dimension kernel
 
 template <int MODE>

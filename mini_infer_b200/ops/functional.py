@@ -315,8 +315,8 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
     """:func:`moe_router` and (with ``permute``) :func:`moe_permute` of a step of a few tokens in
     one launch.
 
-    ``ticket`` is one int32 that is zero before the first call and belongs to the caller (the
-    kernel leaves it zero); calls that share a ticket must not overlap.  Returns
+    ``ticket`` holds ``1 + T`` (or more) int32 counters that are zero before the first call and
+    belong to the caller (the kernel leaves them zero); calls that share them must not overlap.  Returns
     ``(idx, w, gate, probs, offsets, sorted_token, inv_perm)``, the last three None without
     ``permute``.
     """
@@ -328,7 +328,9 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
         _chk(shared_gate_w, "moe_route_small shared gate", router_w.dtype)
         if shared_gate_w.numel() != H:
             raise ValueError("moe_route_small: the shared-expert gate must have hidden_size entries")
-    _chk(ticket, "moe_route_small ticket", I32, (1,))
+    _chk(ticket, "moe_route_small ticket", I32)
+    if ticket.numel() < 1 + T:
+        raise ValueError(f"moe_route_small: {ticket.numel()} ticket counters for {T} tokens (1 + T wanted)")
     dev = x.device
     idx = torch.empty(T, top_k, dtype=I32, device=dev)
     w = torch.empty(T, top_k, dtype=F32, device=dev)

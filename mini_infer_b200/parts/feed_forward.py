@@ -64,6 +64,7 @@ class SparseMoE(FeedForward):
     SKINNY_ROWS_PER_EXPERT = 8
     # up to this many tokens in a step, the shared expert runs on a second stream beside the routed path
     OVERLAP_MAX_TOKENS = 64
+    FORK_AFTER_ROUTING_MAX_TOKENS = 8
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -116,9 +117,9 @@ class SparseMoE(FeedForward):
             self.w_shared_down = m(tensors[q + "down_proj.weight"], dev)
             g = rt.precision.small(tensors[p + "shared_expert_gate.weight"], dev).reshape(-1)
             self.w_shared_gate = g.to(self.w_router.dtype).contiguous()
-        # the one-launch routing of decode-sized steps counts its blocks in this word
-        self._route_ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+        # the one-launch routing of decode-sized steps counts its blocks in these words
         self._route_small_max = F.route_small_max_tokens()
+        self._route_ticket = torch.zeros(1 + self._route_small_max, dtype=torch.int32, device=dev)
         self._pairs_max = min(self._route_small_max, F.skinny_pairs_max_tokens())
         self._tc = (rt.act == torch.bfloat16 and F.grouped_gemm_tc_supported(self.H, self.mI)
                     and F.grouped_gemm_tc_supported(self.mI, self.H) and self.H % 8 == 0)
@@ -130,9 +131,10 @@ class SparseMoE(FeedForward):
 
     def _fork_shared_expert(self, x: torch.Tensor):
         """Start the shared expert on a second stream (decode-sized steps: every kernel is short, so it
-        runs beside the routed experts).  The one-launch routing of the smallest steps is a chain
-        of short dependent loads that a concurrent weight stream slows down, so there the fork
-        comes after it; larger steps fork first."""
+        runs beside the routed experts).  The routing of the smallest steps is a chain of short
+        dependent loads that a concurrent weight stream slows down, so there the fork comes after
+        it; larger steps, whose shared expert is a library product that would crowd the expert
+        kernels off the device, fork first."""
         main = torch.cuda.current_stream()
         if self._side_stream is None:
             self._side_stream = torch.cuda.Stream(device=x.device)
@@ -148,13 +150,16 @@ class SparseMoE(FeedForward):
         shared = side = inv_perm = None
         overlap = self.sI > 0 and T <= self.OVERLAP_MAX_TOKENS
         n = T * self.K
-        if self._skinny and T <= self._pairs_max:
+        if self._skinny and T <= self._pairs_max and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
             # decode-sized step: routing in one launch, no permutation; every used expert's weights
             # are read once and result rows are indexed by (token, slot) pair
+            fork_first = T > self.FORK_AFTER_ROUTING_MAX_TOKENS
+            if overlap and fork_first:
+                side, shared = self._fork_shared_expert(x)
             idx, w, gate, probs, _, _, _ = F.moe_route_small(
                 x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
                 want_probs=self.keep_routing, permute=False)
-            if overlap:
+            if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
             act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True)
             y = F.grouped_gemm_skinny_pairs(act, idx, self.w_down, False)

@@ -423,28 +423,32 @@ def test_qkv_skinny_refuses_partial_rotation():
 
 
 @pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
-@pytest.mark.parametrize("T,E,K,norm", [(1, 6, 3, False), (8, 60, 4, False), (19, 8, 2, True), (32, 130, 8, True)])
+@pytest.mark.parametrize("T,E,K,norm", [(1, 6, 3, False), (8, 60, 4, False), (19, 8, 2, True), (32, 130, 8, True),
+                                        (128, 60, 4, False), (77, 9, 3, True)])
 def test_route_small_equals_router_and_permute(adt, wdt, T, E, K, norm):
     H = 200
     x = rnd(T, H, dtype=adt, seed=E)
     wr = rnd(E, H, dtype=wdt, scale=0.3, seed=K)
     wsg = rnd(H, dtype=wdt, scale=0.2, seed=9)
-    ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
-    idx, w, gate, probs = F().moe_router(x, wr, wsg, K, norm, want_probs=True)
+    ticket = torch.zeros(1 + T, dtype=torch.int32, device=DEV)
+    # the two-kernel router sums a logit in the same order for steps of up to 32 tokens
+    parts = [F().moe_router(x[i:i + 32].contiguous(), wr, wsg, K, norm, want_probs=True) for i in range(0, T, 32)]
+    idx, w, gate, probs = (torch.cat([p[j] for p in parts]) for j in range(4))
     offsets, sorted_token, inv_perm = F().moe_permute(idx, E)
     for _ in range(3):                                                         # the ticket is left at zero
         got = F().moe_route_small(x, wr, wsg, K, norm, ticket, want_probs=True)
         for a, b in zip(got, (idx, w, gate, probs, offsets, sorted_token, inv_perm)):
             assert torch.equal(a, b)
-        assert int(ticket.item()) == 0
+        assert int(ticket.abs().sum()) == 0
     got = F().moe_route_small(x, wr, None, K, norm, ticket)
     assert got[2] is None and torch.equal(got[0], idx) and torch.equal(got[6], inv_perm)
     got = F().moe_route_small(x, wr, wsg, K, norm, ticket, permute=False)
     assert got[4] is None and torch.equal(got[0], idx) and torch.equal(got[1], w) and torch.equal(got[2], gate)
-    assert int(ticket.item()) == 0
+    assert int(ticket.abs().sum()) == 0
     from mini_infer_b200.ops.library import KernelError
     with pytest.raises(KernelError, match="tokens"):
-        F().moe_route_small(rnd(F().route_small_max_tokens() + 1, H, dtype=adt), wr, wsg, K, norm, ticket)
+        n = F().route_small_max_tokens() + 1
+        F().moe_route_small(rnd(n, H, dtype=adt), wr, wsg, K, norm, torch.zeros(1 + n, dtype=torch.int32, device=DEV))
 
 
 @pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8), (700, 9, 3),
@@ -515,7 +519,7 @@ def test_grouped_gemm_skinny_equals_plain(T, E, K, H, I):
 
 
 @pytest.mark.parametrize("T,E,K,H,I", [(1, 8, 2, 64, 32), (8, 60, 4, 256, 96), (32, 12, 4, 128, 160), (19, 6, 3, 96, 64),
-                                       (32, 5, 5, 64, 64)])
+                                       (32, 5, 5, 64, 64), (128, 60, 4, 128, 64), (70, 3, 2, 64, 96)])
 def test_grouped_gemm_skinny_by_pair_equals_sorted(T, E, K, H, I):
     g = torch.Generator().manual_seed(E + T)
     idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
@@ -527,16 +531,24 @@ def test_grouped_gemm_skinny_by_pair_equals_sorted(T, E, K, H, I):
     y_sorted = F().grouped_gemm_skinny(act_sorted, None, w2, offsets, T * K, False)
     act = F().grouped_gemm_skinny_pairs(x, idx, w1, True)
     y = F().grouped_gemm_skinny_pairs(act, idx, w2, False)
-    # the same sums in the same order, only the rows stand elsewhere
-    assert torch.equal(act, act_sorted[inv_perm.long()])
-    assert torch.equal(y, y_sorted[inv_perm.long()])
+    if T > 8:
+        # the same sums in the same order, only the rows stand elsewhere
+        assert torch.equal(act, act_sorted[inv_perm.long()])
+        assert torch.equal(y, y_sorted[inv_perm.long()])
+    else:
+        # the smallest steps split the inner dimension over the warps: float sums in another order
+        close(act, act_sorted[inv_perm.long()], 8e-3, "activation")
+        close(y, y_sorted[inv_perm.long()], 1e-2, "second product")
+        e_of = idx.flatten().long()
+        gu = torch.einsum("nh,nfh->nf", x.float()[torch.arange(T * K, device=DEV) // K], w1.float()[e_of])
+        close(act, torch.nn.functional.silu(gu[:, :I]) * gu[:, I:], 8e-3, "activation against the plain formula")
     wts = rnd(T, K, seed=4).abs()
     assert torch.equal(F().moe_combine(y, None, wts, None, None),
-                       F().moe_combine(y_sorted, inv_perm, wts, None, None))
+                       F().moe_combine(y[inv_perm.long().argsort()].contiguous(), inv_perm, wts, None, None))
     from mini_infer_b200.ops.library import KernelError
     with pytest.raises(KernelError, match="tokens"):
-        F().grouped_gemm_skinny_pairs(rnd(33, H, dtype=torch.bfloat16), torch.zeros(33, K, dtype=torch.int32, device=DEV),
-                                      w1, True)
+        F().grouped_gemm_skinny_pairs(rnd(129, H, dtype=torch.bfloat16),
+                                      torch.zeros(129, K, dtype=torch.int32, device=DEV), w1, True)
 
 
 @pytest.mark.parametrize("T,E,K,H,I", [(300, 6, 3, 128, 64), (2048, 60, 4, 256, 192), (1000, 12, 2, 192, 320),

@@ -159,11 +159,11 @@ qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
                 const int* __restrict__ positions, const float* __restrict__ inv_freq,
                 const int* __restrict__ slot_mapping, AT* __restrict__ q_out,
                 AT* __restrict__ k_cache, AT* __restrict__ v_cache,
-                int nh, int nkv, int d, int rot_dim, int page_size) {
+                int nh, int nkv, int d, int rot_dim, int page_size, int heads_per_block) {
     const int t = blockIdx.x;
     const int total_heads = nh + 2 * nkv;
-    const int h_lo = blockIdx.y * QKV_HEADS_PER_BLOCK;
-    const int h_hi = min(total_heads, h_lo + QKV_HEADS_PER_BLOCK);
+    const int h_lo = blockIdx.y * heads_per_block;
+    const int h_hi = min(total_heads, h_lo + heads_per_block);
     const float* row = qkv + (int64_t)t * total_heads * d;
     const float pos = (float)positions[t];
     const int half = rot_dim >> 1;
@@ -391,11 +391,14 @@ int mi_qkv_post(const float* qkv, const void* bias, int wdtype, const int* posit
         set_last_error("qkv_post: head_dim %d must be even", d);
         return kBadShape;
     }
-    const dim3 grid(T, (nh + 2 * nkv + QKV_HEADS_PER_BLOCK - 1) / QKV_HEADS_PER_BLOCK);
+    // few tokens: many blocks of a few heads; many tokens: a block per token, which looks up its
+    // position and cache slot once and computes each angle once for all heads
+    const int hpb = T >= 512 ? nh + 2 * nkv : QKV_HEADS_PER_BLOCK;
+    const dim3 grid(T, (nh + 2 * nkv + hpb - 1) / hpb);
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         qkv_post_kernel<AT, WT><<<grid, 128, 0, stream>>>(
             qkv, (const WT*)bias, positions, inv_freq, slot_mapping, (AT*)q_out, (AT*)k_cache,
-            (AT*)v_cache, nh, nkv, d, rot_dim, page_size));
+            (AT*)v_cache, nh, nkv, d, rot_dim, page_size, hpb));
     return finish_launch("qkv_post");
 }
 

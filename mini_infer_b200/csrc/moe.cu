@@ -412,25 +412,29 @@ moe_permute_place_kernel(const int* __restrict__ topk_idx, const int* __restrict
             if (e == E - 1) offsets[E] = part + counts[e];
         }
     }
-    __syncthreads();
-    int run = start_s;
-    const int end = run + counts[e];
-    for (int base = 0; base < N && run < end; base += 256) {
-        const int i = base + threadIdx.x;
-        const bool mine = i < N && topk_idx[i] == e;
-        const unsigned bal = __ballot_sync(0xffffffffu, mine);
-        if (lane == 0) warp_cnt[warp] = __popc(bal);
-        __syncthreads();
-        int before = 0, total = 0;
+    // every thread owns a contiguous range of pairs: count its matches, scan the counts over the
+    // block, place the matches in order
+    const int per = (N + 255) / 256;
+    const int lo = min(N, (int)threadIdx.x * per), hi = min(N, lo + per);
+    int c = 0;
+    for (int i = lo; i < hi; ++i) c += topk_idx[i] == e;
+    int v = c;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) { const int c = warp_cnt[w]; total += c; if (w < warp) before += c; }
-        if (mine) {
-            const int pos = run + before + __popc(bal & ((1u << lane) - 1u));
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+    }
+    if (lane == 31) warp_cnt[warp] = v;
+    __syncthreads();
+    int pos = start_s + v - c;
+    for (int w = 0; w < warp; ++w) pos += warp_cnt[w];
+    if (c == 0) return;
+    for (int i = lo; i < hi; ++i) {
+        if (topk_idx[i] == e) {
             sorted_token[pos] = i / K;
             inv_perm[i] = pos;
+            ++pos;
         }
-        run += total;
-        __syncthreads();
     }
 }
 

@@ -5,10 +5,10 @@
 // Rows are the (token, slot) pairs sorted by expert and gathered into a contiguous matrix, so
 // an expert's rows are the contiguous range offsets[e] .. offsets[e+1].  The product is computed
 // transposed: the expert's weights are the M operand (128 features per tile) and the rows are the
-// N operand, whose size follows the expert's row count (a multiple of 16 up to 256).  An expert
-// with 137 rows is one tile with N = 144 instead of two row tiles of 128, and its weights - the
-// bytes that bound this product - are read once.  One block computes one (expert, row tile,
-// feature tile) with two accumulators: gate and up of 128 features (mode 1), or two neighbouring
+// N operand, whose size follows the expert's row count (a multiple of 16 up to the tile limit TN of
+// 128 or 256 rows): an expert with 137 rows is one tile with N = 144 under TN = 256, or a tile of 128
+// and one of 16 under TN = 128, where two blocks share an SM.  One block computes one (expert, row
+// tile, feature tile) with two accumulators: gate and up of 128 features (mode 1), or two neighbouring
 // tiles of 128 features that share the row tile (mode 0):
 //   warp 0    TMA producer: weight tile(s) (128 features x 64 k) and row tile (rows x 64 k)
 //   warp 1    allocates tensor memory, issues the MMAs, commits stages back to the producer
@@ -33,9 +33,7 @@ namespace tc {
 
 constexpr int BF = 128;                        // features per tile (MMA M)
 constexpr int BK = 64;                         // k per pipeline stage (one 128-byte swizzle row)
-constexpr int MAXN = 256;                      // rows per tile at most (MMA N)
 constexpr int W_TILE_BYTES = BF * BK * 2;      // one weight tile of one stage: 16 KiB
-constexpr int R_TILE_BYTES = MAXN * BK * 2;    // room for the row tile of one stage: 32 KiB
 constexpr uint32_t WAIT_LIMIT = 400000;        // try_wait rounds before a wait gives up
 // instruction descriptor without N: D float32, A and B bfloat16, both K-major, M = 128
 constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BF >> 4) << 24);
@@ -110,17 +108,19 @@ struct RowMaps {
 };
 
 // MODE 1: C[r, n] = silu(a_r . W[e, n]) * (a_r . W[e, Nout + n])  (bfloat16); MODE 0: C[r, n] = a_r . W[e, n] (float)
-template <int MODE>
-__global__ void __launch_bounds__(192, 1)
+// TN: rows per tile at most (128 or 256); STAGES: pipeline depth; BLOCKS: blocks meant to share an SM
+// (with TN = 128 two blocks fit: while one drains its accumulators the other keeps the loads going).
+template <int MODE, int TN, int STAGES, int BLOCKS>
+__global__ void __launch_bounds__(192, BLOCKS)
 grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
                        int* __restrict__ status) {
     constexpr int NB = 2;                                 // weight tiles per stage: gate and up (MODE 1), or two
                                                           // neighbouring feature tiles sharing the row tile (MODE 0)
-    constexpr int STAGES = 3;
+    constexpr int R_TILE_BYTES = TN * BK * 2;             // room for the row tile of one stage
     constexpr int FEATS = MODE == 1 ? BF : 2 * BF;        // output features per block
     constexpr int STAGE_BYTES = NB * W_TILE_BYTES + R_TILE_BYTES;
-    constexpr uint32_t TMEM_COLS = NB * MAXN;             // 512 or 256: a power of two >= 32
+    constexpr uint32_t TMEM_COLS = NB * TN;               // 512 or 256: a power of two >= 32
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
     __shared__ uint32_t tmem_base_s;
@@ -131,8 +131,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
     bool found = false;
     for (e = 0; e < E; ++e) {
         const int b0 = offsets[e], cnt = offsets[e + 1] - b0;
-        const int tiles = (cnt + MAXN - 1) / MAXN;
-        if (slot < tiles) { row0 = b0 + slot * MAXN; rows = min(MAXN, cnt - slot * MAXN); found = true; break; }
+        const int tiles = (cnt + TN - 1) / TN;
+        if (slot < tiles) { row0 = b0 + slot * TN; rows = min(TN, cnt - slot * TN); found = true; break; }
         slot -= tiles;
     }
     if (!found) return;                                   // uniform for the whole block
@@ -194,7 +194,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
                     const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
                     const uint64_t rd = umma_desc(r_addr + k * 32);
                     umma_bf16(tmem_base, umma_desc(w_addr + k * 32), rd, idesc, acc);
-                    umma_bf16(tmem_base + MAXN, umma_desc(w_addr + W_TILE_BYTES + k * 32), rd, idesc, acc);
+                    umma_bf16(tmem_base + TN, umma_desc(w_addr + W_TILE_BYTES + k * 32), rd, idesc, acc);
                 }
                 umma_commit(&empty_bar[s]);               // the stage is free once these MMAs have read it
             }
@@ -223,10 +223,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
 #pragma unroll 1
                 for (int c0 = 0; c0 < rows; c0 += 32) {  // columns beyond n_mma hold nothing; they are not stored
                     uint32_t g[32];
-                    tmem_ld32(lane_addr + half * MAXN + c0, g);
+                    tmem_ld32(lane_addr + half * TN + c0, g);
                     if (MODE == 1) {
                         uint32_t u[32];
-                        tmem_ld32(lane_addr + MAXN + c0, u);
+                        tmem_ld32(lane_addr + TN + c0, u);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
                         __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage) + (size_t)c0 * BF + fl;
@@ -351,7 +351,12 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
         return kBadShape;
     }
     const int wrows = mode == 1 ? 2 * Nout : Nout;
-    const int max_tiles = (n_rows + tc::MAXN - 1) / tc::MAXN + E;
+    // Row tiles of 128 let two blocks share an SM (one drains its accumulators while the other loads),
+    // but an expert with more rows than that is read once per row tile; measured on B200 the small
+    // tile wins while the experts hold about one tile's worth of rows on average.
+    const int variant = (int64_t)n_rows <= (int64_t)160 * E ? 0 : 1;
+    const int tn = variant == 0 ? 128 : 256;
+    const int max_tiles = (n_rows + tn - 1) / tn + E;
     if (max_tiles > 65535) {
         set_last_error("grouped product (tensor cores): %d row tiles exceed the grid limit", max_tiles);
         return kBadShape;
@@ -370,17 +375,19 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
     }
     const int feats = mode == 1 ? tc::BF : 2 * tc::BF;
     const dim3 grid((Nout + feats - 1) / feats, max_tiles);
-    if (mode == 1) {
-        const size_t smem = 3 * (size_t)(2 * tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
-        auto kern = tc::grouped_gemm_tc_kernel<1>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);
+#define MI_TC_LAUNCH(MODE, TN, STAGES, BLOCKS)                                                         \
+    do {                                                                                               \
+        const size_t smem = STAGES * (size_t)(2 * tc::W_TILE_BYTES + TN * tc::BK * 2) + 1024;          \
+        auto kern = tc::grouped_gemm_tc_kernel<MODE, TN, STAGES, BLOCKS>;                              \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);             \
+    } while (0)
+    if (variant == 0) {
+        if (mode == 1) MI_TC_LAUNCH(1, 128, 2, 2); else MI_TC_LAUNCH(0, 128, 2, 2);
     } else {
-        const size_t smem = 3 * (size_t)(2 * tc::W_TILE_BYTES + tc::R_TILE_BYTES) + 1024;
-        auto kern = tc::grouped_gemm_tc_kernel<0>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);
+        if (mode == 1) MI_TC_LAUNCH(1, 256, 3, 1); else MI_TC_LAUNCH(0, 256, 3, 1);
     }
+#undef MI_TC_LAUNCH
     return finish_launch("grouped_gemm_tc");
 }
 

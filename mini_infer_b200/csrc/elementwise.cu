@@ -153,6 +153,11 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(128)
 qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
@@ -258,6 +263,91 @@ qkv_post_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
                 if (bias) x += to_float(bias[head * d + i]);
                 dst[i] = from_float<AT>(x);
             }
+        }
+    }
+}
+
+// The same for many tokens in bfloat16 with the rotation over the whole head (or none) and
+// d a multiple of 8: one block per token, four pairs per thread and step (16-byte loads of the
+// float row, 8-byte stores), the angles' cosines and sines computed once when a thread keeps
+// its pair index for all heads.
+template <typename WT>
+__global__ void __launch_bounds__(128)
+qkv_post_rows_kernel(const float* __restrict__ qkv, const WT* __restrict__ bias,
+                     const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                     const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ q_out,
+                     __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                     int nh, int nkv, int d, int page_size) {
+    const int t = blockIdx.x;
+    const int total_heads = nh + 2 * nkv;
+    const float* row = qkv + (int64_t)t * total_heads * d;
+    const float pos = (float)positions[t];
+    const int half = d >> 1, per_head = half >> 2;        // items of 4 pairs per head
+    int64_t kbase = -1;
+    if (nkv > 0) {
+        const int slot = slot_mapping[t];
+        if (slot >= 0) {
+            const int page = slot / page_size, off = slot - page * page_size;
+            kbase = (int64_t)page * nkv * page_size * d + (int64_t)off * d;
+        }
+    }
+    const bool same_i = (blockDim.x % per_head) == 0;
+    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (same_i && inv_freq) {
+        const int i = 4 * (threadIdx.x % per_head);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float a = pos * inv_freq[i + u];
+            cs[u] = cosf(a); sn[u] = sinf(a);
+        }
+    }
+    const int items = (nh + nkv) * per_head;
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
+        const int head = idx / per_head, i = 4 * (idx - head * per_head);
+        __nv_bfloat16* dst = nullptr;
+        if (head < nh) dst = q_out + ((int64_t)t * nh + head) * d;
+        else if (kbase >= 0) dst = k_cache + kbase + (int64_t)(head - nh) * page_size * d;
+        if (!dst) continue;
+        const int c0 = head * d + i, c1 = c0 + half;
+        const float4 l4 = *reinterpret_cast<const float4*>(row + c0);
+        const float4 h4 = *reinterpret_cast<const float4*>(row + c1);
+        float lo[4] = {l4.x, l4.y, l4.z, l4.w}, hi[4] = {h4.x, h4.y, h4.z, h4.w};
+        if (bias) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { lo[u] += to_float(bias[c0 + u]); hi[u] += to_float(bias[c1 + u]); }
+        }
+        float ylo[4], yhi[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float ca = cs[u], sa = sn[u];
+            if (!same_i && inv_freq) {
+                const float a = pos * inv_freq[i + u];
+                ca = cosf(a); sa = sinf(a);
+            }
+            ylo[u] = inv_freq ? lo[u] * ca - hi[u] * sa : lo[u];
+            yhi[u] = inv_freq ? hi[u] * ca + lo[u] * sa : hi[u];
+        }
+        uint2 plo, phi;
+        plo.x = pack2(ylo[0], ylo[1]); plo.y = pack2(ylo[2], ylo[3]);
+        phi.x = pack2(yhi[0], yhi[1]); phi.y = pack2(yhi[2], yhi[3]);
+        *reinterpret_cast<uint2*>(dst + i) = plo;
+        *reinterpret_cast<uint2*>(dst + i + half) = phi;
+    }
+    if (kbase >= 0) {
+        const int per_v = d >> 2;                             // float4 per head
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < nkv * per_v; idx += blockDim.x) {
+            const int hv = idx / per_v, i = 4 * (idx - hv * per_v);
+            const int c = (nh + nkv + hv) * d + i;
+            float4 x = *reinterpret_cast<const float4*>(row + c);
+            if (bias) {
+                x.x += to_float(bias[c]); x.y += to_float(bias[c + 1]);
+                x.z += to_float(bias[c + 2]); x.w += to_float(bias[c + 3]);
+            }
+            uint2 pk;
+            pk.x = pack2(x.x, x.y); pk.y = pack2(x.z, x.w);
+            *reinterpret_cast<uint2*>(v_cache + kbase + (int64_t)hv * page_size * d + i) = pk;
         }
     }
 }
@@ -390,6 +480,15 @@ int mi_qkv_post(const float* qkv, const void* bias, int wdtype, const int* posit
     if (d & 1) {
         set_last_error("qkv_post: head_dim %d must be even", d);
         return kBadShape;
+    }
+    if (adtype == kBF16 && T >= 64 && d % 8 == 0 && (inv_freq == nullptr || rot_dim == d) &&
+        (((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out)) & 15) == 0) &&
+        (nkv == 0 || ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0)) {
+        MI_DISPATCH_1(wdtype, WT,
+            qkv_post_rows_kernel<WT><<<T, 128, 0, stream>>>(
+                qkv, (const WT*)bias, positions, inv_freq, slot_mapping, (__nv_bfloat16*)q_out,
+                (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, d, page_size));
+        return finish_launch("qkv_post");
     }
     // few tokens: many blocks of a few heads; many tokens: a block per token, which looks up its
     // position and cache slot once and computes each angle once for all heads

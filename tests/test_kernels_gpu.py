@@ -72,13 +72,15 @@ def test_add_rmsnorm(H, adt, wdt):
 
 
 @pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,d,rot", [(5, 1, 24, 24), (4, 2, 64, 32), (3, 3, 16, 16), (2, 1, 128, 128)])
-def test_qkv_post(adt, nh, nkv, d, rot):
-    T, ps, pages = 9, 4, 6
+@pytest.mark.parametrize("nh,nkv,d,rot", [(5, 1, 24, 24), (4, 2, 64, 32), (3, 3, 16, 16), (2, 1, 128, 128),
+                                          (7, 1, 48, 48)])
+@pytest.mark.parametrize("T", [9, 70])          # a few tokens; many (one block per token, vector loads)
+def test_qkv_post(adt, nh, nkv, d, rot, T):
+    ps, pages = 4, 6 if T == 9 else 24
     width = (nh + 2 * nkv) * d
     qkv = rnd(T, width, seed=4)
     bias = rnd(width, seed=5).to(adt if adt == torch.bfloat16 else torch.float32)
-    pos = torch.tensor([0, 1, 2, 3, 17, 18, 400, 4000, 5], dtype=torch.int32, device=DEV)
+    pos = torch.tensor(([0, 1, 2, 3, 17, 18, 400, 4000, 5] * 8)[:T], dtype=torch.int32, device=DEV)
     theta = 1e6
     inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
     inv = inv.float().to(DEV)

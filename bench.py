@@ -39,6 +39,11 @@ A27B = {
     "mlp_only_layers": [], "use_sliding_window": False, "sliding_window": 32768, "max_window_layers": 21,
 }
 FULL_LAYERS = 24
+# Qwen2-57B-A14B layer sizes (the second bf16 configuration: decode at batch 1 and 8, 1,024-token prompts)
+A14B = dict(A27B, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28,
+            num_key_value_heads=4, num_experts=64, num_experts_per_tok=8, moe_intermediate_size=2560,
+            shared_expert_intermediate_size=20480, max_window_layers=28)
+SIZES = {"a2.7b": ("Qwen1.5-MoE-A2.7B", A27B), "57b-a14b": ("Qwen2-57B-A14B", A14B)}
 PUBLISHED_DECODE_B1 = 37.0          # the reference's only Qwen2-MoE number: "~37 tok/s", batch 1, FP16, RTX A6000
 
 
@@ -138,7 +143,11 @@ def run_ours(args):
     from mini_infer_b200.sampling.sampler import Sampler
 
     pk = peaks()
-    cfg = dict(A27B)
+    model_name, named = SIZES[args.sizes]
+    cfg = dict(named)
+    full_layers = named["num_hidden_layers"]
+    if args.layers <= 0:
+        args.layers = full_layers
     cfg["num_hidden_layers"] = args.layers
     dev = "cuda:0"
     t0 = time.time()
@@ -149,7 +158,8 @@ def run_ours(args):
     prompt_len, ctx_len = args.prompt_len, args.context
     if args.only != "all":
         args.points = False
-    max_b = max(args.batch, 64 if args.points else args.batch, 1)
+    point_max = max([int(x) for x in args.point_batches.split(",") if x] or [1])
+    max_b = max(args.batch, point_max if args.points else args.batch, 1)
     per_req_tokens = prompt_len + args.steps + args.warmup + 2 * max_b + 16
     num_pages = max_b * (-(-per_req_tokens // page)) + 8
     llm = LLM(model, runtime=rt, max_seq_len=ctx_len, page_size=page, num_pages=num_pages, max_running=max_b,
@@ -268,23 +278,27 @@ def run_ours(args):
 
     points = {}
     if args.points:
-        for b, key in ((1, "decode_b1"), (64, "decode_b64")):
+        for b, key in ((int(x), f"decode_b{int(x)}") for x in args.point_batches.split(",") if x):
             r = decode_run(b, max(4, args.steps // 2), 3)
             points[key] = round(b * max(4, args.steps // 2) / (r["dev_ms"] / 1e3), 1)
 
     staging_bytes = runner._host.numel() * 4
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen1.5-MoE-A2.7B sizes, 2048-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} ({model_name} sizes, {prompt_len}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(points.get("decode_b1", 0.0) / PUBLISHED_DECODE_B1, 2) if points else None,
+        "vs_baseline": round(points.get("decode_b1", 0.0) / PUBLISHED_DECODE_B1, 2)
+        if points and args.sizes == "a2.7b" else None,
         "dtype": "bf16", "data": "synthetic: random-init weights, seeded uniform-random token ids",
         "impl": "ours",
-        "config": {"model": "Qwen1.5-MoE-A2.7B layer sizes (Qwen2MoeForCausalLM)", "global_batch": args.batch,
+        "config": {"model": f"{model_name} layer sizes (Qwen2MoeForCausalLM)", "global_batch": args.batch,
                    "seq_len": prompt_len, "context": ctx_len, "parallelism": "single GPU",
-                   "layers": args.layers, "layers_of_named_config": FULL_LAYERS, "hidden": 2048, "heads": 16,
-                   "kv_heads": 16, "head_dim": 128, "experts": 60, "top_k": 4, "moe_intermediate": 1408,
-                   "shared_intermediate": 5632, "vocab": 151936, "page_size": page,
+                   "layers": args.layers, "layers_of_named_config": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "experts": cfg["num_experts"],
+                   "top_k": cfg["num_experts_per_tok"], "moe_intermediate": cfg["moe_intermediate_size"],
+                   "shared_intermediate": cfg["shared_expert_intermediate_size"], "vocab": cfg["vocab_size"],
+                   "page_size": page,
                    "l2": "every step reads GBs of weights (inputs larger than L2)",
                    "vs_baseline_note": "decode_b1 / the reference's ~37 tok/s (batch 1, FP16, RTX A6000)"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": staging_bytes,
@@ -316,8 +330,12 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
-                    help="fewer layers than the named configuration's 24 (same layer sizes) where memory or time needs it")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="fewer layers than the named configuration has (same layer sizes) where memory or time "
+                         "needs it; 0 = all of them")
+    ap.add_argument("--sizes", default="a2.7b", choices=sorted(SIZES),
+                    help="layer sizes: Qwen1.5-MoE-A2.7B (the headline configuration) or Qwen2-57B-A14B")
+    ap.add_argument("--point-batches", default="1,64", help="batch sizes of the extra decode points")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],

@@ -66,7 +66,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int64_t row_off[NSTAGE][BKEYS];
 
-    const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+    // later query tiles see more keys: they are launched first, so that the short ones fill the tail
+    const int b = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
     const int q0 = q_start[b], q_len = q_start[b + 1] - q0;
     if (qt * BQ >= q_len) return;
     const int kvl = kv_len[b];

@@ -218,6 +218,44 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     return out
 
 
+def prefill_attention_tc_supported(d: int, page_size: int) -> bool:
+    return bool(library().mi_attn_prefill_tc_supported(int(d), int(page_size)))
+
+
+def prefill_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                         q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int, window: int = 0,
+                         scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Same contract as :func:`attention`, on the tcgen05 tensor cores (TMA-fed, accumulators in
+    tensor memory): bfloat16, head sizes 64 and 128, pages of 8 to 128 tokens.  Call
+    :func:`check_tc_status` after the step: a wait inside the kernel that ran out is reported there."""
+    global _tc_pending
+    _chk(q, "prefill_attention_tc q", BF16)
+    T, nh, d = q.shape
+    _chk(k_cache, "prefill_attention_tc k_cache", BF16)
+    num_pages, nkv, page_size, d2 = k_cache.shape
+    _chk(v_cache, "prefill_attention_tc v_cache", BF16, tuple(k_cache.shape))
+    if d2 != d:
+        raise ValueError(f"prefill_attention_tc: head_dim of q ({d}) and of the cache ({d2}) differ")
+    _chk(block_table, "prefill_attention_tc block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "prefill_attention_tc q_start", I32, (B + 1,))
+    _chk(kv_len, "prefill_attention_tc kv_len", I32, (B,))
+    if out is None:
+        out = torch.empty_like(q)
+    _chk(out, "prefill_attention_tc out", BF16, (T, nh, d))
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    dev = q.device
+    if dev not in _tc_status:
+        _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
+    check(library().mi_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(q_start),
+                                       _ptr(kv_len), _ptr(out), _ptr(_tc_status[dev]), T, B, int(max_q_len), nh, nkv,
+                                       d, page_size, num_pages, max_pages, int(window), float(scale), _stream()),
+          "prefill_attention_tc")
+    _tc_pending = True
+    return out
+
+
 def decode_attention_supported(d: int) -> bool:
     return bool(library().mi_attn_decode_supported(int(d)))
 
@@ -541,9 +579,10 @@ def check_tc_status() -> None:
         if code:
             st.zero_()
             from .library import KernelError
-            raise KernelError(f"tensor-core grouped product on {dev}: a wait ran out (code {code}: "
+            raise KernelError(f"tcgen05 kernel on {dev}: a wait ran out (code {code}; grouped product: "
                               f"1 = producer waiting for a free stage, 2 = MMA waiting for data, "
-                              f"3 = epilogue waiting for the accumulators); results of that step are invalid")
+                              f"3 = epilogue waiting for the accumulators; prefill attention: 11-19); "
+                              f"results of that step are invalid")
 
 
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,

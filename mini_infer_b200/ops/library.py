@@ -38,6 +38,7 @@ _SIGNATURES = {
     "mi_dense_skinny": [P, P, P, P, I, I, I, I, P],
     "mi_gather_rows_bf16": [P, P, P, I, I, P],
     "mi_attn_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "mi_attn_prefill_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, P],
 }
 
@@ -73,6 +74,8 @@ def library() -> ctypes.CDLL:
     lib.mi_moe_route_small_max_tokens.restype = c_int
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.argtypes = []
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.restype = c_int
+    lib.mi_attn_prefill_tc_supported.argtypes = [I, I]
+    lib.mi_attn_prefill_tc_supported.restype = c_int
     lib.mi_qkv_skinny_supported.argtypes = [I, I, I]
     lib.mi_qkv_skinny_supported.restype = c_int
     lib.mi_dense_skinny_max_rows.argtypes = []

@@ -114,6 +114,9 @@ class GQAttention(Mixer):
             splits = -(-ctx.max_kv_len // F.decode_split_size())
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
                                    ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window)
+        elif self._tensor_core_prefill and F.prefill_attention_tc_supported(self.d, view.page_size):
+            a = F.prefill_attention_tc(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                                       self.window)
         elif self._tensor_core_prefill:
             a = F.prefill_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
         else:

@@ -274,6 +274,46 @@ def test_prefill_attention_tensor_cores(nh, nkv, d, ps, window):
     close(out, tiled, 1e-2, "prefill vs tiled")
 
 
+@pytest.mark.parametrize("nh,nkv,d", [(2, 2, 128), (4, 2, 64), (6, 1, 128)])
+@pytest.mark.parametrize("ps,window", [(16, 0), (8, 0), (16, 70), (64, 130), (128, 0), (32, 300)])
+def test_prefill_attention_tcgen05(nh, nkv, d, ps, window):
+    """The tcgen05 prefill kernel against the plain attention: portions with and without history,
+    single tokens in the same batch, lengths around the 128-query and 128-key tiles."""
+    assert F().prefill_attention_tc_supported(d, ps)
+    kv = [1, 128, 129, 200, 333, 130, 17, 600]
+    ql = [1, 128, 2, 200, 63, 1, 17, 600]
+    case = paged_case(kv, ql, nh, nkv, d, ps, torch.bfloat16, seed=d + ps)
+    out = F().prefill_attention_tc(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],
+                                   max(ql), window=window)
+    F().check_tc_status()
+    ref = plain_attention(case, window)
+    close(out, ref, 1e-2, "prefill attention (tcgen05)")
+
+
+def test_prefill_attention_tcgen05_far_key_and_refusals():
+    n, d, ps = 700, 128, 16
+    for far, window, visible in ((5, 0, True), (440, 250, True), (439, 250, False)):
+        case = paged_case([n], [60], 2, 1, d, ps, torch.bfloat16, seed=far)
+        q, k, v = case["seqs"][0]
+        k[far] = q[n - 11, 0] * 4.0                             # aligned with the query at position n - 11
+        v[far] = 50.0
+        page, off = int(case["table"][0, far // ps]), far % ps
+        case["kc"][page, :, off] = k[far].to(DEV)
+        case["vc"][page, :, off] = v[far].to(DEV)
+        out = F().prefill_attention_tc(case["q"], case["kc"], case["vc"], case["table"], case["q_start"],
+                                       case["kv_len"], 60, window=window)
+        F().check_tc_status()
+        close(out, plain_attention(case, window), 1e-2, f"far key {far}, window {window}")
+        row = out[60 - 11, 0].float()
+        assert (float(row.mean()) > 40.0) == visible
+    assert not F().prefill_attention_tc_supported(128, 4)
+    assert not F().prefill_attention_tc_supported(96, 16)
+    from mini_infer_b200.ops.library import KernelError
+    case = paged_case([20], [20], 2, 1, 128, 4, torch.bfloat16)
+    with pytest.raises(KernelError, match="not taken"):
+        F().prefill_attention_tc(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 20)
+
+
 def test_prefill_attention_far_key():
     n, d, ps = 700, 128, 16
     for far, window, visible in ((5, 0, True), (440, 250, True), (439, 250, False)):

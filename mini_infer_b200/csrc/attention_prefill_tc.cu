@@ -2,8 +2,9 @@
 // of prompts of a ragged batch over the paged cache, flash-attention style, with both products on
 // tcgen05.mma and their accumulators in tensor memory.
 //
-// Block = 128 queries of one head.  Key tiles of 128, aligned to absolute positions, arrive page by
-// page through TMA (128-byte swizzle) into a two-stage ring.  Per key tile:
+// Block = 128 queries of one head; two blocks share an SM, so that one's softmax runs beside the
+// other's tensor-core work.  Key tiles of 64, aligned to absolute positions, arrive page by page
+// through TMA (128-byte swizzle) into a two-stage ring.  Per key tile:
 //   S = Q K^T    A = Q tile (K-major), B = K tile (K-major), accumulator S[buf] in tensor memory
 //   softmax      one thread per query row (a row is a lane of tensor memory, so the row maximum and
 //                sum need no exchange between threads): the row of S comes to registers with
@@ -15,8 +16,7 @@
 //   warp 0    TMA producer (Q once; K and V tiles of every key tile, one copy per page and 64 columns)
 //   warp 1    allocates tensor memory, issues the MMAs
 //   warps 2-5 softmax and epilogue, one lane quarter of tensor memory each
-// S and P are double-buffered, so the next tile's S = Q K^T and this tile's O += P V run beside the
-// softmax of their neighbours.  Masking is positional: key j is visible from the
+// S is double-buffered, so the next tile's S = Q K^T runs beside this tile's softmax.  Masking is positional: key j is visible from the
 // query at position p iff j <= p and (window == 0 or j > p - window) and j < kv_len.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error status that the host
@@ -33,9 +33,10 @@ namespace pt {
 using namespace mi::tc;
 
 constexpr int BQ = 128;            // queries per block (MMA M)
-constexpr int BN = 128;            // keys per tile
+constexpr int BN = 64;             // keys per tile
 constexpr int NS = 2;              // key/value stages
-constexpr int HALF_BYTES = 128 * 64 * 2;   // a tile of 128 rows x 64 columns: 16 KiB
+constexpr int HALF_BYTES = 128 * 64 * 2;   // a tile of 128 rows x 64 columns: 16 KiB (Q, P)
+constexpr int KV_HALF = BN * 64 * 2;       // a tile of BN keys x 64 columns: 8 KiB
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -68,23 +69,35 @@ struct Maps {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ kv_len,
                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_pages,
                        int window, float scale_log2, int* __restrict__ status) {
     constexpr int DH = D / 64;                            // 64-column halves of a head
-    constexpr uint32_t TMEM_COLS = 512;                   // S[0], S[1] (128 each), O (D)
+    constexpr uint32_t TMEM_COLS = 256;                   // S[0], S[1] (BN columns each), O (D): two blocks share an SM
     constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
     // instruction descriptors: D float32, A and B bfloat16, M = 128
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) |
                                   ((128u >> 4) << 24);    // B (the V tile) MN-major
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_full, k_full[NS], v_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], o_done[2];
-    __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s;
-    __shared__ int tile_pages[BN / 8];
+    extern __shared__ __align__(1024) uint8_t smem[];     // tiles first (the swizzle wants 1024-byte alignment)
+    uint8_t* sQ = smem;                                   // DH halves of [128 queries][64]
+    uint8_t* sK = sQ + DH * HALF_BYTES;                   // NS stages of DH halves of [BN keys][64]
+    uint8_t* sV = sK + NS * DH * KV_HALF;                 // the same for V
+    uint8_t* sP = sV + NS * DH * KV_HALF;                 // [128 queries][BN keys]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + HALF_BYTES);
+    uint64_t* q_full = bars;                              // then the barriers and a few words
+    uint64_t* k_full = bars + 1;
+    uint64_t* v_full = k_full + NS;
+    uint64_t* kv_empty = v_full + NS;
+    uint64_t* s_full = kv_empty + NS;
+    uint64_t* s_empty = s_full + 2;
+    uint64_t* p_full = s_empty + 2;
+    uint64_t* o_done = p_full + 1;
+    uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(o_done + 1);
+    int* abort_p = reinterpret_cast<int*>(tmem_base_p + 1);
+    int* tile_pages = abort_p + 1;                        // BN / 8 entries
 
     // later query tiles see more keys: they are launched first, so that the short ones fill the tail
     const int b = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
@@ -101,44 +114,38 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     const int k_end = min(kvl, p_hi + 1);
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;  // >= 1: the query's own key is visible
 
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* sQ = smem;                                   // DH halves of [128 queries][64]
-    uint8_t* sK = sQ + DH * HALF_BYTES;                   // NS stages of DH halves of [128 keys][64]
-    uint8_t* sV = sK + NS * DH * HALF_BYTES;              // the same for V
-    uint8_t* sP = sV + NS * DH * HALF_BYTES;              // 2 buffers of 2 halves of [128 queries][64 keys]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    volatile int* abort_flag = &abort_s;
+    volatile int* abort_flag = abort_p;
 
     if (threadIdx.x == 0) {
-        abort_s = 0;
-        mbar_init(&q_full, 1);
+        *abort_p = (smem_u32(smem) & 1023u) ? 10 : 0;     // misplaced tiles: nothing is issued
+        mbar_init(q_full, 1);
         for (int s = 0; s < NS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128);
-            mbar_init(&p_full[s], 128); mbar_init(&o_done[s], 1);
-        }
+        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
+        mbar_init(p_full, 128);
+        mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Key and value stages start as zeros: rows that no copy fills (pages a window has released, the
     // end of the last tile) are masked in S, and P = 0 times a finite stale value is 0.
-    for (int i = threadIdx.x; i < 2 * NS * DH * HALF_BYTES / 16; i += blockDim.x)
+    for (int i = threadIdx.x; i < 2 * NS * DH * KV_HALF / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+                     ::"r"(smem_u32(tmem_base_p)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = tmem_base_s;
+    const uint32_t tmem_base = *tmem_base_p;
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(&q_full, DH * HALF_BYTES);
+            mbar_expect_tx(q_full, DH * HALF_BYTES);
             for (int hh = 0; hh < DH; ++hh)
-                tma_load_2d(sQ + hh * HALF_BYTES, &maps.q, h * D + hh * 64, q0 + qt * BQ, &q_full);
+                tma_load_2d(sQ + hh * HALF_BYTES, &maps.q, h * D + hh * 64, q0 + qt * BQ, q_full);
         }
         const int* table = block_table + (int64_t)b * max_pages;
         const int pages_per_tile = BN / page_size;
@@ -172,26 +179,26 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 const int page = tile_pages[pg];
                 if (page < 0) continue;
                 const int row = (page * nkv + hk) * page_size;
-                uint8_t* dst = (pass == 0 ? sK : sV) + (size_t)s * DH * HALF_BYTES + hh * HALF_BYTES + (size_t)pg * page_bytes;
+                uint8_t* dst = (pass == 0 ? sK : sV) + (size_t)s * DH * KV_HALF + hh * KV_HALF + (size_t)pg * page_bytes;
                 tma_load_2d(dst, pass == 0 ? &maps.k : &maps.v, hh * 64, row, pass == 0 ? &k_full[s] : &v_full[s]);
             }
             __syncwarp();                                 // tile_pages is rewritten for the next tile
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = mbar_wait(&q_full, 0, abort_flag, 12);
+            bool ok = *abort_flag == 0 && mbar_wait(q_full, 0, abort_flag, 12);
             // S of tile j is issued one tile ahead of the O += P V of tile j - 1
             auto issue_s = [&](int j) -> bool {
                 const int s = j % NS, buf = j & 1;
                 if (!mbar_wait(&k_full[s], (j / NS) & 1, abort_flag, 13)) return false;
                 if (j >= 2 && !mbar_wait(&s_empty[buf], ((j - 2) >> 1) & 1, abort_flag, 14)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (size_t)s * DH * HALF_BYTES);
+                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (size_t)s * DH * KV_HALF);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)(kk >> 2) * HALF_BYTES + (uint32_t)(kk & 3) * 32;
-                    umma_bf16(tmem_base + COL_S + buf * BN, umma_desc(qa + off), umma_desc(ka + off), IDESC_S,
-                              kk > 0 ? 1u : 0u);
+                    const uint32_t sub = (uint32_t)(kk & 3) * 32;
+                    umma_bf16(tmem_base + COL_S + buf * BN, umma_desc(qa + (uint32_t)(kk >> 2) * HALF_BYTES + sub),
+                              umma_desc(ka + (uint32_t)(kk >> 2) * KV_HALF + sub), IDESC_S, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[buf]);
                 return true;
@@ -201,20 +208,16 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 if (j + 1 < n_tiles) ok = issue_s(j + 1);
                 if (!ok) break;
                 const int s = j % NS;
-                ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, abort_flag, 15) &&
-                     mbar_wait(&v_full[s], (j / NS) & 1, abort_flag, 16);
+                ok = mbar_wait(p_full, j & 1, abort_flag, 15) && mbar_wait(&v_full[s], (j / NS) & 1, abort_flag, 16);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t pa = smem_u32(sP + (size_t)(j & 1) * 2 * HALF_BYTES);
-                const uint32_t va = smem_u32(sV + (size_t)s * DH * HALF_BYTES);
+                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + (size_t)s * DH * KV_HALF);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    const uint32_t poff = (uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32;
-                    umma_bf16(tmem_base + COL_O, umma_desc(pa + poff), umma_desc_mn(va + (uint32_t)ks * 2048, HALF_BYTES),
+                for (int ks = 0; ks < BN / 16; ++ks)
+                    umma_bf16(tmem_base + COL_O, umma_desc(pa + (uint32_t)ks * 32), umma_desc_mn(va + (uint32_t)ks * 2048, KV_HALF),
                               IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
-                }
                 umma_commit(&kv_empty[s]);                // the stage is free once these MMAs have read it
-                umma_commit(&o_done[j & 1]);              // O holds tile j; P[j & 1] is free
+                umma_commit(o_done);                      // O holds tile j; P is free
             }
         }
     } else {
@@ -244,7 +247,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             mbar_arrive_after_tmem(&s_empty[buf]);
             // does any (row, key) of this tile need the mask?
             const bool masked = (k0 + BN - 1 > p_lo) || (k0 + BN > kvl) || (window > 0 && k0 < p_hi - window + 1);
-            float mx = -INFINITY;
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of BN steps
             if (masked) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
@@ -252,16 +255,17 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                     float x = __uint_as_float(v[i]) * scale_log2;
                     if (kj > vis_hi || kj < vis_lo) x = -INFINITY;
                     v[i] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
+                    mxs[i & 3] = fmaxf(mxs[i & 3], x);
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
                     const float x = __uint_as_float(v[i]) * scale_log2;
                     v[i] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
+                    mxs[i & 3] = fmaxf(mxs[i & 3], x);
                 }
             }
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
             // the reference follows the maximum only when that moved by more than 8: exponentials stay
             // below 2^8, and O needs scaling only then
             float alpha = 1.f;
@@ -270,19 +274,18 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 m_ref = mx;
             }
             const float base = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[BN / 2];
 #pragma unroll
             for (int i = 0; i < BN; i += 2) {
                 const float e0 = fast_exp2(__uint_as_float(v[i]) - base), e1 = fast_exp2(__uint_as_float(v[i + 1]) - base);
-                sum += e0 + e1;
+                sums[(i >> 1) & 3] += e0 + e1;
                 pk[i >> 1] = pack_bf16(e0, e1);
             }
-            l_run = l_run * alpha + sum;
-            // P[buf] was read by the O += P V of tile j - 2; O is scaled after that of tile j - 1
-            if (j >= 2) ok = mbar_wait(&o_done[buf], ((j - 2) >> 1) & 1, abort_flag, 18);
+            l_run = l_run * alpha + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            // P was read, and O written, by the O += P V of tile j - 1
+            if (j >= 1) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, 18);
             const bool rescale = j > 0 && !__all_sync(0xffffffffu, alpha == 1.f);
-            if (ok && rescale) ok = mbar_wait(&o_done[buf ^ 1], ((j - 1) >> 1) & 1, abort_flag, 19);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (rescale) {
@@ -298,19 +301,17 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // 8 keys = one 16-byte chunk of this row, in half c / 64, swizzled by the row
-            uint8_t* rowp = sP + (size_t)buf * 2 * HALF_BYTES + r * 128;
+            // 8 keys = one 16-byte chunk of this row, swizzled by the row
+            uint8_t* rowp = sP + r * 128;
 #pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                const int chunk = (c & 7) ^ (r & 7);
-                *reinterpret_cast<uint4*>(rowp + (c >> 3) * HALF_BYTES + chunk * 16) =
+            for (int c = 0; c < BN / 8; ++c)
+                *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) =
                     make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-            mbar_arrive_after_tmem(&p_full[buf]);
+            mbar_arrive_after_tmem(p_full);
         }
         if (ok) {
-            ok = mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, 20);
+            ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag, 20);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
@@ -341,7 +342,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
-    if (threadIdx.x == 0 && abort_s != 0) atomicMax(status, abort_s);
+    if (threadIdx.x == 0 && *abort_p != 0) atomicMax(status, *abort_p);
 }
 
 // Row-major bfloat16 matrix [rows, cols] with a row pitch of `pitch` elements, box of 64 columns x
@@ -366,8 +367,8 @@ using namespace mi;
 
 extern "C" {
 
-// 1 if the tcgen05 prefill attention takes this geometry: head size 64 or 128; pages of 8, 16, 32, 64
-// or 128 tokens (a page is one TMA box of whole 8-row swizzle groups, and pages tile a key tile).
+// 1 if the tcgen05 prefill attention takes this geometry: head size 64 or 128; pages of 8, 16, 32 or 64
+// tokens (a page is one TMA box of whole 8-row swizzle groups, and pages tile a key tile).
 int mi_attn_prefill_tc_supported(int d, int page_size) {
     const bool ps_ok = page_size >= 8 && page_size <= pt::BN && (page_size & (page_size - 1)) == 0;
     return ((d == 64 || d == 128) && ps_ok) ? 1 : 0;
@@ -410,7 +411,7 @@ int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
     const dim3 grid((max_q_len + pt::BQ - 1) / pt::BQ, nh, B);
     const float scale_log2 = scale * 1.4426950408889634f;
     const int dh = d / 64;
-    const size_t smem = (size_t)(dh + 2 * pt::NS * dh + 4) * pt::HALF_BYTES + 1024;
+    const size_t smem = (size_t)(dh + 1) * pt::HALF_BYTES + (size_t)2 * pt::NS * dh * pt::KV_HALF + 256;
 #define MI_PT(DD)                                                                                         \
     do {                                                                                                  \
         auto kern = pt::attn_prefill_tc_kernel<DD>;                                                       \

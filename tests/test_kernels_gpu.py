@@ -275,7 +275,7 @@ def test_prefill_attention_tensor_cores(nh, nkv, d, ps, window):
 
 
 @pytest.mark.parametrize("nh,nkv,d", [(2, 2, 128), (4, 2, 64), (6, 1, 128)])
-@pytest.mark.parametrize("ps,window", [(16, 0), (8, 0), (16, 70), (64, 130), (128, 0), (32, 300)])
+@pytest.mark.parametrize("ps,window", [(16, 0), (8, 0), (16, 70), (64, 130), (64, 0), (32, 300)])
 def test_prefill_attention_tcgen05(nh, nkv, d, ps, window):
     """The tcgen05 prefill kernel against the plain attention: portions with and without history,
     single tokens in the same batch, lengths around the 128-query and 128-key tiles."""
@@ -307,6 +307,7 @@ def test_prefill_attention_tcgen05_far_key_and_refusals():
         row = out[60 - 11, 0].float()
         assert (float(row.mean()) > 40.0) == visible
     assert not F().prefill_attention_tc_supported(128, 4)
+    assert not F().prefill_attention_tc_supported(128, 128)
     assert not F().prefill_attention_tc_supported(96, 16)
     from mini_infer_b200.ops.library import KernelError
     case = paged_case([20], [20], 2, 1, 128, 4, torch.bfloat16)

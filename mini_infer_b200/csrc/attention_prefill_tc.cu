@@ -4,7 +4,7 @@
 //
 // Block = 128 queries of one head; two blocks share an SM, so that one's softmax runs beside the
 // other's tensor-core work.  Key tiles of 64, aligned to absolute positions, arrive page by page
-// through TMA (128-byte swizzle) into a two-stage ring.  Per key tile:
+// through TMA (128-byte swizzle) into two-stage rings of K and of V tiles.  Per key tile:
 //   S = Q K^T    A = Q tile (K-major), B = K tile (K-major), accumulator S[buf] in tensor memory
 //   softmax      one thread per query row (a row is a lane of tensor memory, so the row maximum and
 //                sum need no exchange between threads): the row of S comes to registers with
@@ -90,8 +90,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     uint64_t* q_full = bars;                              // then the barriers and a few words
     uint64_t* k_full = bars + 1;
     uint64_t* v_full = k_full + NS;
-    uint64_t* kv_empty = v_full + NS;
-    uint64_t* s_full = kv_empty + NS;
+    uint64_t* k_empty = v_full + NS;
+    uint64_t* v_empty = k_empty + NS;
+    uint64_t* s_full = v_empty + NS;
     uint64_t* s_empty = s_full + 2;
     uint64_t* p_full = s_empty + 2;
     uint64_t* o_done = p_full + 1;
@@ -120,7 +121,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     if (threadIdx.x == 0) {
         *abort_p = (smem_u32(smem) & 1023u) ? 10 : 0;     // misplaced tiles: nothing is issued
         mbar_init(q_full, 1);
-        for (int s = 0; s < NS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+        }
         for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
         mbar_init(p_full, 128);
         mbar_init(o_done, 1);
@@ -150,15 +153,17 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         const int* table = block_table + (int64_t)b * max_pages;
         const int pages_per_tile = BN / page_size;
         const uint32_t page_bytes = (uint32_t)page_size * 128u;
-        const int items = 2 * pages_per_tile * DH;        // (K | V) x page x 64-column half: one copy each
-        for (int j = 0; j < n_tiles; ++j) {
+        const int items = pages_per_tile * DH;            // page x 64-column half: one copy each
+        // One tile of K or of V: wait for its stage, look its pages up, copy those that exist (inside the
+        // request, not released by a window).  A K stage is free once S = Q K^T of two tiles before has
+        // run, a V stage once O += P V of two tiles before has: K runs a tile ahead of V.
+        auto load_tile = [&](int j, bool is_k) -> bool {
             const int s = j % NS;
             const uint32_t parity = ((j / NS) & 1) ^ 1;
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(&kv_empty[s], parity, abort_flag, 11);
-            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            if (lane == 0) ok = mbar_wait(is_k ? &k_empty[s] : &v_empty[s], parity, abort_flag, is_k ? 11 : 21);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
             const int k0 = k_begin + j * BN;
-            // the pages of this tile that exist (inside the request, not released by a window)
             int my_page = -1;
             if (lane < pages_per_tile) {
                 const int kpos = k0 + lane * page_size;
@@ -166,23 +171,23 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             }
             const unsigned have = __ballot_sync(0xffffffffu, my_page >= 0);
             if (lane < pages_per_tile) tile_pages[lane] = my_page;
-            if (lane == 0) {
-                const uint32_t bytes = (uint32_t)__popc(have) * page_bytes * DH;
-                mbar_expect_tx(&k_full[s], bytes);
-                mbar_expect_tx(&v_full[s], bytes);
-            }
+            uint64_t* bar = is_k ? &k_full[s] : &v_full[s];
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(have) * page_bytes * DH);
             __syncwarp();
-            for (int it = lane; it < items; it += 32) {   // K copies first: S = Q K^T can start before V is in
-                const int pass = it / (pages_per_tile * DH);
-                const int rem = it - pass * pages_per_tile * DH;
-                const int pg = rem / DH, hh = rem - pg * DH;
+            for (int it = lane; it < items; it += 32) {
+                const int pg = it / DH, hh = it - pg * DH;
                 const int page = tile_pages[pg];
                 if (page < 0) continue;
                 const int row = (page * nkv + hk) * page_size;
-                uint8_t* dst = (pass == 0 ? sK : sV) + (size_t)s * DH * KV_HALF + hh * KV_HALF + (size_t)pg * page_bytes;
-                tma_load_2d(dst, pass == 0 ? &maps.k : &maps.v, hh * 64, row, pass == 0 ? &k_full[s] : &v_full[s]);
+                uint8_t* dst = (is_k ? sK : sV) + (size_t)s * DH * KV_HALF + hh * KV_HALF + (size_t)pg * page_bytes;
+                tma_load_2d(dst, is_k ? &maps.k : &maps.v, hh * 64, row, bar);
             }
-            __syncwarp();                                 // tile_pages is rewritten for the next tile
+            __syncwarp();                                 // tile_pages is rewritten by the next call
+            return true;
+        };
+        for (int i = 0; i <= n_tiles; ++i) {
+            if (i < n_tiles && !load_tile(i, true)) break;
+            if (i >= 1 && !load_tile(i - 1, false)) break;
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -201,6 +206,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                               umma_desc(ka + (uint32_t)(kk >> 2) * KV_HALF + sub), IDESC_S, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[buf]);
+                umma_commit(&k_empty[s]);                 // the K stage is free once these MMAs have read it
                 return true;
             };
             if (ok) ok = issue_s(0);
@@ -216,7 +222,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 for (int ks = 0; ks < BN / 16; ++ks)
                     umma_bf16(tmem_base + COL_O, umma_desc(pa + (uint32_t)ks * 32), umma_desc_mn(va + (uint32_t)ks * 2048, KV_HALF),
                               IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(&kv_empty[s]);                // the stage is free once these MMAs have read it
+                umma_commit(&v_empty[s]);                 // the V stage is free once these MMAs have read it
                 umma_commit(o_done);                      // O holds tile j; P is free
             }
         }

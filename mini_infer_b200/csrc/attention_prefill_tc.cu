@@ -160,15 +160,15 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         auto load_tile = [&](int j, bool is_k) -> bool {
             const int s = j % NS;
             const uint32_t parity = ((j / NS) & 1) ^ 1;
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait(is_k ? &k_empty[s] : &v_empty[s], parity, abort_flag, is_k ? 11 : 21);
-            if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
             const int k0 = k_begin + j * BN;
-            int my_page = -1;
+            int my_page = -1;                             // looked up before the wait: the latencies overlap
             if (lane < pages_per_tile) {
                 const int kpos = k0 + lane * page_size;
                 if (kpos < kvl) my_page = table[kpos / page_size];
             }
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(is_k ? &k_empty[s] : &v_empty[s], parity, abort_flag, is_k ? 11 : 21);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
             const unsigned have = __ballot_sync(0xffffffffu, my_page >= 0);
             if (lane < pages_per_tile) tile_pages[lane] = my_page;
             uint64_t* bar = is_k ? &k_full[s] : &v_full[s];

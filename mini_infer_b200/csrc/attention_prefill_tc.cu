@@ -34,7 +34,7 @@ using namespace mi::tc;
 
 constexpr int BQ = 128;            // queries per block (MMA M)
 constexpr int BN = 64;             // keys per tile
-constexpr int NS = 2;              // key/value stages
+constexpr int NS = 2;              // key/value stages (the descriptor choice below assumes two)
 constexpr int HALF_BYTES = 128 * 64 * 2;   // a tile of 128 rows x 64 columns: 16 KiB (Q, P)
 constexpr int KV_HALF = BN * 64 * 2;       // a tile of BN keys x 64 columns: 8 KiB
 
@@ -192,18 +192,26 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = *abort_flag == 0 && mbar_wait(q_full, 0, abort_flag, 12);
+            // descriptors of the tile origins; an offset of b bytes inside a tile adds b / 16 to the address field
+            const uint64_t dq = umma_desc(smem_u32(sQ)), dp = umma_desc(smem_u32(sP));
+            uint64_t dk[NS], dv[NS];
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                dk[s] = umma_desc(smem_u32(sK + (size_t)s * DH * KV_HALF));
+                dv[s] = umma_desc_mn(smem_u32(sV + (size_t)s * DH * KV_HALF), KV_HALF);
+            }
             // S of tile j is issued one tile ahead of the O += P V of tile j - 1
             auto issue_s = [&](int j) -> bool {
                 const int s = j % NS, buf = j & 1;
                 if (!mbar_wait(&k_full[s], (j / NS) & 1, abort_flag, 13)) return false;
                 if (j >= 2 && !mbar_wait(&s_empty[buf], ((j - 2) >> 1) & 1, abort_flag, 14)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (size_t)s * DH * KV_HALF);
+                const uint64_t dks = s == 0 ? dk[0] : dk[NS - 1];
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t sub = (uint32_t)(kk & 3) * 32;
-                    umma_bf16(tmem_base + COL_S + buf * BN, umma_desc(qa + (uint32_t)(kk >> 2) * HALF_BYTES + sub),
-                              umma_desc(ka + (uint32_t)(kk >> 2) * KV_HALF + sub), IDESC_S, kk > 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + COL_S + buf * BN, dq + (((uint32_t)(kk >> 2) * HALF_BYTES + sub) >> 4),
+                              dks + (((uint32_t)(kk >> 2) * KV_HALF + sub) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[buf]);
                 umma_commit(&k_empty[s]);                 // the K stage is free once these MMAs have read it
@@ -217,11 +225,11 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 ok = mbar_wait(p_full, j & 1, abort_flag, 15) && mbar_wait(&v_full[s], (j / NS) & 1, abort_flag, 16);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + (size_t)s * DH * KV_HALF);
+                const uint64_t dvs = s == 0 ? dv[0] : dv[NS - 1];
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_bf16(tmem_base + COL_O, umma_desc(pa + (uint32_t)ks * 32), umma_desc_mn(va + (uint32_t)ks * 2048, KV_HALF),
-                              IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_bf16(tmem_base + COL_O, dp + (((uint32_t)ks * 32) >> 4), dvs + (((uint32_t)ks * 2048) >> 4), IDESC_PV,
+                              (j > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(&v_empty[s]);                 // the V stage is free once these MMAs have read it
                 umma_commit(o_done);                      // O holds tile j; P is free
             }

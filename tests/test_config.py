@@ -123,3 +123,35 @@ def test_schedule_plans_caches():
     assert [b.layer_slot for b in m2.bindings] == [0, 1, 2, 1]
     assert [b.writes for b in m2.bindings] == [True, True, True, False]
     assert m2.kv_groups[0].num_layers == 3
+
+
+@pytest.mark.parametrize("name", sorted(tiny.CONFIGS))
+def test_agrees_with_the_reference_parser_on_the_keys_it_reads(name):
+    """tests/golden/reference_config_<name>.json is what the reference's own parser
+    (src/model/model_config.cpp:61-178, compiled on the host by tests/golden/make_config_golden.py)
+    reads from the same config.json.  It never reads norm_topk_prob, decoder_sparse_step,
+    mlp_only_layers or use_sliding_window, and it keeps sliding_window whatever
+    use_sliding_window says (src/model/model_config.cpp:153); those are ours alone."""
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    with open(os.path.join(here, "golden", f"reference_config_{name}.json")) as f:
+        ref = json.load(f)
+    cfg = Qwen2MoeConfig.from_json_dict(tiny.CONFIGS[name])
+    for key in ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                "num_key_value_heads", "vocab_size", "max_position_embeddings", "tie_word_embeddings",
+                "hidden_act", "num_experts", "num_experts_per_tok", "moe_intermediate_size",
+                "shared_expert_intermediate_size", "sliding_window"):
+        assert getattr(cfg, key) == ref[key], key
+    raw = tiny.CONFIGS[name]
+    # the reference takes head_dim = hidden_size / heads for this family (it reads the key for Gemma only,
+    # src/model/model_config.cpp:117) and decides the bias by the architecture's name (:146-151); a
+    # config.json that states either gets its way here
+    if "head_dim" not in raw:
+        assert cfg.head_dim == ref["head_dim"]
+    else:
+        assert ref["head_dim"] == raw["hidden_size"] // raw["num_attention_heads"]
+    if "qkv_bias" not in raw:
+        assert cfg.qkv_bias == ref["has_qkv_bias"]
+    assert abs(cfg.rms_norm_eps - ref["rms_norm_eps"]) <= 1e-7 * ref["rms_norm_eps"] + 1e-12   # float in the reference
+    assert abs(cfg.rope_theta - ref["rope_theta"]) <= 1e-6 * ref["rope_theta"]
+    assert ref["is_moe"] == (cfg.num_experts > 0 and cfg.num_experts_per_tok > 0)

@@ -146,3 +146,30 @@ def test_random_source_is_order_independent():
     a = {n: s1.read(n) for n in names}
     b = {n: s2.read(n) for n in reversed(names)}
     assert all(torch.equal(a[n], b[n]) for n in names)
+
+
+def test_the_reference_loader_finds_what_our_writer_wrote(tmp_path):
+    """tests/golden/reference_safetensors_A.json is what the reference's own loader
+    (src/model/safetensors_loader.cpp:44-116, compiled on the host by
+    tests/golden/make_safetensors_golden.py) found in the file this repository's writer produces for
+    configuration A with seed 11: names, dtype codes (src/core/tensor.h:11-17: 2 = BF16), shapes, byte
+    sizes and a hash of every tensor's bytes.  The same folder written again and read by our own
+    reader must give the same."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    with open(os.path.join(here, "golden", "reference_safetensors_A.json")) as f:
+        golden = json.load(f)
+    folder = str(tmp_path / "model")
+    tiny.make_folder(folder, tiny.CONFIGS["A"], seed=11, dtype=torch.bfloat16)
+    ck = CheckpointFolder(folder)
+    assert sorted(ck.names()) == sorted(golden)
+    for name, ref in golden.items():
+        t = ck.read(name)
+        assert t.dtype == torch.bfloat16 and ref["dtype"] == 2
+        assert list(t.shape) == ref["shape"]
+        raw = t.contiguous().view(torch.uint8).numpy().tobytes()
+        assert len(raw) == ref["nbytes"]
+        h = 1469598103934665603
+        for b in raw:
+            h = ((h ^ b) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+        assert f"{h:016x}" == ref["fnv64"], name
+    ck.close()

@@ -260,9 +260,13 @@ def run_ours(args):
         dt = time.perf_counter() - t
         assert all(len(o.token_ids) == new_tokens for o in outs)
         return dt
+    # Two calls that differ by `steps` new tokens per request; both hold the same prefill, the same
+    # staggered start (a prompt per step) and the same tail in which the first requests have ended, so
+    # their difference is `steps` decode steps of the full batch.
+    head = 2 * args.batch
     generate_seconds(2)                                            # warm-up of this path
-    t_short = min(generate_seconds(1) for _ in range(2))           # prefill and the first token
-    t_long = min(generate_seconds(args.steps + 1) for _ in range(2))
+    t_short = min(generate_seconds(head) for _ in range(3))
+    t_long = min(generate_seconds(args.steps + head) for _ in range(3))
     e2e_value = args.batch * args.steps / max(t_long - t_short, 1e-9)
 
     # ---- roofline of the decode step ----------------------------------------------------------- #

@@ -222,10 +222,10 @@ template <int E> struct RawVec<__nv_bfloat16, E> {
     }
 };
 
-constexpr int DEC_SPLIT = 512;
+constexpr int DEC_SPLIT = 512;      // keys per split by default; smaller splits spread one or two requests over the device
 constexpr int DEC_GROUPS = 16;
 
-template <typename AT, int D>
+template <typename AT, int D, int SPLIT>
 __global__ void __launch_bounds__(128)
 attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const AT* __restrict__ v_cache,
                          const int* __restrict__ block_table, const int* __restrict__ q_start,
@@ -238,8 +238,8 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     const int pos = kvl - 1;
     int k_first = 0;
     if (window > 0) k_first = max(0, pos - window + 1);
-    const int first_split = k_first / DEC_SPLIT;
-    const int n_splits = (kvl + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int first_split = k_first / SPLIT;
+    const int n_splits = (kvl + SPLIT - 1) / SPLIT;
     if (sp < first_split || sp >= n_splits) return;
     const int hk = h / (nh / nkv);
     const int tid = threadIdx.x, grp = tid >> 3, sub = tid & 7;
@@ -254,14 +254,14 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     float acc[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) acc[i] = 0.f;
-    const int k_lo = max(sp * DEC_SPLIT, k_first);
-    const int k_hi = min(kvl, (sp + 1) * DEC_SPLIT);
+    const int k_lo = max(sp * SPLIT, k_first);
+    const int k_hi = min(kvl, (sp + 1) * SPLIT);
     // the pages of this split, looked up once
-    __shared__ int64_t key_off[DEC_SPLIT];
+    __shared__ int64_t key_off[SPLIT];
     {
         const int* table = block_table + (int64_t)b * max_pages;
-        for (int i = tid; i < DEC_SPLIT; i += 128) {
-            const int kj = sp * DEC_SPLIT + i;
+        for (int i = tid; i < SPLIT; i += 128) {
+            const int kj = sp * SPLIT + i;
             int64_t off = -1;
             if (kj >= k_lo && kj < k_hi) {
                 const int page = table[kj / page_size];
@@ -274,13 +274,13 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     // KPR keys per round: all their loads are issued before any is used
     constexpr int KPR = (sizeof(AT) == 2 || E <= 16) ? 4 : 2;
     using Raw = RawVec<AT, E>;
-    for (int i0 = grp; i0 < DEC_SPLIT; i0 += KPR * DEC_GROUPS) {
+    for (int i0 = grp; i0 < SPLIT; i0 += KPR * DEC_GROUPS) {
         int64_t off[KPR];
         Raw kr[KPR], vr[KPR];
 #pragma unroll
         for (int u = 0; u < KPR; ++u) {
             const int i = i0 + u * DEC_GROUPS;
-            off[u] = i < DEC_SPLIT ? key_off[i] : -1;
+            off[u] = i < SPLIT ? key_off[i] : -1;
             if (off[u] >= 0) { kr[u].load(k_cache + off[u] + sub * E); vr[u].load(v_cache + off[u] + sub * E); }
         }
 #pragma unroll
@@ -332,7 +332,7 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     }
 }
 
-template <typename AT, int D>
+template <typename AT, int D, int SPLIT>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
                                          AT* __restrict__ out, int nh, int max_splits, int window) {
@@ -341,8 +341,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
     const int pos = kvl - 1;
     int k_first = 0;
     if (window > 0) k_first = max(0, pos - window + 1);
-    const int first_split = k_first / DEC_SPLIT;
-    const int n_splits = (kvl + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int first_split = k_first / SPLIT;
+    const int n_splits = (kvl + SPLIT - 1) / SPLIT;
     const int64_t base = ((int64_t)b * nh + h) * max_splits;
     float m_all = -INFINITY;
     for (int s = first_split; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(base + s) * 2]);
@@ -423,16 +423,22 @@ int mi_attn_decode_supported(int d) { return (d == 64 || d == 128 || d == 256) ?
 
 int mi_attn_decode_split_size() { return DEC_SPLIT; }
 
+// 1 if `split` keys per split is built (128, 256, 512).
+int mi_attn_decode_split_supported(int split) { return (split == 128 || split == 256 || split == 512) ? 1 : 0; }
+
 // Decode attention: every request has exactly one query token.  `part_o` needs
-// B*nh*max_splits*d floats, `part_ml` B*nh*max_splits*2, with
-// max_splits >= ceil(max_kv_len / mi_attn_decode_split_size()).
-int mi_attn_decode(const void* q, const void* k_cache, const void* v_cache, int adtype, const int* block_table,
-                   const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
-                   int nh, int nkv, int d, int page_size, int max_pages, int max_splits, int window,
-                   float scale, cudaStream_t stream) {
+// B*nh*max_splits*d floats, `part_ml` B*nh*max_splits*2, with max_splits >= ceil(max_kv_len / split).
+int mi_attn_decode_split(const void* q, const void* k_cache, const void* v_cache, int adtype, const int* block_table,
+                         const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
+                         int nh, int nkv, int d, int page_size, int max_pages, int max_splits, int split, int window,
+                         float scale, cudaStream_t stream) {
     if (B <= 0) return kOk;
     if (!mi_attn_decode_supported(d)) {
         set_last_error("decode attention: head_dim %d is not built (64, 128, 256)", d);
+        return kBadShape;
+    }
+    if (!mi_attn_decode_split_supported(split)) {
+        set_last_error("decode attention: splits of %d keys are not built (128, 256, 512)", split);
         return kBadShape;
     }
     if (nkv < 1 || nh % nkv != 0) {
@@ -445,18 +451,29 @@ int mi_attn_decode(const void* q, const void* k_cache, const void* v_cache, int 
     }
     const dim3 grid(max_splits, nh, B);
     const dim3 mgrid(nh, B);
-#define MI_DEC(DD)                                                                                        \
+#define MI_DEC(DD, SS)                                                                                    \
     do {                                                                                                  \
-        attn_decode_split_kernel<AT, DD><<<grid, 128, 0, stream>>>(                                       \
+        attn_decode_split_kernel<AT, DD, SS><<<grid, 128, 0, stream>>>(                                   \
             (const AT*)q, (const AT*)k_cache, (const AT*)v_cache, block_table, q_start, kv_len, part_o,  \
             part_ml, nh, nkv, page_size, max_pages, max_splits, window, scale);                           \
-        attn_decode_merge_kernel<AT, DD><<<mgrid, DD <= 128 ? DD : 128, 0, stream>>>(                    \
+        attn_decode_merge_kernel<AT, DD, SS><<<mgrid, DD <= 128 ? DD : 128, 0, stream>>>(                \
             part_o, part_ml, q_start, kv_len, (AT*)out, nh, max_splits, window);                          \
     } while (0)
+#define MI_DEC_D(SS) do { if (d == 64) MI_DEC(64, SS); else if (d == 128) MI_DEC(128, SS); else MI_DEC(256, SS); } while (0)
     MI_DISPATCH_1(adtype, AT,
-        if (d == 64) MI_DEC(64); else if (d == 128) MI_DEC(128); else MI_DEC(256));
+        if (split == 128) MI_DEC_D(128); else if (split == 256) MI_DEC_D(256); else MI_DEC_D(512));
+#undef MI_DEC_D
 #undef MI_DEC
     return finish_launch("attn_decode", 2);
+}
+
+// The same with the default split size.
+int mi_attn_decode(const void* q, const void* k_cache, const void* v_cache, int adtype, const int* block_table,
+                   const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
+                   int nh, int nkv, int d, int page_size, int max_pages, int max_splits, int window,
+                   float scale, cudaStream_t stream) {
+    return mi_attn_decode_split(q, k_cache, v_cache, adtype, block_table, q_start, kv_len, out, part_o, part_ml, B, nh,
+                                nkv, d, page_size, max_pages, max_splits, DEC_SPLIT, window, scale, stream);
 }
 
 }  // extern "C"

@@ -261,17 +261,23 @@ def decode_attention_supported(d: int) -> bool:
 
 
 def decode_split_size() -> int:
+    """Keys per split of the decode attention by default."""
     return int(library().mi_attn_decode_split_size())
+
+
+DECODE_SPLIT_SIZES = (128, 256, 512)      # the split sizes the decode attention is built for
 
 
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                      q_start: torch.Tensor, kv_len: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                      max_splits: int, window: int = 0, scale: Optional[float] = None,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, split: Optional[int] = None) -> torch.Tensor:
     """Split-KV attention when every request brings exactly one token.
 
     ``part_o`` (``>= B*nh*max_splits*d`` floats) and ``part_ml`` (``>= B*nh*max_splits*2``)
-    are scratch; ``max_splits >= ceil(longest kv_len / decode_split_size())``.
+    are scratch; ``max_splits >= ceil(longest kv_len / split)`` with ``split`` keys per split
+    (one of ``DECODE_SPLIT_SIZES``, default ``decode_split_size()``): smaller splits spread one or
+    two requests over more blocks.
     """
     _chk(q, "decode_attention q")
     T, nh, d = q.shape
@@ -295,10 +301,12 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _chk(out, "decode_attention out", q.dtype, (T, nh, d))
     if scale is None:
         scale = 1.0 / math.sqrt(d)
-    check(library().mi_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "decode_attention q"),
-                                   _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o),
-                                   _ptr(part_ml), B, nh, nkv, d, page_size, max_pages, int(max_splits),
-                                   int(window), float(scale), _stream()), "decode_attention")
+    if split is None:
+        split = decode_split_size()
+    check(library().mi_attn_decode_split(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "decode_attention q"),
+                                         _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o),
+                                         _ptr(part_ml), B, nh, nkv, d, page_size, max_pages, int(max_splits),
+                                         int(split), int(window), float(scale), _stream()), "decode_attention")
     return out
 
 

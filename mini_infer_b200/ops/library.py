@@ -27,6 +27,7 @@ _SIGNATURES = {
     "mi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     "mi_attn_tiled": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "mi_attn_decode_split": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "mi_moe_router": [P, I, P, P, I, P, P, P, P, P, I, I, I, I, I, P],
     "mi_moe_permute": [P, P, P, P, P, I, I, I, P],
     "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],

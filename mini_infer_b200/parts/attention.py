@@ -92,7 +92,7 @@ class GQAttention(Mixer):
     def scratch_need(self, max_requests: int, max_context: int) -> Dict[str, int]:
         if not F.decode_attention_supported(self.d):
             return {}
-        splits = -(-max_context // F.decode_split_size())
+        splits = -(-max_context // min(F.DECODE_SPLIT_SIZES))
         return {"attn_part_o": max_requests * self.nh * splits * self.d,
                 "attn_part_ml": max_requests * self.nh * splits * 2}
 
@@ -111,9 +111,12 @@ class GQAttention(Mixer):
                            view.slot_mapping if nkv_in else None, kc if nkv_in else None, vc if nkv_in else None,
                            self.nh, nkv_in, self.d, view.page_size, self.rt.act)
         if ctx.all_decode and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d):
-            splits = -(-ctx.max_kv_len // F.decode_split_size())
+            # one or two requests alone cannot fill the device with splits of 512 keys
+            split = 128 if ctx.num_requests <= 2 else (256 if ctx.num_requests <= 4 else F.decode_split_size())
+            splits = -(-ctx.max_kv_len // split)
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
-                                   ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window)
+                                   ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window,
+                                   split=split)
         elif self._tensor_core_prefill and F.prefill_attention_tc_supported(self.d, view.page_size):
             a = F.prefill_attention_tc(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
                                        self.window)

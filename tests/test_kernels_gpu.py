@@ -252,6 +252,12 @@ def test_decode_attention(adt, nh, nkv, d, window):
     out2 = F().decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],
                                 po2, pml2, splits2, window=window)
     assert torch.equal(out, out2)
+    # smaller splits (used for one or two requests) agree within rounding
+    for split in (128, 256):
+        po3, pml3, _ = decode_scratch(len(kv), nh, 4 * 4096, d)
+        out3 = F().decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"],
+                                    case["kv_len"], po3, pml3, -(-max(kv) // split), window=window, split=split)
+        close(out3, ref, 3e-6 if adt == torch.float32 else 1e-2, f"decode attention, splits of {split}")
     tiled = F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 1,
                           window=window)
     close(out, tiled, 3e-6 if adt == torch.float32 else 1e-2, "decode vs tiled")

@@ -163,7 +163,8 @@ def run_ours(args):
     per_req_tokens = prompt_len + args.steps + args.warmup + 2 * max_b + 16
     num_pages = max_b * (-(-per_req_tokens // page)) + 8
     llm = LLM(model, runtime=rt, max_seq_len=ctx_len, page_size=page, num_pages=num_pages, max_running=max_b,
-              max_tokens_per_step=max(2048, max_b), prefill_chunk=2048, cuda_graphs=not args.eager)
+              max_tokens_per_step=max(2048, max_b, prompt_len), prefill_chunk=max(2048, prompt_len),
+              cuda_graphs=not args.eager)
     runner, sampler = llm.runner, llm.sampler
     g = torch.Generator().manual_seed(args.seed)
 
@@ -206,7 +207,7 @@ def run_ours(args):
     # ---- decode through the scheduler (what the Python entry point drives) -------------------- #
     def decode_run(batch, steps, warmup, clocks=False):
         ex = GPUExecutor(runner, sampler)
-        sched = Scheduler(ex, SchedulerConfig(max_tokens_per_step=max(2048, batch), max_running=batch,
+        sched = Scheduler(ex, SchedulerConfig(max_tokens_per_step=max(2048, batch, prompt_len), max_running=batch,
                                               prefill_chunk=2048, max_context=ctx_len))
         sp = SamplingParams(greedy=True, max_new_tokens=steps + warmup + 2 * batch + 8)   # early requests decode
         # while later prompts are still being prefilled

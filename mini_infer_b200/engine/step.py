@@ -88,7 +88,7 @@ class ModelRunner:
         # keep host-side state per step, or were not written with replay in mind, switch this off.
         self.cuda_graphs = bool(cuda_graphs) and not model.state_needs and \
             all(getattr(p, "graph_safe", False) for p in model.all_parts())
-        self._graphs: Dict[int, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_pool = None
         self.graph_replays = 0
         self.graph_kernel_launches = 0      # kernels of this library launched through graph replays
@@ -268,12 +268,19 @@ class ModelRunner:
         return not any(getattr(p, "keep_routing", False) for p in self.model.all_parts())
 
     def _decode_with_graph(self, ctx: StepContext, logit_rows: torch.Tensor) -> torch.Tensor:
-        """Replay (or first capture) the forward pass for this batch size.  The captured pass reads
-        the same staging views every time and is launched with the worst-case context length, so
-        only the data in the staging buffer changes between replays."""
+        """Replay (or first capture) the forward pass for this batch size and context-length bucket.
+        The captured pass reads the same staging views every time and is launched for the longest
+        context of its bucket, so only the data in the staging buffer changes between replays."""
         B = ctx.num_requests
-        ctx.max_kv_len = self.max_context
-        if B not in self._graphs:
+        # launch shapes that follow the context length (the splits of the decode attention) are captured
+        # for the next power of two, at least 1024: a few graphs per batch size, and a short context is
+        # not launched with the grid of the longest one
+        bucket = 1024
+        while bucket < ctx.max_kv_len:
+            bucket *= 2
+        ctx.max_kv_len = min(bucket, self.max_context)
+        key = (B, ctx.max_kv_len)
+        if key not in self._graphs:
             side = torch.cuda.Stream(device=self.rt.device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -287,8 +294,8 @@ class ModelRunner:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=self._graph_pool):
                 out = self.model.forward(ctx, logit_rows)
-            self._graphs[B] = (g, out, launch_count() - before)
-        g, out, kernels = self._graphs[B]
+            self._graphs[key] = (g, out, launch_count() - before)
+        g, out, kernels = self._graphs[key]
         g.replay()
         self.graph_replays += 1
         self.graph_kernel_launches += kernels

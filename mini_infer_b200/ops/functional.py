@@ -42,11 +42,24 @@ def _chk(t: Optional[torch.Tensor], what: str, dtype=None, shape=None) -> None:
     if dtype is not None and t.dtype != dtype:
         raise TypeError(f"{what}: expected {dtype}, got {t.dtype}")
     if shape is not None:
-        if len(shape) != t.dim() or any(s is not None and s != a for s, a in zip(shape, t.shape)):
-            raise ValueError(f"{what}: expected shape {list(shape)}, got {list(t.shape)}")
+        actual = t.shape
+        bad = len(shape) != len(actual)
+        if not bad:
+            for s, a in zip(shape, actual):
+                if s is not None and s != a:
+                    bad = True
+                    break
+        if bad:
+            raise ValueError(f"{what}: expected shape {list(shape)}, got {list(actual)}")
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def _stream() -> int:
+    """The current CUDA stream of the current device, as the integer the launchers take."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -321,7 +321,7 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference",
         "unavailable": "Deyu-Kong/mini-infer is a CMake/C++ project with no setup.py or pyproject.toml at its root "
-                       "('pip install ... /root/reference' fails: not installable); its binary targets sm_86, needs "
+                       "('pip install' of its checkout fails: not installable); its binary targets sm_86, needs "
                        "a real checkpoint with tokenizer.json and runs Qwen2-MoE in FP16 only"}))
     return 0
 

@@ -4,15 +4,16 @@
 //
 // Block = 128 queries of one head; two blocks share an SM, so that one's softmax runs beside the
 // other's tensor-core work.  Key tiles of 64, aligned to absolute positions, arrive page by page
-// through TMA (128-byte swizzle) into two-stage rings of K and of V tiles.  Per key tile:
+// through TMA (128-byte swizzle) into rings of three K and two V tiles.  Per key tile:
 //   S = Q K^T    A = Q tile (K-major), B = K tile (K-major), accumulator S[buf] in tensor memory
 //   softmax      one thread per query row (a row is a lane of tensor memory, so the row maximum and
 //                sum need no exchange between threads): the row of S comes to registers with
-//                tcgen05.ld, P = exp2(s - reference) is rounded to bfloat16 into shared memory in the
-//                operand layout; the reference follows the running maximum only when that moved by
-//                more than 8 (P stays below 2^8), and only then O is scaled in place (tcgen05.ld / .st)
-//   O += P V     A = P (K-major over keys), B = V tile as it lies in the cache (keys x head, i.e.
-//                MN-major), accumulator O in tensor memory
+//                tcgen05.ld, P = exp2(s - reference) is rounded to bfloat16 and written over S in
+//                place with tcgen05.st (two keys per 32-bit column); the reference follows the
+//                running maximum only when that moved by more than 8 (P stays below 2^8), and only
+//                then O is scaled in place (tcgen05.ld / .st)
+//   O += P V     A = P straight from tensor memory, B = V tile as it lies in the cache (keys x head,
+//                i.e. MN-major), accumulator O in tensor memory
 //   warp 0    TMA producer (Q once; K and V tiles of every key tile, one copy per page and 64 columns)
 //   warp 1    allocates tensor memory, issues the MMAs
 //   warps 2-5 softmax and epilogue, one lane quarter of tensor memory each
@@ -34,7 +35,8 @@ using namespace mi::tc;
 
 constexpr int BQ = 128;            // queries per block (MMA M)
 constexpr int BN = 64;             // keys per tile
-constexpr int NS = 2;              // key/value stages (the descriptor choice below assumes two)
+constexpr int NK = 3;              // stages of the K ring
+constexpr int NV = 2;              // stages of the V ring
 constexpr int HALF_BYTES = 128 * 64 * 2;   // a tile of 128 rows x 64 columns: 16 KiB (Q, P)
 constexpr int KV_HALF = BN * 64 * 2;       // a tile of BN keys x 64 columns: 8 KiB
 
@@ -53,6 +55,15 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lb
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
+}
+// tcgen05.mma with the A operand in tensor memory (lane = row, a 32-bit column holds two bfloat16 of
+// consecutive k) and B in shared memory.
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -83,19 +94,17 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                                   ((128u >> 4) << 24);    // B (the V tile) MN-major
     extern __shared__ __align__(1024) uint8_t smem[];     // tiles first (the swizzle wants 1024-byte alignment)
     uint8_t* sQ = smem;                                   // DH halves of [128 queries][64]
-    uint8_t* sK = sQ + DH * HALF_BYTES;                   // NS stages of DH halves of [BN keys][64]
-    uint8_t* sV = sK + NS * DH * KV_HALF;                 // the same for V
-    uint8_t* sP = sV + NS * DH * KV_HALF;                 // [128 queries][BN keys]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + HALF_BYTES);
+    uint8_t* sK = sQ + DH * HALF_BYTES;                   // NK stages of DH halves of [BN keys][64]
+    uint8_t* sV = sK + NK * DH * KV_HALF;                 // NV stages of the same for V
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NV * DH * KV_HALF);
     uint64_t* q_full = bars;                              // then the barriers and a few words
     uint64_t* k_full = bars + 1;
-    uint64_t* v_full = k_full + NS;
-    uint64_t* k_empty = v_full + NS;
-    uint64_t* v_empty = k_empty + NS;
-    uint64_t* s_full = v_empty + NS;
-    uint64_t* s_empty = s_full + 2;
-    uint64_t* p_full = s_empty + 2;
-    uint64_t* o_done = p_full + 1;
+    uint64_t* v_full = k_full + NK;
+    uint64_t* k_empty = v_full + NV;
+    uint64_t* v_empty = k_empty + NK;
+    uint64_t* s_full = v_empty + NV;
+    uint64_t* p_full = s_full + 2;                        // per S/P buffer: the softmax may be a tile ahead
+    uint64_t* o_done = p_full + 2;
     uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(o_done + 1);
     int* abort_p = reinterpret_cast<int*>(tmem_base_p + 1);
     int* tile_pages = abort_p + 1;                        // BN / 8 entries
@@ -121,17 +130,15 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     if (threadIdx.x == 0) {
         *abort_p = (smem_u32(smem) & 1023u) ? 10 : 0;     // misplaced tiles: nothing is issued
         mbar_init(q_full, 1);
-        for (int s = 0; s < NS; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
-        }
-        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
-        mbar_init(p_full, 128);
+        for (int s = 0; s < NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 128); }
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Key and value stages start as zeros: rows that no copy fills (pages a window has released, the
     // end of the last tile) are masked in S, and P = 0 times a finite stale value is 0.
-    for (int i = threadIdx.x; i < 2 * NS * DH * KV_HALF / 16; i += blockDim.x)
+    for (int i = threadIdx.x; i < (NK + NV) * DH * KV_HALF / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1) {
@@ -158,8 +165,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         // request, not released by a window).  A K stage is free once S = Q K^T of two tiles before has
         // run, a V stage once O += P V of two tiles before has: K runs a tile ahead of V.
         auto load_tile = [&](int j, bool is_k) -> bool {
-            const int s = j % NS;
-            const uint32_t parity = ((j / NS) & 1) ^ 1;
+            const int ns = is_k ? NK : NV;
+            const int s = j % ns;
+            const uint32_t parity = ((j / ns) & 1) ^ 1;
             const int k0 = k_begin + j * BN;
             int my_page = -1;                             // looked up before the wait: the latencies overlap
             if (lane < pages_per_tile) {
@@ -185,28 +193,23 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             __syncwarp();                                 // tile_pages is rewritten by the next call
             return true;
         };
-        for (int i = 0; i <= n_tiles; ++i) {
+        for (int i = 0; i <= n_tiles + 1; ++i) {          // K runs two tiles ahead of V
             if (i < n_tiles && !load_tile(i, true)) break;
-            if (i >= 1 && !load_tile(i - 1, false)) break;
+            if (i >= 2 && !load_tile(i - 2, false)) break;
         }
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = *abort_flag == 0 && mbar_wait(q_full, 0, abort_flag, 12);
             // descriptors of the tile origins; an offset of b bytes inside a tile adds b / 16 to the address field
-            const uint64_t dq = umma_desc(smem_u32(sQ)), dp = umma_desc(smem_u32(sP));
-            uint64_t dk[NS], dv[NS];
-#pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                dk[s] = umma_desc(smem_u32(sK + (size_t)s * DH * KV_HALF));
-                dv[s] = umma_desc_mn(smem_u32(sV + (size_t)s * DH * KV_HALF), KV_HALF);
-            }
-            // S of tile j is issued one tile ahead of the O += P V of tile j - 1
+            const uint64_t dq = umma_desc(smem_u32(sQ));
+            // S of tile j goes to buffer j & 1.  P of tile j overwrites S of tile j in place (bfloat16, two
+            // keys per 32-bit column) and is the A operand of O += P V straight from tensor memory; S of
+            // tile j + 2 goes to the same buffer and is issued once O += P V of tile j is complete.
             auto issue_s = [&](int j) -> bool {
-                const int s = j % NS, buf = j & 1;
-                if (!mbar_wait(&k_full[s], (j / NS) & 1, abort_flag, 13)) return false;
-                if (j >= 2 && !mbar_wait(&s_empty[buf], ((j - 2) >> 1) & 1, abort_flag, 14)) return false;
+                const int s = j % NK, buf = j & 1;
+                if (!mbar_wait(&k_full[s], (j / NK) & 1, abort_flag, 13)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t dks = s == 0 ? dk[0] : dk[NS - 1];
+                const uint64_t dks = umma_desc(smem_u32(sK + (size_t)s * DH * KV_HALF));
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t sub = (uint32_t)(kk & 3) * 32;
@@ -218,20 +221,21 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 return true;
             };
             if (ok) ok = issue_s(0);
+            if (ok && n_tiles > 1) ok = issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) ok = issue_s(j + 1);
-                if (!ok) break;
-                const int s = j % NS;
-                ok = mbar_wait(p_full, j & 1, abort_flag, 15) && mbar_wait(&v_full[s], (j / NS) & 1, abort_flag, 16);
+                const int s = j % NV, buf = j & 1;
+                ok = mbar_wait(&p_full[buf], (j >> 1) & 1, abort_flag, 15) &&
+                     mbar_wait(&v_full[s], (j / NV) & 1, abort_flag, 16);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t dvs = s == 0 ? dv[0] : dv[NS - 1];
+                const uint64_t dvs = umma_desc_mn(smem_u32(sV + (size_t)s * DH * KV_HALF), KV_HALF);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_bf16(tmem_base + COL_O, dp + (((uint32_t)ks * 32) >> 4), dvs + (((uint32_t)ks * 2048) >> 4), IDESC_PV,
-                              (j > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < BN / 16; ++ks)     // 16 keys of P are 8 columns of tensor memory
+                    umma_bf16_tmem_a(tmem_base + COL_O, tmem_base + COL_S + buf * BN + ks * 8,
+                                     dvs + (((uint32_t)ks * 2048) >> 4), IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(&v_empty[s]);                 // the V stage is free once these MMAs have read it
-                umma_commit(o_done);                      // O holds tile j; P is free
+                umma_commit(o_done);                      // O holds tile j
+                if (j + 2 < n_tiles) ok = mbar_wait(o_done, j & 1, abort_flag, 14) && issue_s(j + 2);
             }
         }
     } else {
@@ -258,7 +262,6 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            mbar_arrive_after_tmem(&s_empty[buf]);
             // does any (row, key) of this tile need the mask?
             const bool masked = (k0 + BN - 1 > p_lo) || (k0 + BN > kvl) || (window > 0 && k0 < p_hi - window + 1);
             float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of BN steps
@@ -297,9 +300,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 pk[i >> 1] = pack_bf16(e0, e1);
             }
             l_run = l_run * alpha + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
-            // P was read, and O written, by the O += P V of tile j - 1
-            if (j >= 1) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, 18);
+            // O is scaled only after the O += P V of tile j - 1 is complete
             const bool rescale = j > 0 && !__all_sync(0xffffffffu, alpha == 1.f);
+            if (rescale) ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, 18);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (rescale) {
@@ -315,14 +318,17 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // 8 keys = one 16-byte chunk of this row, swizzled by the row
-            uint8_t* rowp = sP + r * 128;
-#pragma unroll
-            for (int c = 0; c < BN / 8; ++c)
-                *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-            mbar_arrive_after_tmem(p_full);
+            // P over S in place: 64 keys are 32 columns of two bfloat16 each
+            tmem_st32(s_addr, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            mbar_arrive_after_tmem(&p_full[buf]);
+            // Follow the O += P V barrier phase by phase (a parity wait must not fall two phases behind):
+            // the one of tile j - 1 was issued a tile ago, so this seldom waits.
+            if (j > 0) {
+                ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, 19);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
         }
         if (ok) {
             ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag, 20);
@@ -425,7 +431,7 @@ int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
     const dim3 grid((max_q_len + pt::BQ - 1) / pt::BQ, nh, B);
     const float scale_log2 = scale * 1.4426950408889634f;
     const int dh = d / 64;
-    const size_t smem = (size_t)(dh + 1) * pt::HALF_BYTES + (size_t)2 * pt::NS * dh * pt::KV_HALF + 256;
+    const size_t smem = (size_t)dh * pt::HALF_BYTES + (size_t)(pt::NK + pt::NV) * dh * pt::KV_HALF + 256;
 #define MI_PT(DD)                                                                                         \
     do {                                                                                                  \
         auto kern = pt::attn_prefill_tc_kernel<DD>;                                                       \

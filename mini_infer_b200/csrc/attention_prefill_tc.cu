@@ -269,20 +269,15 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
                     const int kj = k0 + i;
-                    float x = __uint_as_float(v[i]) * scale_log2;
-                    if (kj > vis_hi || kj < vis_lo) x = -INFINITY;
-                    v[i] = __float_as_uint(x);
-                    mxs[i & 3] = fmaxf(mxs[i & 3], x);
+                    if (kj > vis_hi || kj < vis_lo) v[i] = 0xff800000u;                 // -inf
+                    mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(v[i]));
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const float x = __uint_as_float(v[i]) * scale_log2;
-                    v[i] = __float_as_uint(x);
-                    mxs[i & 3] = fmaxf(mxs[i & 3], x);
-                }
+                for (int i = 0; i < BN; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(v[i]));
             }
-            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+            // the scale is positive: the maximum of the scaled scores is the scaled maximum
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * scale_log2;
             // the reference follows the maximum only when that moved by more than 8: exponentials stay
             // below 2^8, and O needs scaling only then
             float alpha = 1.f;
@@ -295,7 +290,8 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             uint32_t pk[BN / 2];
 #pragma unroll
             for (int i = 0; i < BN; i += 2) {
-                const float e0 = fast_exp2(__uint_as_float(v[i]) - base), e1 = fast_exp2(__uint_as_float(v[i + 1]) - base);
+                const float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), scale_log2, -base));
+                const float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -base));
                 sums[(i >> 1) & 3] += e0 + e1;
                 pk[i >> 1] = pack_bf16(e0, e1);
             }

@@ -147,6 +147,68 @@ moe_router_logits_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, co
     }
 }
 
+// Many tokens, bfloat16 activations and weights: the same logits on the tensor cores (products of
+// two bfloat16 are exact in float, the accumulator is float).  Block = 16 tokens x 64 columns, 8 warps
+// that take the 32-wide k chunks in turn (warp w: chunks w, w + 8, ...); fragments are loaded straight
+// from global memory with the k permutation of a 16-byte load on both operands, which leaves a dot
+// product unchanged.  The warps' partial sums are added in warp order, so the order of a logit's
+// additions depends on H only.
+constexpr int RM_TOK = 16, RM_COLS = 64, RM_WARPS = 8, RM_PITCH = RM_COLS + 2;
+
+__global__ void __launch_bounds__(32 * RM_WARPS)
+moe_router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
+                             const __nv_bfloat16* __restrict__ wsg, float* __restrict__ z, int T, int H, int E) {
+    __shared__ float part[RM_WARPS][RM_TOK * RM_PITCH];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int t0 = blockIdx.x * RM_TOK, c0 = blockIdx.y * RM_COLS;
+    const int ncols = E + (wsg ? 1 : 0);
+    // rows past the end repeat a valid one; their results are not stored
+    const uint4* xa = reinterpret_cast<const uint4*>(x + (int64_t)min(t0 + g, T - 1) * H) + t;
+    const uint4* xb = reinterpret_cast<const uint4*>(x + (int64_t)min(t0 + g + 8, T - 1) * H) + t;
+    const uint4* wp[RM_COLS / 8];
+#pragma unroll
+    for (int j = 0; j < RM_COLS / 8; ++j) {
+        const int c = c0 + 8 * j + g;
+        const __nv_bfloat16* row = c < E ? wr + (int64_t)c * H : (c == E && wsg ? wsg : wr);
+        wp[j] = reinterpret_cast<const uint4*>(row) + t;
+    }
+    float acc[RM_COLS / 8][4];
+#pragma unroll
+    for (int j = 0; j < RM_COLS / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+    const int chunks = H >> 5;
+#pragma unroll 2
+    for (int c = warp; c < chunks; c += RM_WARPS) {
+        const uint4 va = __ldg(xa + 4 * c), vb = __ldg(xb + 4 * c);
+        uint4 w[RM_COLS / 8];
+#pragma unroll
+        for (int j = 0; j < RM_COLS / 8; ++j) w[j] = __ldg(wp[j] + 4 * c);
+#pragma unroll
+        for (int j = 0; j < RM_COLS / 8; ++j) {
+            mma_bf16_16816(acc[j], va.x, vb.x, va.y, vb.y, w[j].x, w[j].y);
+            mma_bf16_16816(acc[j], va.z, vb.z, va.w, vb.w, w[j].z, w[j].w);
+        }
+    }
+    // fragment: [0] (token g, column 8j+2t) [1] (g, 8j+2t+1) [2] (g+8, 8j+2t) [3] (g+8, 8j+2t+1)
+    float* mine = part[warp];
+#pragma unroll
+    for (int j = 0; j < RM_COLS / 8; ++j) {
+        mine[g * RM_PITCH + 8 * j + 2 * t] = acc[j][0];
+        mine[g * RM_PITCH + 8 * j + 2 * t + 1] = acc[j][1];
+        mine[(g + 8) * RM_PITCH + 8 * j + 2 * t] = acc[j][2];
+        mine[(g + 8) * RM_PITCH + 8 * j + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < RM_TOK * RM_COLS; o += 32 * RM_WARPS) {
+        const int r = o / RM_COLS, c = o - r * RM_COLS;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < RM_WARPS; ++w) v += part[w][r * RM_PITCH + c];
+        if (t0 + r < T && c0 + c < ncols) z[(int64_t)(t0 + r) * ncols + c0 + c] = v;
+    }
+}
+
 // Few tokens (decode): one block per weight row and group of RT_TOK tokens; the 8 warps split the
 // row, so every lane has a single round of loads in flight, and the warps' partial sums are added
 // in warp order.  The order of a dot product's additions depends on H only.
@@ -373,68 +435,48 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
     permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + E, T * K, E, K, 3);
 }
 
-// For many rows: one block per expert, no atomics.
-//   counts:  counts[e] = number of (token, slot) pairs routed to e
-//   place:   offsets[e] = sum of counts below e; pairs of e placed in token order
-__global__ void __launch_bounds__(256)
-moe_permute_count_kernel(const int* __restrict__ topk_idx, int* __restrict__ counts, int N) {
-    __shared__ int warp_cnt[8];
+// For many rows: one block per expert, no atomics and no scratch.  A warp owns a contiguous run of
+// pairs.  Pass 1 counts, per warp, the block's own pairs and the pairs of lower experts (their total
+// is the expert's first place); a scan over the warps gives every warp its first place; pass 2 places
+// the pairs in token order.
+__global__ void __launch_bounds__(1024)
+moe_permute_expert_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets,
+                          int* __restrict__ sorted_token, int* __restrict__ inv_perm, int N, int E, int K) {
+    __shared__ int own_s[32], below_s[32];
     const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int c = 0;
-    for (int base = 0; base < N; base += 256) {
-        const int i = base + threadIdx.x;
-        c += __popc(__ballot_sync(0xffffffffu, i < N && topk_idx[i] == e));
+    const int per = ((N + 1023) / 1024) * 32;                 // pairs per warp: whole rounds of 32
+    const int lo = min(N, warp * per), hi = min(N, lo + per);
+    int own = 0, below = 0;
+#pragma unroll 4
+    for (int i = lo; i < hi; i += 32) {
+        const int v = i + lane < hi ? __ldg(topk_idx + i + lane) : E;
+        own += __popc(__ballot_sync(0xffffffffu, v == e));
+        below += __popc(__ballot_sync(0xffffffffu, v < e));
     }
-    if (lane == 0) warp_cnt[warp] = c;
+    if (lane == 0) { own_s[warp] = own; below_s[warp] = below; }
     __syncthreads();
+    int o = own_s[lane], b = below_s[lane], before = lane < warp ? o : 0;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        o += __shfl_xor_sync(0xffffffffu, o, d);
+        b += __shfl_xor_sync(0xffffffffu, b, d);
+        before += __shfl_xor_sync(0xffffffffu, before, d);
+    }
     if (threadIdx.x == 0) {
-        int t = 0;
-        for (int w = 0; w < 8; ++w) t += warp_cnt[w];
-        counts[e] = t;
+        offsets[e] = b;
+        if (e == E - 1) offsets[E] = b + o;
     }
-}
-
-__global__ void __launch_bounds__(256)
-moe_permute_place_kernel(const int* __restrict__ topk_idx, const int* __restrict__ counts,
-                         int* __restrict__ offsets, int* __restrict__ sorted_token, int* __restrict__ inv_perm,
-                         int N, int E, int K) {
-    __shared__ int warp_cnt[8];
-    __shared__ int start_s;
-    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp == 0) {
-        int part = 0;
-        for (int i = lane; i < e; i += 32) part += counts[i];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        if (lane == 0) {
-            start_s = part;
-            offsets[e] = part;
-            if (e == E - 1) offsets[E] = part + counts[e];
+    if (own == 0) return;                                     // uniform for the warp
+    int pos = b + before;
+    for (int i = lo; i < hi; i += 32) {
+        const int v = i + lane < hi ? __ldg(topk_idx + i + lane) : E;
+        const unsigned m = __ballot_sync(0xffffffffu, v == e);
+        if (v == e) {
+            const int p = pos + __popc(m & ((1u << lane) - 1u));
+            sorted_token[p] = (i + lane) / K;
+            inv_perm[i + lane] = p;
         }
-    }
-    // every thread owns a contiguous range of pairs: count its matches, scan the counts over the
-    // block, place the matches in order
-    const int per = (N + 255) / 256;
-    const int lo = min(N, (int)threadIdx.x * per), hi = min(N, lo + per);
-    int c = 0;
-    for (int i = lo; i < hi; ++i) c += topk_idx[i] == e;
-    int v = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += n;
-    }
-    if (lane == 31) warp_cnt[warp] = v;
-    __syncthreads();
-    int pos = start_s + v - c;
-    for (int w = 0; w < warp; ++w) pos += warp_cnt[w];
-    if (c == 0) return;
-    for (int i = lo; i < hi; ++i) {
-        if (topk_idx[i] == e) {
-            sorted_token[pos] = i / K;
-            inv_perm[i] = pos;
-            ++pos;
-        }
+        pos += __popc(m);
     }
 }
 
@@ -557,6 +599,17 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
                                                                         gate, probs_out, T, E, K, norm_topk);
         return finish_launch("moe_router", 2);
     }
+    if (adtype == kBF16 && wdtype == kBF16 && H % 32 == 0 &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(wsg)) & 15) == 0) {
+        const dim3 mgrid((T + RM_TOK - 1) / RM_TOK, (ncols + RM_COLS - 1) / RM_COLS);
+        if (mgrid.y <= 65535) {
+            moe_router_logits_mma_kernel<<<mgrid, 32 * RM_WARPS, 0, stream>>>(
+                (const __nv_bfloat16*)x, (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, z_scratch, T, H, E);
+            moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w,
+                                                                            gate, probs_out, T, E, K, norm_topk);
+            return finish_launch("moe_router", 2);
+        }
+    }
 #define MI_ROUTER_ATTR(AT, WT)                                                                              \
     if (smem_x > 48 * 1024)                                                                                 \
         cudaFuncSetAttribute(moe_router_logits_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
@@ -608,7 +661,7 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
     return finish_launch("moe_route_small");
 }
 
-// `counts_scratch` holds E ints (used when there are many rows).
+// `counts_scratch` is not used any more (the signature is kept).
 int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* inv_perm, int* counts_scratch, int T,
                    int E, int K, cudaStream_t stream) {
     if (E + 1 > 12000) {
@@ -617,10 +670,9 @@ int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* in
     }
     const int64_t N = (int64_t)T * K;
     if (N > 2048 && E <= 65535) {
-        moe_permute_count_kernel<<<E, 256, 0, stream>>>(topk_idx, counts_scratch, (int)N);
-        moe_permute_place_kernel<<<E, 256, 0, stream>>>(topk_idx, counts_scratch, offsets, sorted_token, inv_perm,
-                                                        (int)N, E, K);
-        return finish_launch("moe_permute", 2);
+        (void)counts_scratch;
+        moe_permute_expert_kernel<<<E, 1024, 0, stream>>>(topk_idx, offsets, sorted_token, inv_perm, (int)N, E, K);
+        return finish_launch("moe_permute");
     }
     size_t smem = sizeof(int) * (E + 1);
     const int idx_in_smem = (smem + sizeof(int) * N <= 160 * 1024) ? 1 : 0;

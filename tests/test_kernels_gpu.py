@@ -382,6 +382,34 @@ def test_router(adt, wdt, E, K, norm):
         assert torch.allclose(w.sum(-1).cpu(), torch.ones(T), atol=1e-5)
 
 
+@pytest.mark.parametrize("T,H", [(130, 224), (700, 96), (333, 200), (2050, 64)])
+@pytest.mark.parametrize("E,K,gate", [(60, 4, True), (130, 8, False), (5, 2, True), (64, 3, True)])
+def test_router_of_many_tokens_on_the_tensor_cores(T, H, E, K, gate):
+    """bfloat16 steps of more than 128 tokens take the mma.sync logits kernel when H is a multiple of 32
+    (H = 200 stays on the float kernel); both give the float logits of the plain router."""
+    x = rnd(T, H, dtype=torch.bfloat16, seed=T)
+    wr = rnd(E, H, dtype=torch.bfloat16, scale=0.05, seed=E)      # a flat softmax: the K best stay apart
+    wsg = rnd(H, dtype=torch.bfloat16, scale=0.2, seed=9) if gate else None
+    idx, w, g, probs = F().moe_router(x, wr, wsg, K, True, want_probs=True)
+    rp, ri, rw = pm.route(x.float().cpu(), wr.float().cpu(), K, True)
+    close(probs, rp, 5e-6, "router probabilities")
+    s = torch.sort(rp, dim=-1, descending=True).values
+    clear = torch.ones(T, dtype=torch.bool)
+    for k in range(min(K, E - 1)):
+        clear &= (s[:, k] - s[:, k + 1]) > 2e-7
+    assert clear.sum() >= T // 2
+    assert torch.equal(idx.cpu().long()[clear], ri[clear])
+    close(w.cpu()[clear], rw[clear], 5e-6, "router weights")
+    if gate:
+        close(g, torch.sigmoid(x.float().cpu() @ wsg.float().cpu()), 5e-6, "shared gate")
+    else:
+        assert g is None
+    # a token's logits do not depend on its neighbours in the step
+    part = F().moe_router(x[129:].contiguous(), wr, wsg, K, True, want_probs=True)[3] if T - 129 > 128 else None
+    if part is not None:
+        assert torch.equal(part, probs[129:])
+
+
 def test_router_ties_go_to_the_lowest_index():
     T, H, E = 4, 64, 10
     x = rnd(T, H)
@@ -501,7 +529,7 @@ def test_route_small_equals_router_and_permute(adt, wdt, T, E, K, norm):
 
 
 @pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8), (700, 9, 3),
-                                   (2100, 7, 1)])
+                                   (2100, 7, 1), (4099, 60, 4), (3001, 130, 8), (513, 64, 8)])
 def test_permute(T, E, K):
     g = torch.Generator().manual_seed(T)
     idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)

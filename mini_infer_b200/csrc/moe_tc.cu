@@ -34,9 +34,11 @@ constexpr int W_TILE_BYTES = BF * BK * 2;      // one weight tile of one stage: 
 // instruction descriptor without N: D float32, A and B bfloat16, both K-major, M = 128
 constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BF >> 4) << 24);
 
-// The four row-tile maps differ in their box height only (32, 64, 128, 256 rows).
+// The row-tile maps differ in their box height only (16, 32, 64, 128, 256 rows): a row tile is fetched
+// as the fewest boxes that cover its rows rounded up to 16, so that no bandwidth goes to rows that
+// the MMA does not read.
 struct RowMaps {
-    CUtensorMap m[4];
+    CUtensorMap m[5];
 };
 
 // MODE 1: C[r, n] = silu(a_r . W[e, n]) * (a_r . W[e, Nout + n])  (bfloat16); MODE 0: C[r, n] = a_r . W[e, n] (float)
@@ -72,8 +74,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     const int num_kb = Kd / BK;
     const int n_mma = (rows + 15) & ~15;                  // MMA N: a multiple of 16 for M = 128
-    const int box = rows <= 32 ? 0 : (rows <= 64 ? 1 : (rows <= 128 ? 2 : 3));
-    const uint32_t row_bytes = (32u << box) * BK * 2;     // bytes the row-tile copy delivers
+    const uint32_t row_bytes = (uint32_t)n_mma * BK * 2;  // bytes the row-tile copies deliver
     const uint32_t idesc = IDESC_BASE | ((uint32_t)(n_mma >> 3) << 17);
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -107,7 +108,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
                 mbar_expect_tx(&full_bar[s], NB * W_TILE_BYTES + row_bytes);
                 tma_load_2d(st, &map_w, kb * BK, e * wrows + n0, &full_bar[s]);
                 tma_load_2d(st + W_TILE_BYTES, &map_w, kb * BK, e * wrows + (MODE == 1 ? Nout + n0 : n0 + BF), &full_bar[s]);
-                tma_load_2d(st + NB * W_TILE_BYTES, &maps_a.m[box], kb * BK, row0, &full_bar[s]);
+                for (int done = 0; done < n_mma;) {
+                    const int left = n_mma - done;
+                    const int b = left >= 256 ? 4 : (left >= 128 ? 3 : (left >= 64 ? 2 : (left >= 32 ? 1 : 0)));
+                    tma_load_2d(st + NB * W_TILE_BYTES + done * (BK * 2), &maps_a.m[b], kb * BK, row0 + done,
+                                &full_bar[s]);
+                    done += 16 << b;
+                }
             }
         }
     } else if (warp == 1) {
@@ -213,6 +220,257 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
     if (threadIdx.x == 0 && abort_s != 0) atomicMax(status, abort_s);
 }
 
+// The same product as a persistent kernel: one block per SM walks over the (row tile, feature tile)
+// pairs, feature tiles fastest.  The loads never stop at a tile's end: the producer runs on into the
+// next tile's k blocks while the epilogue warps drain the accumulators.  A tile's accumulators lie at
+// the low end of the tensor memory for even tiles and at the high end for odd ones, so the MMA warp
+// starts the next tile at once when the two tiles fit side by side (2 x NW x N columns of 512), and
+// after the epilogue otherwise.  An expert's rows are split evenly over its row tiles of up to TN
+// rows, so an expert with 137 rows is one tile (N = 144) and its weights cross the memory system
+// once.  The table of row tiles is built by every block for itself from the experts' offsets.
+//   warp 0    builds the table; TMA producer
+//   warp 1    tensor memory, MMAs
+//   warps 2-5 epilogue, one TMEM lane quarter each; a warp turns its 32 features x 32 rows through its
+//             own patch of shared memory so that rows leave in 16-byte stores
+// NB: feature tiles of 128 per block in mode 0 (they share the row tile); mode 1 has gate and up.
+template <int MODE, int TN, int STAGES, int NB>
+__global__ void __launch_bounds__(192, 1)
+grouped_gemm_tc_persistent_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
+                                  const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
+                                  int* __restrict__ status) {
+    constexpr int NW = MODE == 1 ? 2 : NB;                // weight tiles per stage = accumulators per tile
+    constexpr int STAGE_BYTES = NW * W_TILE_BYTES + TN * BK * 2;
+    constexpr int FEATS = MODE == 1 ? BF : NB * BF;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int OUT_BYTES = MODE == 1 ? 2 : 4;
+    constexpr int PER16 = 16 / OUT_BYTES;                 // features per 16-byte group
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_full[2], accum_empty[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s, row_tiles_s;
+    constexpr int TURN_ROWS = MODE == 1 ? 32 : 16;        // rows of a warp's patch: 2 KiB either way
+    __shared__ __align__(16) uint8_t turn_s[4][TURN_ROWS * 32 * OUT_BYTES];   // per epilogue warp: [rows][32 features]
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    int2* table = reinterpret_cast<int2*>(smem + (size_t)STAGES * STAGE_BYTES);   // .x first row, .y expert << 16 | rows
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&accum_full[s], 1); mbar_init(&accum_empty[s], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        int base = 0;                                     // row tiles of the experts before this round of 32
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane;
+            int b0 = 0, cnt = 0;
+            if (e < E) { b0 = offsets[e]; cnt = offsets[e + 1] - b0; }
+            const int tiles = (cnt + TN - 1) / TN;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
+            }
+            if (tiles > 0) {
+                const int per = ((cnt + tiles - 1) / tiles + 15) & ~15;          // an even split, whole MMA columns
+                for (int j = 0; j < tiles; ++j)
+                    table[base + incl - tiles + j] = make_int2(b0 + j * per, (e << 16) | max(0, min(per, cnt - j * per)));
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) row_tiles_s = base;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    const int n_feat = (Nout + FEATS - 1) / FEATS;
+    const int total = row_tiles_s * n_feat;
+    const int wrows = MODE == 1 ? 2 * Nout : Nout;
+    const int num_kb = Kd / BK;
+    // accumulator b of a tile with `n_mma` columns: tensor-memory columns col0 + b * pitch .. + n_mma, with
+    // pitch = n_mma rounded up to 32 and col0 = 0 (even tiles of this block) or 512 - NW * pitch (odd)
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;                              // k blocks so far, over all tiles of this block
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                const int r = tile / n_feat, n0 = (tile - r * n_feat) * FEATS;
+                const int2 ent = table[r];
+                const int rows = ent.y & 0xffff, e = ent.y >> 16, row0 = ent.x;
+                if (rows == 0) continue;
+                const int n_mma = (rows + 15) & ~15;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+                    ok = mbar_wait(&empty_bar[s], parity, abort_flag, 1);
+                    if (!ok) break;
+                    uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], NW * W_TILE_BYTES + (uint32_t)n_mma * BK * 2);
+#pragma unroll
+                    for (int b = 0; b < NW; ++b)
+                        tma_load_2d(st + b * W_TILE_BYTES, &map_w, kb * BK,
+                                    e * wrows + (MODE == 1 ? b * Nout + n0 : n0 + b * BF), &full_bar[s]);
+                    for (int done = 0; done < n_mma;) {
+                        const int left = n_mma - done;
+                        const int b = left >= 256 ? 4 : (left >= 128 ? 3 : (left >= 64 ? 2 : (left >= 32 ? 1 : 0)));
+                        tma_load_2d(st + NW * W_TILE_BYTES + done * (BK * 2), &maps_a.m[b], kb * BK, row0 + done,
+                                    &full_bar[s]);
+                        done += 16 << b;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, i = 0;                       // k blocks and tiles of this block so far
+            int width_before = 0;                         // columns of the tile before
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                const int rows = table[tile / n_feat].y & 0xffff;
+                if (rows == 0) continue;
+                const int n_mma = (rows + 15) & ~15, pitch = (n_mma + 31) & ~31, width = NW * pitch;
+                const uint32_t side = i & 1;
+                const uint32_t col0 = tmem_base + (side ? 512 - width : 0);
+                const uint32_t idesc = IDESC_BASE | ((uint32_t)(n_mma >> 3) << 17);
+                // this side is free once the epilogue warps have read tile i - 2; the other side's tile
+                // i - 1 must have been read too if the two tiles overlap
+                ok = mbar_wait(&accum_empty[side], ((i >> 1) & 1) ^ 1, abort_flag, 4);
+                if (ok && i > 0 && width_before + width > 512)
+                    ok = mbar_wait(&accum_empty[side ^ 1], ((i - 1) >> 1) & 1, abort_flag, 5);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t w_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t r_addr = w_addr + NW * W_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t rd = umma_desc(r_addr + k * 32);
+#pragma unroll
+                        for (int b = 0; b < NW; ++b)
+                            umma_bf16(col0 + b * pitch, umma_desc(w_addr + b * W_TILE_BYTES + k * 32), rd, idesc, acc);
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&accum_full[side]);
+                width_before = width;
+                ++i;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int fl = quarter * 32 + lane;
+        const bool staged = (Nout % PER16) == 0 && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        uint8_t* turn = turn_s[quarter];
+        uint32_t i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            const int r = tile / n_feat, n0 = (tile - r * n_feat) * FEATS;
+            const int2 ent = table[r];
+            const int rows = ent.y & 0xffff, row0 = ent.x;
+            if (rows == 0) continue;
+            const int n_mma = (rows + 15) & ~15, pitch = (n_mma + 31) & ~31, width = NW * pitch;
+            const uint32_t side = i & 1;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (side ? 512 - width : 0);
+            ok = mbar_wait(&accum_full[side], (i >> 1) & 1, abort_flag, 3);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int half = 0; half < (MODE == 1 ? 1 : NB); ++half) {
+                const int fbase = n0 + half * BF;
+                if (fbase >= Nout) break;
+                const int f = fbase + fl;
+#pragma unroll 1
+                for (int c0 = 0; c0 < rows; c0 += 32) {
+                    uint32_t g[32];
+                    tmem_ld32(lane_addr + half * pitch + c0, g);
+                    if (MODE == 1) {
+                        uint32_t u[32];
+                        tmem_ld32(lane_addr + pitch + c0, u);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float gv = __uint_as_float(g[j]);
+                            // the result is rounded to bfloat16: the fast exponential and division are exact enough
+                            g[j] = (uint32_t)__bfloat16_as_ushort(
+                                __float2bfloat16_rn(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[j])));
+                        }
+                    } else {
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    }
+                    if (staged) {
+                        constexpr int GROUPS = 32 / PER16;                // 16-byte groups per row of the patch
+                        const uint4* src = reinterpret_cast<const uint4*>(turn);
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(C);
+#pragma unroll
+                        for (int h0 = 0; h0 < 32; h0 += TURN_ROWS) {
+                            __syncwarp();                                 // the patch's readers of the round before
+                            if (MODE == 1) {
+                                __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(turn) + lane;
+#pragma unroll
+                                for (int j = 0; j < TURN_ROWS; ++j) st[j * 32] = __ushort_as_bfloat16((unsigned short)g[h0 + j]);
+                            } else {
+                                float* st = reinterpret_cast<float*>(turn) + lane;
+#pragma unroll
+                                for (int j = 0; j < TURN_ROWS; ++j) st[j * 32] = __uint_as_float(g[h0 + j]);
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int q = 0; q < TURN_ROWS * GROUPS / 32; ++q) {
+                                const int idx = q * 32 + lane;
+                                const int rr = h0 + idx / GROUPS, gq = idx % GROUPS;
+                                const int feat = fbase + quarter * 32 + gq * PER16;
+                                if (c0 + rr < rows && feat < Nout)
+                                    *reinterpret_cast<uint4*>(dst + ((int64_t)(row0 + c0 + rr) * Nout + feat) * OUT_BYTES) = src[idx];
+                            }
+                        }
+                    } else if (f < Nout) {
+                        if (MODE == 1) {
+                            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + (int64_t)(row0 + c0) * Nout + f;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (c0 + j < rows) out[(int64_t)j * Nout] = __ushort_as_bfloat16((unsigned short)g[j]);
+                        } else {
+                            float* out = reinterpret_cast<float*>(C) + (int64_t)(row0 + c0) * Nout + f;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (c0 + j < rows) out[(int64_t)j * Nout] = __uint_as_float(g[j]);
+                        }
+                    }
+                }
+            }
+            // this warp has read its quarter of the tile's accumulators
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&accum_empty[side]);
+            ++i;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_s != 0) atomicMax(status, abort_s);
+}
+
 // out[r, :] = x[rows[r], :]  (bfloat16, 16 bytes per thread and step)
 __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows, uint4* __restrict__ out,
                                    int vec_per_row) {
@@ -242,25 +500,53 @@ int mi_gather_rows_bf16(const void* x, const int* rows, void* out, int n_rows, i
     return finish_launch("gather_rows");
 }
 
+// Shared memory a persistent form needs beside its static part: alignment slack, the pipeline and
+// the table of row tiles (one entry per tile; n_rows / tn + E bounds their number).
+static size_t persistent_smem(int tn, int stages, int nw, int n_rows, int E) {
+    return 1024 + (size_t)stages * (nw * tc::W_TILE_BYTES + tn * tc::BK * 2) + ((size_t)n_rows / tn + E) * sizeof(int2);
+}
+constexpr size_t kPersistentSmemLimit = 232448 - 8704;    // 227 KiB less the kernel's static shared memory
+
 // A: [n_rows, Kd] bfloat16, rows sorted by expert (offsets[E+1]); W: [E, wrows, Kd] bfloat16.
 // mode 1: C bfloat16 [n_rows, Nout] = silu(gate) * up with W holding 2*Nout rows per expert;
 // mode 0: C float [n_rows, Nout].  `status` (device int, zero before the first call) receives a
 // non-zero code if a wait inside the kernel ran out.
-int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows, int E,
-                       int Nout, int Kd, int mode, cudaStream_t stream) {
+// form: -1 chooses; 0 / 1 one block per tile with row tiles of 128 (two blocks per SM) / 256;
+//       2 / 3 persistent with row tiles of 160 and four pipeline stages / 256 and three.
+int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows,
+                            int E, int Nout, int Kd, int mode, int form, cudaStream_t stream) {
     if (n_rows <= 0) return kOk;
     if (!mi_grouped_gemm_tc_supported(Kd)) {
         set_last_error("grouped product (tensor cores): inner size %d is not a multiple of %d", Kd, tc::BK);
         return kBadShape;
     }
+    if (form < -1 || form > 3) {
+        set_last_error("grouped product (tensor cores): no form %d", form);
+        return kBadShape;
+    }
     const int wrows = mode == 1 ? 2 * Nout : Nout;
-    // Row tiles of 128 let two blocks share an SM (one drains its accumulators while the other loads),
-    // but an expert with more rows than that is read once per row tile; measured on B200 the small
-    // tile wins while the experts hold about one tile's worth of rows on average.
-    const int variant = (int64_t)n_rows <= (int64_t)160 * E ? 0 : 1;
-    const int tn = variant == 0 ? 128 : 256;
+    // Measured on B200 (60 experts, 2048 x 1408): the persistent forms win everywhere; four stages
+    // win while an expert's rows make one or two row tiles of 160, the larger tile otherwise.
+    // With few rows per expert the product is bound by reading the weights once, and single feature
+    // tiles in mode 0 spread that more evenly over the SMs.
+    const double per_expert = (double)n_rows / E;
+    const int nb160 = per_expert <= 170.0 ? 1 : 2;        // feature tiles per block in mode 0, form 2
+    const bool fits2 = E < 32768 && persistent_smem(160, 4, mode == 1 ? 2 : nb160, n_rows, E) <= kPersistentSmemLimit;
+    const bool fits3 = E < 32768 && persistent_smem(256, 3, 2, n_rows, E) <= kPersistentSmemLimit;
+    if (form == -1) {
+        const bool want2 = per_expert <= 170.0 || (per_expert > 256.0 && per_expert <= 330.0);
+        if (want2 && fits2) form = 2;
+        else if (fits3) form = 3;
+        else form = (int64_t)n_rows <= (int64_t)160 * E ? 0 : 1;
+    }
+    if ((form == 2 && !fits2) || (form == 3 && !fits3)) {
+        set_last_error("grouped product (tensor cores): %d rows of %d experts exceed the persistent form's table",
+                       n_rows, E);
+        return kBadShape;
+    }
+    const int tn = form == 0 ? 128 : 256;
     const int max_tiles = (n_rows + tn - 1) / tn + E;
-    if (max_tiles > 65535) {
+    if (form < 2 && max_tiles > 65535) {
         set_last_error("grouped product (tensor cores): %d row tiles exceed the grid limit", max_tiles);
         return kBadShape;
     }
@@ -271,10 +557,35 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
     tc::RowMaps maps_a;
     CUtensorMap map_w;
     bool ok = tc::make_map(&map_w, W, (uint64_t)E * wrows, (uint64_t)Kd, tc::BF);
-    for (int i = 0; i < 4 && ok; ++i) ok = tc::make_map(&maps_a.m[i], A, (uint64_t)n_rows, (uint64_t)Kd, 32u << i);
+    for (int i = 0; i < 5 && ok; ++i) ok = tc::make_map(&maps_a.m[i], A, (uint64_t)n_rows, (uint64_t)Kd, 16u << i);
     if (!ok) {
         set_last_error("grouped product (tensor cores): cuTensorMapEncodeTiled failed");
         return kLaunchFailed;
+    }
+    if (form >= 2) {
+        static int num_sms = 0;
+        if (num_sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        const int ptn = form == 2 ? 160 : 256, nb = form == 2 ? nb160 : 2;
+        const int feats = mode == 1 ? tc::BF : nb * tc::BF;
+        const int64_t tiles = ((int64_t)n_rows / ptn + E) * ((Nout + feats - 1) / feats);
+        const size_t smem = persistent_smem(ptn, form == 2 ? 4 : 3, mode == 1 ? 2 : nb, n_rows, E);
+        const int blocks = (int)(tiles < num_sms ? tiles : num_sms);
+#define MI_TCP_LAUNCH(MODE, TN, ST, NB)                                                               \
+    do {                                                                                              \
+        auto kern = tc::grouped_gemm_tc_persistent_kernel<MODE, TN, ST, NB>;                          \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        kern<<<blocks, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);          \
+    } while (0)
+        if (form == 3) { if (mode == 1) MI_TCP_LAUNCH(1, 256, 3, 2); else MI_TCP_LAUNCH(0, 256, 3, 2); }
+        else if (mode == 1) MI_TCP_LAUNCH(1, 160, 4, 2);
+        else if (nb == 1) MI_TCP_LAUNCH(0, 160, 4, 1);
+        else MI_TCP_LAUNCH(0, 160, 4, 2);
+#undef MI_TCP_LAUNCH
+        return finish_launch("grouped_gemm_tc");
     }
     const int feats = mode == 1 ? tc::BF : 2 * tc::BF;
     const dim3 grid((Nout + feats - 1) / feats, max_tiles);
@@ -285,13 +596,18 @@ int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
         kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);             \
     } while (0)
-    if (variant == 0) {
+    if (form == 0) {
         if (mode == 1) MI_TC_LAUNCH(1, 128, 2, 2); else MI_TC_LAUNCH(0, 128, 2, 2);
     } else {
         if (mode == 1) MI_TC_LAUNCH(1, 256, 3, 1); else MI_TC_LAUNCH(0, 256, 3, 1);
     }
 #undef MI_TC_LAUNCH
     return finish_launch("grouped_gemm_tc");
+}
+
+int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows, int E,
+                       int Nout, int Kd, int mode, cudaStream_t stream) {
+    return mi_grouped_gemm_tc_form(A, W, offsets, C, status, n_rows, E, Nout, Kd, mode, -1, stream);
 }
 
 }  // extern "C"

@@ -564,12 +564,18 @@ _tc_status = {}
 _tc_pending = False
 
 
-def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, swiglu_pair: bool) -> torch.Tensor:
+TC_FORMS = (0, 1, 2, 3)
+
+
+def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, swiglu_pair: bool,
+                    form: Optional[int] = None) -> torch.Tensor:
     """The grouped product for many rows per expert (prefill): tcgen05 tensor cores fed by TMA.
 
     ``a_sorted [N, K]`` holds the rows already in expert order.  Result as for
     :func:`grouped_gemm_skinny`.  Call :func:`check_tc_status` after the step: a wait inside the
-    kernel that ran out is reported there rather than hanging the device.
+    kernel that ran out is reported there rather than hanging the device.  ``form`` picks one of the
+    kernel's forms (``TC_FORMS``: one block per tile with row tiles of 128 or 256, persistent with
+    row tiles of 160 or 256); the library chooses by the rows per expert when it is None.
     """
     global _tc_pending
     _chk(a_sorted, "grouped_gemm_tc a", BF16)
@@ -582,8 +588,9 @@ def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tens
     if dev not in _tc_status:
         _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
     out = torch.empty(n_rows, nout, dtype=BF16 if swiglu_pair else F32, device=dev)
-    check(library().mi_grouped_gemm_tc(_ptr(a_sorted), _ptr(w), _ptr(offsets), _ptr(out), _ptr(_tc_status[dev]),
-                                       n_rows, E, nout, Kd, 1 if swiglu_pair else 0, _stream()), "grouped_gemm_tc")
+    check(library().mi_grouped_gemm_tc_form(_ptr(a_sorted), _ptr(w), _ptr(offsets), _ptr(out), _ptr(_tc_status[dev]),
+                                            n_rows, E, nout, Kd, 1 if swiglu_pair else 0,
+                                            -1 if form is None else int(form), _stream()), "grouped_gemm_tc")
     _tc_pending = True
     return out
 

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "mi_attn_prefill": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_prefill_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, P],
+    "mi_grouped_gemm_tc_form": [P, P, P, P, P, I, I, I, I, I, I, P],
 }
 
 

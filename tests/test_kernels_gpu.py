@@ -629,10 +629,13 @@ def test_grouped_gemm_skinny_by_pair_equals_sorted(T, E, K, H, I):
 
 
 @pytest.mark.parametrize("T,E,K,H,I", [(300, 6, 3, 128, 64), (2048, 60, 4, 256, 192), (1000, 12, 2, 192, 320),
-                                       (129, 4, 1, 64, 128), (512, 8, 8, 2048, 1408)])
+                                       (129, 4, 1, 64, 128), (512, 8, 8, 2048, 1408), (3000, 3, 1, 64, 192),
+                                       (700, 5, 2, 128, 64)])
 def test_grouped_gemm_tensor_core_equals_plain(T, E, K, H, I):
-    """The tcgen05 grouped product against the plain kernel: experts with 0, 1, 127, 128, 129 and many
-    rows; feature counts that are and are not multiples of the 128-column tile."""
+    """The tcgen05 grouped product, in each of its forms (one block per tile or persistent, row tiles
+    of 128, 160 and 256), against the plain kernel: experts with 0, 1, 127, 128, 129 and thousands of
+    rows; feature counts that are and are not multiples of the 128-column tile.  All forms add in the
+    same order, so they agree to the bit."""
     g = torch.Generator().manual_seed(T + E)
     idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
     if E > 2 and K < E:
@@ -645,14 +648,31 @@ def test_grouped_gemm_tensor_core_equals_plain(T, E, K, H, I):
     assert F().grouped_gemm_tc_supported(H, I) and F().grouped_gemm_tc_supported(I, H)
     xs = F().gather_rows(x, sorted_token)
     assert torch.equal(xs, x[sorted_token.long()])
-    act = F().grouped_gemm_tc(xs, wgu, offsets, True)
-    F().check_tc_status()
     ref = F().grouped_gemm_plain(x, sorted_token, wgu, offsets, T * K, True, torch.float32)
-    close(act, ref, 6e-3, "gate/up product")
-    y = F().grouped_gemm_tc(act, wd, offsets, False)
-    F().check_tc_status()
-    ref_y = F().grouped_gemm_plain(act, None, wd, offsets, T * K, False, torch.float32)
-    close(y, ref_y, 2e-5, "down product")
+    first = None
+    for form in (None,) + tuple(F().TC_FORMS):
+        act = F().grouped_gemm_tc(xs, wgu, offsets, True, form)
+        F().check_tc_status()
+        close(act, ref, 6e-3, f"gate/up product, form {form}")
+        y = F().grouped_gemm_tc(act, wd, offsets, False, form)
+        F().check_tc_status()
+        ref_y = F().grouped_gemm_plain(act, None, wd, offsets, T * K, False, torch.float32)
+        close(y, ref_y, 2e-5, f"down product, form {form}")
+        if first is None:
+            first = (act, y)
+        else:
+            assert torch.equal(act, first[0]) and torch.equal(y, first[1]), form
+
+
+def test_grouped_gemm_tensor_core_refuses_what_it_cannot_take():
+    from mini_infer_b200.ops.library import KernelError
+    x = rnd(40, 64, dtype=torch.bfloat16)
+    w = rnd(2, 32, 64, dtype=torch.bfloat16)
+    offsets = torch.tensor([0, 15, 40], dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="no form"):
+        F().grouped_gemm_tc(x, w, offsets, False, 7)
+    with pytest.raises(KernelError, match="multiple of 64"):
+        F().grouped_gemm_tc(rnd(40, 48, dtype=torch.bfloat16), rnd(2, 32, 48, dtype=torch.bfloat16), offsets, False)
 
 
 # --------------------------------------------------------------------------- #

@@ -332,10 +332,16 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     }
 }
 
+// Merge of a (request, head)'s splits in split order.  The splits' maxima and sums are fetched by all
+// threads at once and their weights exp(m_s - m) kept in shared memory (up to MERGE_CAP splits; more
+// are re-read from global memory), so the block waits for global memory twice, not once per split.
+constexpr int MERGE_CAP = 512;
+
 template <typename AT, int D, int SPLIT>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
                                          AT* __restrict__ out, int nh, int max_splits, int window) {
+    __shared__ float sm_w[MERGE_CAP], sm_l[MERGE_CAP], sm_red[4];
     const int b = blockIdx.y, h = blockIdx.x;
     const int kvl = kv_len[b];
     const int pos = kvl - 1;
@@ -344,6 +350,39 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
     const int first_split = k_first / SPLIT;
     const int n_splits = (kvl + SPLIT - 1) / SPLIT;
     const int64_t base = ((int64_t)b * nh + h) * max_splits;
+    const int t = q_start[b];
+    const int n = n_splits - first_split;
+    if (n <= MERGE_CAP) {
+        const float2* ml = reinterpret_cast<const float2*>(part_ml) + base + first_split;
+        float mx = -INFINITY;
+        for (int s = threadIdx.x; s < n; s += blockDim.x) {
+            const float2 v = ml[s];
+            sm_w[s] = v.x;
+            sm_l[s] = v.y;
+            mx = fmaxf(mx, v.x);
+        }
+        mx = warp_max(mx);
+        if ((threadIdx.x & 31) == 0) sm_red[threadIdx.x >> 5] = mx;
+        __syncthreads();
+        float m_all = -INFINITY;
+        for (int w = 0; w < (int)(blockDim.x + 31) / 32; ++w) m_all = fmaxf(m_all, sm_red[w]);
+        for (int s = threadIdx.x; s < n; s += blockDim.x) {
+            const float m = sm_w[s];
+            sm_w[s] = m == -INFINITY ? 0.f : expf(m - m_all);
+        }
+        __syncthreads();
+        float l = 0.f;
+        for (int s = 0; s < n; ++s) l += sm_w[s] * sm_l[s];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const float* po = part_o + (base + first_split) * D;
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            float o = 0.f;
+#pragma unroll 4
+            for (int s = 0; s < n; ++s) o += sm_w[s] * po[(int64_t)s * D + c];
+            out[((int64_t)t * nh + h) * D + c] = from_float<AT>(o * inv);
+        }
+        return;
+    }
     float m_all = -INFINITY;
     for (int s = first_split; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(base + s) * 2]);
     float l = 0.f;
@@ -352,7 +391,6 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
         l += (m == -INFINITY ? 0.f : expf(m - m_all)) * part_ml[(base + s) * 2 + 1];
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    const int t = q_start[b];
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float o = 0.f;
         for (int s = first_split; s < n_splits; ++s) {

@@ -422,6 +422,121 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv_perm
     }
 }
 
+// ---------------------------------------------------------------------------
+// The expert combine and the residual addition and RMSNorm that follow it, in one pass over a row:
+//   delta[t, :] = sum_k w[t, k] * y[inv_perm[t*K + k], :] + gate[t] * shared[t, :]   (as moe_combine)
+//   hidden[t, :] += delta[t, :];  out = hidden * rsqrt(mean(hidden^2) + eps) * weight  (as add_rmsnorm)
+// The additions run in the order of the two separate kernels, so the result is theirs bit for bit.
+// ---------------------------------------------------------------------------
+struct CombineArgs {
+    const float* y;
+    const int* inv_perm;
+    const float* w;
+    const float* shared;
+    const float* gate;
+    int K;
+};
+
+template <typename AT, typename WT>
+__global__ void combine_add_rmsnorm_kernel(float* __restrict__ hidden, CombineArgs ca, const int* __restrict__ rows,
+                                           const WT* __restrict__ weight, AT* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* h = hidden + (int64_t)src * H;
+    AT* o = out + (int64_t)r * H;
+    const float gt = ca.shared ? ca.gate[src] : 0.f;
+    auto delta = [&](int i) {
+        float acc = 0.f;
+        for (int k = 0; k < ca.K; ++k) {
+            const int yr = ca.inv_perm ? ca.inv_perm[src * ca.K + k] : src * ca.K + k;
+            acc += ca.w[src * ca.K + k] * ca.y[(int64_t)yr * H + i];
+        }
+        if (ca.shared) acc += gt * ca.shared[(int64_t)src * H + i];
+        return acc;
+    };
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = h[i] + delta(i);
+        if (!rows) h[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rrms = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = rows ? h[i] + delta(i) : h[i];
+        o[i] = from_float<AT>(v * rrms * to_float(weight[i]));
+    }
+}
+
+template <typename AT, typename WT, int VPT>
+__global__ void __launch_bounds__(256)
+combine_add_rmsnorm_vec_kernel(float* __restrict__ hidden, CombineArgs ca, const int* __restrict__ rows,
+                               const WT* __restrict__ weight, AT* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float4* h = reinterpret_cast<float4*>(hidden + (int64_t)src * H);
+    const int nv = H >> 2;
+    float4 v[VPT], acc[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < ca.K; ++k) {
+        const int yr = ca.inv_perm ? ca.inv_perm[src * ca.K + k] : src * ca.K + k;
+        const float wk = ca.w[src * ca.K + k];
+        const float4* yv = reinterpret_cast<const float4*>(ca.y + (int64_t)yr * H);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < nv) {
+                const float4 t = yv[i];
+                acc[j].x += wk * t.x; acc[j].y += wk * t.y; acc[j].z += wk * t.z; acc[j].w += wk * t.w;
+            }
+        }
+    }
+    if (ca.shared) {
+        const float gt = ca.gate[src];
+        const float4* sv = reinterpret_cast<const float4*>(ca.shared + (int64_t)src * H);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < nv) {
+                const float4 t = sv[i];
+                acc[j].x += gt * t.x; acc[j].y += gt * t.y; acc[j].z += gt * t.z; acc[j].w += gt * t.w;
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nv) {
+            v[j] = h[i];
+            v[j].x += acc[j].x; v[j].y += acc[j].y; v[j].z += acc[j].z; v[j].w += acc[j].w;
+            if (!rows) h[i] = v[j];
+            ss += v[j].x * v[j].x;
+            ss += v[j].y * v[j].y;
+            ss += v[j].z * v[j].z;
+            ss += v[j].w * v[j].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rrms = rsqrtf(ss / (float)H + eps);
+    AT* o = out + (int64_t)r * H;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < nv) {
+            const int c = 4 * i;
+            o[c] = from_float<AT>(v[j].x * rrms * to_float(weight[c]));
+            o[c + 1] = from_float<AT>(v[j].y * rrms * to_float(weight[c + 1]));
+            o[c + 2] = from_float<AT>(v[j].z * rrms * to_float(weight[c + 2]));
+            o[c + 3] = from_float<AT>(v[j].w * rrms * to_float(weight[c + 3]));
+        }
+    }
+}
+
 }  // namespace mi
 
 using namespace mi;
@@ -466,6 +581,38 @@ int mi_add_rmsnorm(float* hidden, const float* delta, const int* rows, const voi
         add_rmsnorm_kernel<AT, WT><<<n_rows, threads, 0, stream>>>(
             hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
     return finish_launch("add_rmsnorm");
+}
+
+// The expert combine (arguments as mi_moe_combine, rows of `y` indexed through `inv_perm` or by pair)
+// fused with the residual addition and RMSNorm that follow (arguments as mi_add_rmsnorm).
+int mi_combine_add_rmsnorm(float* hidden, const float* y, const int* inv_perm, const float* w, const float* shared,
+                           const float* gate, int K, const int* rows, const void* weight, int wdtype, void* out,
+                           int adtype, int n_rows, int H, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return kOk;
+    const CombineArgs ca{y, inv_perm, w, shared, gate, K};
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(y) |
+                           reinterpret_cast<uintptr_t>(shared)) & 15) == 0;
+    if (H % 4 == 0 && H >= 1024 && H <= 8192 && aligned) {
+        if (H <= 2048) {
+            MI_DISPATCH_2(adtype, AT, wdtype, WT,
+                combine_add_rmsnorm_vec_kernel<AT, WT, 2><<<n_rows, 256, 0, stream>>>(
+                    hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+        } else if (H <= 4096) {
+            MI_DISPATCH_2(adtype, AT, wdtype, WT,
+                combine_add_rmsnorm_vec_kernel<AT, WT, 4><<<n_rows, 256, 0, stream>>>(
+                    hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+        } else {
+            MI_DISPATCH_2(adtype, AT, wdtype, WT,
+                combine_add_rmsnorm_vec_kernel<AT, WT, 8><<<n_rows, 256, 0, stream>>>(
+                    hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+        }
+        return finish_launch("combine_add_rmsnorm");
+    }
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        combine_add_rmsnorm_kernel<AT, WT><<<n_rows, threads, 0, stream>>>(
+            hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+    return finish_launch("combine_add_rmsnorm");
 }
 
 int mi_qkv_post(const float* qkv, const void* bias, int wdtype, const int* positions, const float* inv_freq,

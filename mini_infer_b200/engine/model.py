@@ -17,7 +17,8 @@ import torch
 from ..cache.manager import KVGroupSpec, plan_groups
 from ..config.registry import part_class
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import (BuiltLayer, CacheBinding, KVNeed, Part, Runtime, StateNeed, StepContext, TensorDecl)
+from ..parts.base import (BuiltLayer, CacheBinding, KVNeed, Part, Runtime, StateNeed, StepContext, TensorDecl,
+                          apply_norm, resolve)
 
 
 def _make(category: str, spec: PartSpec, prefix: str) -> Part:
@@ -137,10 +138,12 @@ class Model:
         pending = None
         for pos, e in enumerate(self.spec.schedule):
             layer = self.layers[e.layer]
+            if not layer.block.accepts_deferred:
+                pending = resolve(pending)
             pending = layer.block.forward(layer, hidden, pending, ctx, self.bindings[pos])
         if logit_rows is None or logit_rows.numel() == 0:
             return None
-        x = self.final_norm.apply(hidden, pending, rows=logit_rows)
+        x = apply_norm(self.final_norm, hidden, pending, rows=logit_rows)
         return self.lm_head.forward(x)
 
 

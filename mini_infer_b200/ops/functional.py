@@ -174,6 +174,37 @@ def moe_combine(y: torch.Tensor, inv_perm: Optional[torch.Tensor], weights: torc
     return out
 
 
+def combine_add_rmsnorm(hidden: torch.Tensor, y: torch.Tensor, inv_perm: Optional[torch.Tensor],
+                        weights: torch.Tensor, shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                        norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                        rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`moe_combine` and the :func:`add_rmsnorm` that takes its result as ``delta``, in one kernel:
+    the combined rows are added to ``hidden`` (written back unless ``rows``) and normalised without
+    ever being stored.  Bit for bit the result of the two separate calls."""
+    _chk(hidden, "combine_add_rmsnorm hidden", F32)
+    T, H = hidden.shape
+    if weights.shape[0] != T:
+        raise ValueError("combine_add_rmsnorm: one row of expert weights per row of hidden")
+    K = weights.shape[1]
+    _chk(y, "combine_add_rmsnorm y", F32, (T * K, H))
+    _chk(inv_perm, "combine_add_rmsnorm inv_perm", I32)
+    _chk(weights, "combine_add_rmsnorm weights", F32)
+    _chk(shared, "combine_add_rmsnorm shared", F32, (T, H))
+    _chk(gate, "combine_add_rmsnorm gate", F32, (T,))
+    if (shared is None) != (gate is None):
+        raise ValueError("combine_add_rmsnorm: shared output and gate come together")
+    _chk(norm_weight, "combine_add_rmsnorm weight", None, (H,))
+    _chk(rows, "combine_add_rmsnorm rows", I32)
+    n = T if rows is None else rows.numel()
+    out = torch.empty(n, H, dtype=out_dtype, device=hidden.device)
+    check(library().mi_combine_add_rmsnorm(_ptr(hidden), _ptr(y), _ptr(inv_perm), _ptr(weights), _ptr(shared),
+                                           _ptr(gate), K, _ptr(rows), _ptr(norm_weight),
+                                           _code(norm_weight, "combine_add_rmsnorm weight"), _ptr(out),
+                                           _code(out, "combine_add_rmsnorm out"), n, H, float(eps), _stream()),
+          "combine_add_rmsnorm")
+    return out
+
+
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
               q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int, window: int = 0,
               scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:

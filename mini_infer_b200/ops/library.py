@@ -25,6 +25,7 @@ _SIGNATURES = {
     "mi_qkv_post": [P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "mi_swiglu": [P, P, I, L, I, P],
     "mi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
+    "mi_combine_add_rmsnorm": [P, P, P, P, P, P, I, P, P, I, P, I, I, I, F, P],
     "mi_attn_tiled": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode_split": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],

@@ -202,12 +202,50 @@ class Part:
         self.rt = rt
 
 
+class Deferred:
+    """A part's output that has not been written out yet.  A consumer that can fold the computation
+    into its own kernel says so with ``accepts_deferred`` and is handed the object; every other consumer
+    gets the tensor (:func:`resolve`)."""
+
+    def materialize(self) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass
+class WeightedRowSum(Deferred):
+    """``out[t] = sum_k weights[t, k] * rows[index[t, k]] + scale[t] * extra[t]`` (float32; without
+    ``index`` the rows are taken in order, ``rows[t * K + k]``; ``extra`` and ``scale`` come together
+    or not at all)."""
+
+    rows: torch.Tensor
+    index: Optional[torch.Tensor]
+    weights: torch.Tensor
+    extra: Optional[torch.Tensor]
+    scale: Optional[torch.Tensor]
+
+    def materialize(self) -> torch.Tensor:
+        from ..ops import functional as F
+        return F.moe_combine(self.rows, self.index, self.weights, self.extra, self.scale)
+
+
+def resolve(pending):
+    return pending.materialize() if isinstance(pending, Deferred) else pending
+
+
 class Norm(Part):
     category = "norm"
+    accepts_deferred = False    # True: ``apply`` takes a Deferred as ``delta``
 
     def apply(self, hidden: torch.Tensor, delta: Optional[torch.Tensor],
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
+
+
+def apply_norm(norm: "Norm", hidden: torch.Tensor, pending, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``norm.apply`` with a pending output that may be deferred."""
+    if isinstance(pending, Deferred) and not norm.accepts_deferred:
+        pending = pending.materialize()
+    return norm.apply(hidden, pending, rows)
 
 
 class PositionEncoding(Part):
@@ -234,6 +272,10 @@ class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_deferred(self, x: torch.Tensor, ctx: StepContext):
+        """As ``forward``, but the result may be a :class:`Deferred` whose last step the consumer runs."""
+        return self.forward(x, ctx)
+
 
 class Embedding(Part):
     category = "embedding"
@@ -251,6 +293,7 @@ class LMHead(Part):
 
 class Block(Part):
     category = "block"
+    accepts_deferred = False    # True: ``forward`` takes a Deferred as ``pending`` and may return one
 
     def forward(self, layer: "BuiltLayer", hidden: torch.Tensor, pending: Optional[torch.Tensor],
                 ctx: StepContext, cache: CacheBinding) -> torch.Tensor:

@@ -4,7 +4,9 @@
 (src/model/transformer_model.h:25-28, src/model/transformer_model.cpp:578-641).
 The residual stream ``hidden`` is float32 in both precision paths.  A part's
 output is not added at once: it travels as ``pending`` to the next norm, whose
-kernel adds it while it reads the row anyway.
+kernel adds it while it reads the row anyway.  A feed-forward may even leave its last
+step (the weighted sum of its experts' rows) to that kernel: ``pending`` is then a
+``Deferred``.
 """
 
 from __future__ import annotations
@@ -16,18 +18,18 @@ import torch
 from ..config.registry import register_part
 from ..ops import functional as F
 from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl,
-                   linear)
+                   apply_norm, linear)
 
 
 class PreNormResidual(Block):
     graph_safe = True
+    accepts_deferred = True
 
-    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending: Optional[torch.Tensor],
-                ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
-        x = layer.mixer_norm.apply(hidden, pending)
+    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, cache: CacheBinding):
+        x = apply_norm(layer.mixer_norm, hidden, pending)
         y = layer.mixer.forward(x, ctx, cache)
-        x = layer.feed_forward_norm.apply(hidden, y)
-        return layer.feed_forward.forward(x, ctx)
+        x = apply_norm(layer.feed_forward_norm, hidden, y)
+        return layer.feed_forward.forward_deferred(x, ctx)
 
 
 class TokenEmbedding(Embedding):

@@ -15,7 +15,7 @@ import torch
 
 from ..config.registry import register_part
 from ..ops import functional as F
-from .base import FeedForward, Runtime, StepContext, TensorDecl, linear, linear_swiglu
+from .base import FeedForward, Runtime, StepContext, TensorDecl, WeightedRowSum, linear, linear_swiglu
 
 
 class SwiGLUMLP(FeedForward):
@@ -147,6 +147,11 @@ class SparseMoE(FeedForward):
         return side, shared
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return self.forward_deferred(x, ctx).materialize()
+
+    def forward_deferred(self, x: torch.Tensor, ctx: StepContext) -> WeightedRowSum:
+        """Everything but the weighted sum of the experts' rows (and of the shared expert's): the
+        norm that follows forms it inside its own kernel."""
         T = x.shape[0]
         shared = side = inv_perm = None
         overlap = self.sI > 0 and self.OVERLAP_SHARED_EXPERT
@@ -193,7 +198,7 @@ class SparseMoE(FeedForward):
             torch.cuda.current_stream().wait_stream(side)
         elif self.sI > 0:
             shared = self._shared_expert(x)
-        return F.moe_combine(y, inv_perm, w, shared, gate)
+        return WeightedRowSum(y, inv_perm, w, shared, gate if shared is not None else None)
 
 
 register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)

@@ -12,13 +12,14 @@ import torch
 
 from ..config.registry import register_part
 from ..ops import functional as F
-from .base import Norm, Runtime, TensorDecl
+from .base import Deferred, Norm, Runtime, TensorDecl, WeightedRowSum
 
 
 class RMSNorm(Norm):
     """params: ``size``, ``eps``.  Tensor: ``<prefix>weight [size]``."""
 
     graph_safe = True
+    accepts_deferred = True
 
     def tensor_decls(self) -> List[TensorDecl]:
         return [TensorDecl(self.prefix + "weight", (self.params["size"],), "norm")]
@@ -30,6 +31,12 @@ class RMSNorm(Norm):
 
     def apply(self, hidden: torch.Tensor, delta: Optional[torch.Tensor],
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if isinstance(delta, WeightedRowSum):
+            # the sum is formed row by row inside the norm's kernel and never written out
+            return F.combine_add_rmsnorm(hidden, delta.rows, delta.index, delta.weights, delta.extra, delta.scale,
+                                         self.weight, self.eps, self.rt.act, rows)
+        if isinstance(delta, Deferred):
+            delta = delta.materialize()
         return F.add_rmsnorm(hidden, delta, self.weight, self.eps, self.rt.act, rows)
 
 

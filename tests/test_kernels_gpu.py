@@ -137,6 +137,30 @@ def test_moe_combine():
     close(out2, (w[:, :, None] * y[perm.long()].view(T, K, H)).sum(1), 2e-6)
 
 
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("T,K,H", [(6, 3, 100), (9, 4, 2048), (5, 2, 3584), (3, 8, 8192), (4, 1, 1028)])
+@pytest.mark.parametrize("indexed,with_extra", [(True, True), (False, True), (True, False)])
+def test_combine_add_rmsnorm_is_the_two_kernels(adt, wdt, T, K, H, indexed, with_extra):
+    """The fused kernel adds in the order of moe_combine followed by add_rmsnorm: same bits, in hidden
+    and in the normalised rows, for whole steps and for selected rows."""
+    y = rnd(T * K, H, seed=1)
+    w = rnd(T, K, seed=2).abs()
+    perm = torch.randperm(T * K, generator=torch.Generator().manual_seed(1)).to(torch.int32).to(DEV) if indexed else None
+    shared = rnd(T, H, seed=3) if with_extra else None
+    gate = torch.sigmoid(rnd(T, seed=4)) if with_extra else None
+    nw = (1.0 + 0.1 * rnd(H, seed=5)).to(wdt)
+    h0 = rnd(T, H, seed=6)
+    h_ref, h_got = h0.clone(), h0.clone()
+    ref = F().add_rmsnorm(h_ref, F().moe_combine(y, perm, w, shared, gate), nw, 1e-5, adt)
+    got = F().combine_add_rmsnorm(h_got, y, perm, w, shared, gate, nw, 1e-5, adt)
+    assert torch.equal(got, ref) and torch.equal(h_got, h_ref) and not torch.equal(h_got, h0)
+    rows = torch.tensor([T - 1, 0, T - 1], dtype=torch.int32, device=DEV)
+    h_ref, h_got = h0.clone(), h0.clone()
+    ref = F().add_rmsnorm(h_ref, F().moe_combine(y, perm, w, shared, gate), nw, 1e-5, adt, rows)
+    got = F().combine_add_rmsnorm(h_got, y, perm, w, shared, gate, nw, 1e-5, adt, rows)
+    assert torch.equal(got, ref) and torch.equal(h_got, h0)
+
+
 # --------------------------------------------------------------------------- #
 # attention
 # --------------------------------------------------------------------------- #

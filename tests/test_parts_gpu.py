@@ -152,6 +152,39 @@ def test_sparse_moe_part(dtype, E, K, mI, sI, norm):
     close(out, ref, TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_deferred_sum_of_the_experts_rows(dtype):
+    """The experts' weighted sum may be left to the norm that follows: the same bits as summing first,
+    through the framework's RMSNorm (which folds it into its kernel) and through a norm that knows
+    nothing of deferred outputs (which is handed the tensor)."""
+    from mini_infer_b200.config import part_class
+    from mini_infer_b200.parts import Deferred, Norm, WeightedRowSum, apply_norm, resolve
+    rt = runtime(dtype)
+    H, T = 104, 21
+    moe = part_class("feed_forward", "sparse_moe")({
+        "hidden_size": H, "num_experts": 6, "top_k": 3, "expert_intermediate_size": 48,
+        "shared_intermediate_size": 80, "norm_topk_prob": True}, "f.")
+    moe.load(random_tensors(moe, 5, rt.act), rt)
+    norm = part_class("norm", "rmsnorm")({"size": H, "eps": 1e-6}, "n.")
+    norm.load(random_tensors(norm, 1, rt.act), rt)
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(6)).to(rt.act).to(DEV)
+    plain = moe.forward(x, None)
+    later = moe.forward_deferred(x, None)
+    assert isinstance(later, WeightedRowSum) and isinstance(later, Deferred)
+    assert torch.equal(resolve(later), plain) and resolve(plain) is plain
+    h0 = torch.randn(T, H, device=DEV)
+    h1, h2 = h0.clone(), h0.clone()
+    assert norm.accepts_deferred
+    assert torch.equal(apply_norm(norm, h1, later), norm.apply(h2, plain)) and torch.equal(h1, h2)
+
+    class PlainNorm(Norm):
+        def apply(self, hidden, delta, rows=None):
+            assert isinstance(delta, torch.Tensor)
+            return hidden + delta
+
+    assert torch.equal(apply_norm(PlainNorm({}, ""), h0, later), h0 + plain)
+
+
 def test_embedding_and_head_parts():
     from mini_infer_b200.config import part_class
     rt = runtime("bfloat16")

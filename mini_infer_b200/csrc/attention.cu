@@ -222,6 +222,13 @@ template <int E> struct RawVec<__nv_bfloat16, E> {
     }
 };
 
+// Splits of a request with `kvl` keys: SPLIT keys each; a tail of up to a quarter of a split joins
+// the split before it instead of making a block of its own.  A function of the request's own length only.
+template <int SPLIT>
+__device__ __forceinline__ int decode_splits(int kvl) {
+    return max(1, (kvl + SPLIT - SPLIT / 4 - 1) / SPLIT);
+}
+
 constexpr int DEC_SPLIT = 512;      // keys per split by default; smaller splits spread one or two requests over the device
 constexpr int DEC_GROUPS = 16;
 
@@ -238,8 +245,8 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     const int pos = kvl - 1;
     int k_first = 0;
     if (window > 0) k_first = max(0, pos - window + 1);
-    const int first_split = k_first / SPLIT;
-    const int n_splits = (kvl + SPLIT - 1) / SPLIT;
+    const int n_splits = decode_splits<SPLIT>(kvl);
+    const int first_split = min(k_first / SPLIT, n_splits - 1);
     if (sp < first_split || sp >= n_splits) return;
     const int hk = h / (nh / nkv);
     const int tid = threadIdx.x, grp = tid >> 3, sub = tid & 7;
@@ -254,13 +261,15 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     float acc[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) acc[i] = 0.f;
+    constexpr int SPAN = SPLIT + SPLIT / 4;                   // the last split may hold a short tail too
     const int k_lo = max(sp * SPLIT, k_first);
-    const int k_hi = min(kvl, (sp + 1) * SPLIT);
+    const int k_hi = sp == n_splits - 1 ? kvl : (sp + 1) * SPLIT;
+    const int span = k_hi - sp * SPLIT;
     // the pages of this split, looked up once
-    __shared__ int64_t key_off[SPLIT];
+    __shared__ int64_t key_off[SPAN];
     {
         const int* table = block_table + (int64_t)b * max_pages;
-        for (int i = tid; i < SPLIT; i += 128) {
+        for (int i = tid; i < span; i += 128) {
             const int kj = sp * SPLIT + i;
             int64_t off = -1;
             if (kj >= k_lo && kj < k_hi) {
@@ -274,13 +283,13 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     // KPR keys per round: all their loads are issued before any is used
     constexpr int KPR = (sizeof(AT) == 2 || E <= 16) ? 4 : 2;
     using Raw = RawVec<AT, E>;
-    for (int i0 = grp; i0 < SPLIT; i0 += KPR * DEC_GROUPS) {
+    for (int i0 = grp; i0 < span; i0 += KPR * DEC_GROUPS) {
         int64_t off[KPR];
         Raw kr[KPR], vr[KPR];
 #pragma unroll
         for (int u = 0; u < KPR; ++u) {
             const int i = i0 + u * DEC_GROUPS;
-            off[u] = i < SPLIT ? key_off[i] : -1;
+            off[u] = i < span ? key_off[i] : -1;
             if (off[u] >= 0) { kr[u].load(k_cache + off[u] + sub * E); vr[u].load(v_cache + off[u] + sub * E); }
         }
 #pragma unroll
@@ -347,8 +356,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
     const int pos = kvl - 1;
     int k_first = 0;
     if (window > 0) k_first = max(0, pos - window + 1);
-    const int first_split = k_first / SPLIT;
-    const int n_splits = (kvl + SPLIT - 1) / SPLIT;
+    const int n_splits = decode_splits<SPLIT>(kvl);
+    const int first_split = min(k_first / SPLIT, n_splits - 1);
     const int64_t base = ((int64_t)b * nh + h) * max_splits;
     const int t = q_start[b];
     const int n = n_splits - first_split;

@@ -262,9 +262,11 @@ def decode_scratch(B, nh, max_kv, d):
 
 @pytest.mark.parametrize("adt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,d", [(4, 2, 64), (3, 3, 128), (7, 1, 128), (2, 1, 256)])
-@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("window", [0, 100, 5])
 def test_decode_attention(adt, nh, nkv, d, window):
-    kv = [1, 255, 256, 257, 700, 1030, 16]
+    # lengths around the splits' edges: a tail of up to a quarter of a split joins the split before it
+    # (1030 = 2 x 512 + 6, 640 = 512 + 128, 161 = 128 + 33), and a window of 5 lies inside such a tail
+    kv = [1, 255, 256, 257, 700, 1030, 16, 640, 641, 160, 161]
     case = paged_case(kv, [1] * len(kv), nh, nkv, d, 16, adt, seed=nh)
     po, pml, splits = decode_scratch(len(kv), nh, max(kv), d)
     out = F().decode_attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"],

@@ -435,6 +435,141 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
     permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + E, T * K, E, K, 3);
 }
 
+// The same with the residual addition and RMSNorm that precede the router folded in, for the
+// smallest steps: every block of a token forms v = hidden[t] + delta[t] and its RMS itself (the
+// additions in the order of add_rmsnorm's vector kernel), takes its logit from the normalised row
+// rounded to the activation type, and the block that finishes the token last writes hidden[t] and
+// the normalised row x_out[t] for the kernels that follow: by then no block reads hidden[t] any more.
+// H is a multiple of 4 of at most 4 * 8 * 256.
+// four consecutive elements of a row, held as loaded and widened when used
+template <typename T4> struct Row4;
+template <> struct Row4<float> {
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = __ldg(reinterpret_cast<const float4*>(p)); }
+    __device__ __forceinline__ void get(float (&o)[4]) const { o[0] = raw.x; o[1] = raw.y; o[2] = raw.z; o[3] = raw.w; }
+};
+template <> struct Row4<__nv_bfloat16> {
+    uint2 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = __ldg(reinterpret_cast<const uint2*>(p)); }
+    __device__ __forceinline__ void get(float (&o)[4]) const {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+    }
+};
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+
+constexpr int NR_VMAX = 8;
+
+template <typename AT, typename WT, typename NT>
+__global__ void __launch_bounds__(256)
+moe_norm_route_small_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
+                            const NT* __restrict__ norm_w, float eps, AT* __restrict__ x_out,
+                            const WT* __restrict__ wr, const WT* __restrict__ wsg, float* __restrict__ z,
+                            unsigned* __restrict__ tickets, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                            float* __restrict__ gate, float* __restrict__ probs_out, int* __restrict__ offsets,
+                            int* __restrict__ sorted_token, int* __restrict__ inv_perm, int T, int H, int E, int K,
+                            int norm_topk) {
+    extern __shared__ int route_sh[];  // select: [E] floats; then permute: [E+1] + [T*K] ints
+    __shared__ bool last;
+    __shared__ float scratch[32], part[8];
+    const int t = blockIdx.y, e = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nv = H >> 2;
+    float4* h4 = reinterpret_cast<float4*>(hidden + (int64_t)t * H);
+    const float4* d4 = delta ? reinterpret_cast<const float4*>(delta + (int64_t)t * H) : nullptr;
+    const int ncols = E + (wsg ? 1 : 0);
+    const WT* w = e < E ? wr + (int64_t)e * H : wsg;
+    float4 v[NR_VMAX];
+    Row4<NT> nrow[NR_VMAX];                                  // fetched before the sum of squares is known
+    Row4<WT> wrow[NR_VMAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NR_VMAX; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nv) {
+            nrow[j].load(norm_w + 4 * i);
+            wrow[j].load(w + 4 * i);
+            v[j] = h4[i];
+            if (d4) {
+                const float4 dv = d4[i];
+                v[j].x += dv.x; v[j].y += dv.y; v[j].z += dv.z; v[j].w += dv.w;
+            }
+            ss += v[j].x * v[j].x;
+            ss += v[j].y * v[j].y;
+            ss += v[j].z * v[j].z;
+            ss += v[j].w * v[j].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rrms = rsqrtf(ss / (float)H + eps);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < NR_VMAX; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < nv) {
+            float nw[4], ww[4];
+            nrow[j].get(nw);
+            wrow[j].get(ww);
+            // the row as the following kernels will read it: rounded to the activation type
+            acc += to_float(from_float<AT>(v[j].x * rrms * nw[0])) * ww[0];
+            acc += to_float(from_float<AT>(v[j].y * rrms * nw[1])) * ww[1];
+            acc += to_float(from_float<AT>(v[j].z * rrms * nw[2])) * ww[2];
+            acc += to_float(from_float<AT>(v[j].w * rrms * nw[3])) * ww[3];
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float zz = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) zz += part[wv];
+        z[(int64_t)t * ncols + e] = zz;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&tickets[1 + t], 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x == 0) tickets[1 + t] = 0u;
+    AT* xo = x_out + (int64_t)t * H;
+#pragma unroll
+    for (int j = 0; j < NR_VMAX; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < nv) {
+            if (d4) h4[i] = v[j];
+            float nw[4];
+            nrow[j].get(nw);
+            const float xs[4] = {v[j].x * rrms * nw[0], v[j].y * rrms * nw[1], v[j].z * rrms * nw[2],
+                                 v[j].w * rrms * nw[3]};
+            store4(xo + 4 * i, xs);
+        }
+    }
+    if (threadIdx.x < 32)
+        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, reinterpret_cast<float*>(route_sh),
+                            nullptr, t, E, K, norm_topk);
+    if (!offsets) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&tickets[0], 1u) == (unsigned)T - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x == 0) tickets[0] = 0u;
+    permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + E, T * K, E, K, 3);
+}
+
 // For many rows: one block per expert, no atomics and no scratch.  A warp owns a contiguous run of
 // pairs.  Pass 1 counts, per warp, the block's own pairs and the pairs of lower experts (their total
 // is the expert's first place); a scan over the warps gives every warp its first place; pass 2 places
@@ -659,6 +794,67 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
             offsets, sorted_token, inv_perm, T, H, E, K, norm_topk));
 #undef MI_ROUTE_ATTR
     return finish_launch("moe_route_small");
+}
+
+// mi_moe_route_small with the residual addition and RMSNorm before it in the same launch:
+// hidden [T, H] float (+= delta if given), x_out [T, H] of type `adtype` receives the normalised rows.
+// ndtype: type of the norm's weights.  Takes H % 4 == 0, H <= mi_moe_norm_route_small_max_width().
+int mi_moe_norm_route_small_max_width() { return 4 * NR_VMAX * 256; }
+
+int mi_moe_norm_route_small(float* hidden, const float* delta, const void* norm_w, int ndtype, float eps,
+                            void* x_out, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
+                            unsigned* tickets, int* topk_idx, float* topk_w, float* gate, float* probs_out,
+                            int* offsets, int* sorted_token, int* inv_perm, int T, int H, int E, int K,
+                            int norm_topk, cudaStream_t stream) {
+    if (T <= 0) return kOk;
+    if (T > mi_moe_route_small_max_tokens()) {
+        set_last_error("router (decode): %d tokens, takes at most %d", T, mi_moe_route_small_max_tokens());
+        return kBadShape;
+    }
+    if (K < 1 || K > 32 || K > E) {
+        set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
+        return kBadShape;
+    }
+    if (H % 4 != 0 || H > mi_moe_norm_route_small_max_width() ||
+        ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(x_out) |
+          reinterpret_cast<uintptr_t>(norm_w) | reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(wsg)) & 15)) {
+        set_last_error("router with norm: width %d must be a multiple of 4 of at most %d and all rows 16-byte aligned",
+                       H, mi_moe_norm_route_small_max_width());
+        return kBadShape;
+    }
+    const size_t smem = sizeof(float) * (size_t)E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
+    if (smem > 160 * 1024 || E + 1 > 65535) {
+        set_last_error("router (decode): %d experts exceed the shared memory of a block", E);
+        return kBadShape;
+    }
+    const int ncols = E + (wsg ? 1 : 0);
+    const dim3 grid(ncols, T);
+#define MI_NR_LAUNCH(AT, WT, NT)                                                                                 \
+    do {                                                                                                         \
+        if (smem > 48 * 1024)                                                                                    \
+            cudaFuncSetAttribute(moe_norm_route_small_kernel<AT, WT, NT>,                                        \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
+        moe_norm_route_small_kernel<AT, WT, NT><<<grid, 256, smem, stream>>>(                                    \
+            hidden, delta, (const NT*)norm_w, eps, (AT*)x_out, (const WT*)wr, (const WT*)wsg, z_scratch,         \
+            tickets, topk_idx, topk_w, gate, probs_out, offsets, sorted_token, inv_perm, T, H, E, K, norm_topk); \
+    } while (0)
+    const int combo = adtype * 4 + wdtype * 2 + ndtype;
+    if (adtype < 0 || adtype > 1 || wdtype < 0 || wdtype > 1 || ndtype < 0 || ndtype > 1) {
+        set_last_error("router with norm: unknown dtype code");
+        return kBadDType;
+    }
+    switch (combo) {
+        case 0: MI_NR_LAUNCH(float, float, float); break;
+        case 4: MI_NR_LAUNCH(__nv_bfloat16, float, float); break;
+        case 5: MI_NR_LAUNCH(__nv_bfloat16, float, __nv_bfloat16); break;
+        case 6: MI_NR_LAUNCH(__nv_bfloat16, __nv_bfloat16, float); break;
+        case 7: MI_NR_LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16); break;
+        default:
+            set_last_error("router with norm: float activations want float weights");
+            return kBadDType;
+    }
+#undef MI_NR_LAUNCH
+    return finish_launch("moe_norm_route_small");
 }
 
 // `counts_scratch` is not used any more (the signature is kept).

@@ -240,6 +240,11 @@ class Norm(Part):
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def rms_parameters(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """``(weight, eps)`` if this norm is ``x * rsqrt(mean(x^2) + eps) * weight`` and nothing else, so
+        that the part that follows may run it inside a kernel of its own; None otherwise."""
+        return None
+
 
 def apply_norm(norm: "Norm", hidden: torch.Tensor, pending, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``norm.apply`` with a pending output that may be deferred."""
@@ -275,6 +280,11 @@ class FeedForward(Part):
     def forward_deferred(self, x: torch.Tensor, ctx: StepContext):
         """As ``forward``, but the result may be a :class:`Deferred` whose last step the consumer runs."""
         return self.forward(x, ctx)
+
+    def forward_from_residual(self, hidden: torch.Tensor, delta, norm: "Norm", ctx: StepContext):
+        """``forward_deferred(norm(hidden + delta))`` with ``hidden`` updated; a feed-forward may
+        override it to run the norm inside its first kernel."""
+        return self.forward_deferred(apply_norm(norm, hidden, delta), ctx)
 
 
 class Embedding(Part):

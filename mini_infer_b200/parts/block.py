@@ -28,8 +28,7 @@ class PreNormResidual(Block):
     def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, cache: CacheBinding):
         x = apply_norm(layer.mixer_norm, hidden, pending)
         y = layer.mixer.forward(x, ctx, cache)
-        x = apply_norm(layer.feed_forward_norm, hidden, y)
-        return layer.feed_forward.forward_deferred(x, ctx)
+        return layer.feed_forward.forward_from_residual(hidden, y, layer.feed_forward_norm, ctx)
 
 
 class TokenEmbedding(Embedding):

@@ -152,6 +152,23 @@ class SparseMoE(FeedForward):
     def forward_deferred(self, x: torch.Tensor, ctx: StepContext) -> WeightedRowSum:
         """Everything but the weighted sum of the experts' rows (and of the shared expert's): the
         norm that follows forms it inside its own kernel."""
+        return self._run(x, ctx, None)
+
+    def forward_from_residual(self, hidden: torch.Tensor, delta, norm, ctx: StepContext):
+        """The smallest steps run the residual addition, an RMSNorm and the routing in one launch
+        (the routing's blocks read the row anyway); the others take the norm's own kernel."""
+        T = hidden.shape[0]
+        rms = norm.rms_parameters()
+        if (rms is not None and self._skinny and T <= min(self._pairs_max, self.FORK_AFTER_ROUTING_MAX_TOKENS)
+                and T * self.K <= self.SKINNY_ROWS_PER_EXPERT * self.E and F.norm_route_small_takes(self.H)
+                and (delta is None or isinstance(delta, torch.Tensor))):
+            x, idx, w, gate, probs, _, _, _ = F.moe_norm_route_small(
+                hidden, delta, rms[0], rms[1], self.rt.act, self.w_router, self.w_shared_gate, self.K,
+                self.norm_topk, self._route_ticket, want_probs=self.keep_routing)
+            return self._run(x, ctx, (idx, w, gate, probs))
+        return super().forward_from_residual(hidden, delta, norm, ctx)
+
+    def _run(self, x: torch.Tensor, ctx: StepContext, routed) -> WeightedRowSum:
         T = x.shape[0]
         shared = side = inv_perm = None
         overlap = self.sI > 0 and self.OVERLAP_SHARED_EXPERT
@@ -162,9 +179,12 @@ class SparseMoE(FeedForward):
             fork_first = T > self.FORK_AFTER_ROUTING_MAX_TOKENS
             if overlap and fork_first:
                 side, shared = self._fork_shared_expert(x)
-            idx, w, gate, probs, _, _, _ = F.moe_route_small(
-                x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                want_probs=self.keep_routing, permute=False)
+            if routed is not None:
+                idx, w, gate, probs = routed
+            else:
+                idx, w, gate, probs, _, _, _ = F.moe_route_small(
+                    x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
+                    want_probs=self.keep_routing, permute=False)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
             act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True)

@@ -29,6 +29,9 @@ class RMSNorm(Norm):
         self.eps = float(self.params["eps"])
         self.weight = rt.precision.small(tensors[self.prefix + "weight"], rt.device)
 
+    def rms_parameters(self):
+        return self.weight, self.eps
+
     def apply(self, hidden: torch.Tensor, delta: Optional[torch.Tensor],
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         if isinstance(delta, WeightedRowSum):

@@ -554,6 +554,53 @@ def test_route_small_equals_router_and_permute(adt, wdt, T, E, K, norm):
         F().moe_route_small(rnd(n, H, dtype=adt), wr, wsg, K, norm, torch.zeros(1 + n, dtype=torch.int32, device=DEV))
 
 
+@pytest.mark.parametrize("adt,wdt,ndt", [(torch.float32, torch.float32, torch.float32),
+                                         (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                         (torch.bfloat16, torch.float32, torch.bfloat16),
+                                         (torch.bfloat16, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("T,H,E,K,gated,with_delta", [(1, 2048, 60, 4, True, True), (8, 2048, 60, 4, True, True),
+                                                      (5, 104, 6, 3, False, True), (3, 3584, 64, 8, True, False),
+                                                      (8, 8192, 9, 2, True, True), (2, 1028, 130, 8, False, True)])
+def test_norm_and_route_in_one_launch(adt, wdt, ndt, T, H, E, K, gated, with_delta):
+    """Residual addition, RMSNorm and routing of the smallest steps in one kernel against the separate
+    kernels: the same residual stream; the same normalised rows bit for bit where the norm's own kernel
+    adds in the same order (widths from 1024), within rounding otherwise; the routing of those rows."""
+    hidden = rnd(T, H, seed=T)
+    delta = rnd(T, H, seed=H) if with_delta else None
+    nw = (1.0 + 0.1 * rnd(H, seed=5)).to(ndt)
+    wr = rnd(E, H, dtype=wdt, scale=0.05, seed=K)
+    wsg = rnd(H, dtype=wdt, scale=0.05, seed=9) if gated else None
+    ticket = torch.zeros(1 + T, dtype=torch.int32, device=DEV)
+    h_ref = hidden.clone()
+    x_ref = F().add_rmsnorm(h_ref, delta, nw, 1e-5, adt)
+    r_idx, r_w, r_gate, r_probs, _, _, _ = F().moe_route_small(x_ref, wr, wsg, K, True, ticket, want_probs=True, permute=False)
+    for _ in range(2):                                                         # the ticket is left at zero
+        h = hidden.clone()
+        x, idx, w, gate, probs, offsets, _, _ = F().moe_norm_route_small(h, delta, nw, 1e-5, adt, wr, wsg, K, True,
+                                                                         ticket, want_probs=True)
+        assert int(ticket.abs().sum()) == 0 and offsets is None and x.dtype == adt
+        assert torch.equal(h, h_ref)
+        if H >= 1024:
+            assert torch.equal(x, x_ref)
+        else:
+            close(x, x_ref, 3e-6 if adt == torch.float32 else 8e-3, "normalised rows")
+        close(probs, r_probs, 2e-5 if H >= 1024 else 2e-3, "router probabilities")
+        s = torch.sort(r_probs, dim=-1, descending=True).values
+        clear = torch.ones(T, dtype=torch.bool, device=DEV)
+        for k in range(min(K, E - 1)):
+            clear &= (s[:, k] - s[:, k + 1]) > (1e-5 if H >= 1024 else 1e-3)
+        assert torch.equal(idx[clear], r_idx[clear])
+        close(w[clear], r_w[clear], 2e-5 if H >= 1024 else 2e-3, "router weights")
+        if gated:
+            close(gate, r_gate, 2e-5 if H >= 1024 else 2e-3, "shared gate")
+        else:
+            assert gate is None
+    from mini_infer_b200.ops.library import KernelError
+    with pytest.raises(KernelError, match="multiple of 4"):
+        F().moe_norm_route_small(rnd(2, 102), None, rnd(102), 1e-5, torch.float32, rnd(4, 102), None, 2, True,
+                                 torch.zeros(8, dtype=torch.int32, device=DEV))
+
+
 @pytest.mark.parametrize("T,E,K", [(1, 8, 2), (37, 6, 3), (300, 60, 4), (2048, 60, 4), (5, 130, 8), (700, 9, 3),
                                    (2100, 7, 1), (4099, 60, 4), (3001, 130, 8), (513, 64, 8)])
 def test_permute(T, E, K):

@@ -398,41 +398,43 @@ moe_permute_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets, 
     permute_block(topk_idx, offsets, sorted_token, inv_perm, sh, N, E, K, idx_in_smem);
 }
 
-// Routing of a decode-sized step in one launch: every block computes one logit (weight row, token).
-// No block waits for another: the block that finishes a token's row of logits last (a ticket
-// counter per token) selects that token's experts, and, if `offsets` is given, the block that
-// finishes the last token (one more counter) builds the permutation.  `tickets` holds 1 + T
-// counters that are zero before the launch and zero again after.
-template <typename AT, typename WT>
+// Routing of a decode-sized step in one launch: every block computes the logits of one weight row for
+// a group of TOK tokens (one token for the smallest steps, where more blocks mean less latency).
+// No block waits for another: the block that finishes a group's rows of logits last (a ticket
+// counter per group) selects those tokens' experts, a warp per token, and, if `offsets` is given, the
+// block that finishes the last group (one more counter) builds the permutation.  `tickets` holds
+// 1 + T counters that are zero before the launch and zero again after.
+template <typename AT, typename WT, int TOK>
 __global__ void __launch_bounds__(256)
 moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, const WT* __restrict__ wsg,
                        float* __restrict__ z, unsigned* __restrict__ tickets, int* __restrict__ topk_idx,
                        float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
                        int* __restrict__ offsets, int* __restrict__ sorted_token, int* __restrict__ inv_perm,
                        int T, int H, int E, int K, int norm_topk) {
-    extern __shared__ int route_sh[];  // select: [E] floats; then permute: [E+1] + [T*K] ints
+    extern __shared__ int route_sh[];  // select: [TOK][E] floats; then permute: [E+1] + [T*K] ints
     __shared__ bool last;
-    const int t = blockIdx.y;
-    router_logits_small_block<AT, WT, 1>(x, wr, wsg, z, T, H, E, blockIdx.x, t);
+    const int grp = blockIdx.y, t0 = grp * TOK;
+    router_logits_small_block<AT, WT, TOK>(x, wr, wsg, z, T, H, E, blockIdx.x, t0);
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(&tickets[1 + t], 1u) == gridDim.x - 1;
+    if (threadIdx.x == 0) last = atomicAdd(&tickets[1 + grp], 1u) == gridDim.x - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
-    if (threadIdx.x == 0) tickets[1 + t] = 0u;
-    if (threadIdx.x < 32)
-        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, reinterpret_cast<float*>(route_sh),
-                            nullptr, t, E, K, norm_topk);
+    if (threadIdx.x == 0) tickets[1 + grp] = 0u;
+    const int warp = threadIdx.x >> 5;
+    if (warp < TOK && t0 + warp < T)
+        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out,
+                            reinterpret_cast<float*>(route_sh) + warp * E, nullptr, t0 + warp, E, K, norm_topk);
     if (!offsets) return;
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(&tickets[0], 1u) == (unsigned)T - 1;
+    if (threadIdx.x == 0) last = atomicAdd(&tickets[0], 1u) == gridDim.y - 1;
     __syncthreads();
     if (!last) return;
     __threadfence();
     if (threadIdx.x == 0) tickets[0] = 0u;
-    permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + E, T * K, E, K, 3);
+    permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + TOK * E, T * K, E, K, 3);
 }
 
 // The same with the residual addition and RMSNorm that precede the router folded in, for the
@@ -776,23 +778,30 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
         set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
         return kBadShape;
     }
-    const size_t smem = sizeof(float) * (size_t)E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
+    // groups of four tokens from 33 tokens on: a weight row is then read once for four tokens
+    const int tok = T > 32 ? 4 : 1;
+    const size_t smem = sizeof(float) * (size_t)tok * E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
     if (smem > 160 * 1024 || E + 1 > 65535) {
         set_last_error("router (decode): %d experts exceed the shared memory of a block", E);
         return kBadShape;
     }
     const int ncols = E + (wsg ? 1 : 0);
-    const dim3 grid(ncols, T);
-#define MI_ROUTE_ATTR(AT, WT)                                                                             \
-    if (smem > 48 * 1024)                                                                                 \
-        cudaFuncSetAttribute(moe_route_small_kernel<AT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                             (int)smem)
-    MI_DISPATCH_2(adtype, AT, wdtype, WT,
-        MI_ROUTE_ATTR(AT, WT);
-        moe_route_small_kernel<AT, WT><<<grid, 256, smem, stream>>>(
-            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, tickets, topk_idx, topk_w, gate, probs_out,
-            offsets, sorted_token, inv_perm, T, H, E, K, norm_topk));
-#undef MI_ROUTE_ATTR
+    const dim3 grid(ncols, (T + tok - 1) / tok);
+#define MI_ROUTE_LAUNCH(AT, WT, TOK)                                                                           \
+    do {                                                                                                       \
+        if (smem > 48 * 1024)                                                                                  \
+            cudaFuncSetAttribute(moe_route_small_kernel<AT, WT, TOK>,                                          \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+        moe_route_small_kernel<AT, WT, TOK><<<grid, 256, smem, stream>>>(                                      \
+            (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, tickets, topk_idx, topk_w, gate, probs_out, \
+            offsets, sorted_token, inv_perm, T, H, E, K, norm_topk);                                           \
+    } while (0)
+    if (tok == 1) {
+        MI_DISPATCH_2(adtype, AT, wdtype, WT, MI_ROUTE_LAUNCH(AT, WT, 1));
+    } else {
+        MI_DISPATCH_2(adtype, AT, wdtype, WT, MI_ROUTE_LAUNCH(AT, WT, 4));
+    }
+#undef MI_ROUTE_LAUNCH
     return finish_launch("moe_route_small");
 }
 

@@ -5,8 +5,9 @@
 // (src/layers/moe.cpp:215-220), selects with one thread per token
 // (src/kernels/moe_kernel.cu:12-63), copies the indices to the host, runs every
 // used expert on all tokens and masks (src/layers/moe.cpp:239-270).  Here the
-// routing stays on the device: router logits are float dot products in a fixed
-// order per token, the (token, slot) pairs are sorted by expert with a stable
+// routing stays on the device: router logits are float sums in a fixed order per
+// token (float dot products; for large bfloat16 steps tensor-core products with
+// float accumulation), the (token, slot) pairs are sorted by expert with a stable
 // counting sort, and each expert multiplies only its own rows.
 
 #include "common.cuh"

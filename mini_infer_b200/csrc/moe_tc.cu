@@ -7,9 +7,11 @@
 // transposed: the expert's weights are the M operand (128 features per tile) and the rows are the
 // N operand, whose size follows the expert's row count (a multiple of 16 up to the tile limit TN of
 // 128 or 256 rows): an expert with 137 rows is one tile with N = 144 under TN = 256, or a tile of 128
-// and one of 16 under TN = 128, where two blocks share an SM.  One block computes one (expert, row
-// tile, feature tile) with two accumulators: gate and up of 128 features (mode 1), or two neighbouring
-// tiles of 128 features that share the row tile (mode 0):
+// and one of 16 under TN = 128, where two blocks share an SM.  Two families of kernels: the first
+// below computes one (expert, row tile, feature tile) per block; the persistent one further down
+// (the default) walks one block per SM over all of them.  Either way a tile has two accumulators,
+// gate and up of 128 features (mode 1), or one or two neighbouring tiles of 128 features that share
+// the row tile (mode 0), and three roles:
 //   warp 0    TMA producer: weight tile(s) (128 features x 64 k) and row tile (rows x 64 k)
 //   warp 1    allocates tensor memory, issues the MMAs, commits stages back to the producer
 //   warps 2-5 epilogue: accumulators -> registers -> SwiGLU / store, one TMEM lane quarter each

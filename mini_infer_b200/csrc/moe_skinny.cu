@@ -266,33 +266,56 @@ dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __
 // The pair-indexed grouped product for the smallest steps (at most 8 tokens, so at most 8 rows per
 // expert): with few experts in use, blocks of 64 features leave most of the device idle, so here a
 // block owns 16 features and its 8 warps split the inner dimension, as in the dense kernel.
-// grid = (ceil(Nout / 16), E).
-template <int MODE>
+// grid = (ceil(Nout / 16), E), block row y serving expert y; or, with `compact` (few pairs beside many
+// experts), grid = (ceil(Nout / 16), pairs) and block row y serving the y-th distinct expert of
+// topk_idx in the order of first occurrence, so that no block is launched for an expert that nobody
+// chose (at batch 1 that is 4 block rows instead of 60; finding the expert costs every block a little,
+// which from a handful of tokens on is more than the empty blocks cost).
+template <int MODE, bool COMPACT>
 __global__ void __launch_bounds__(256)
 grouped_gemm_skinny_pairs_splitk_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ topk_idx,
                                         const __nv_bfloat16* __restrict__ W, void* __restrict__ C, int n_pairs,
                                         int K, int src_is_token, int Nout, int Kd) {
     __shared__ int pair_sh[8], from_sh[8];
-    __shared__ int cnt_sh;
-    const int e = blockIdx.y;
+    __shared__ int cnt_sh, e_sh;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp == 0) {
-        int run = 0;
-        for (int base = 0; base < n_pairs; base += 32) {
+        // the blockIdx.y-th distinct expert
+        int e = COMPACT ? -1 : (int)blockIdx.y, distinct = 0;
+        for (int base = 0; COMPACT && base < n_pairs && e < 0; base += 32) {
             const int i = base + lane;
-            const bool mine = i < n_pairs && topk_idx[i] == e;
-            const unsigned bal = __ballot_sync(0xffffffffu, mine);
-            const int at = run + __popc(bal & ((1u << lane) - 1u));
-            if (mine && at < 8) {
-                pair_sh[at] = i;
-                from_sh[at] = src_is_token ? i / K : i;
-            }
-            run += __popc(bal);
+            const int v = i < n_pairs ? topk_idx[i] : -1 - lane;     // lanes past the end match nobody
+            bool seen = false;                                       // in a round before this one
+            for (int j = 0; j < base; ++j) seen |= topk_idx[j] == v;
+            const unsigned same = __match_any_sync(0xffffffffu, v);
+            const bool first = i < n_pairs && !seen && lane == __ffs(same) - 1;
+            const unsigned firsts = __ballot_sync(0xffffffffu, first);
+            const int rank = distinct + __popc(firsts & ((1u << lane) - 1u));
+            const unsigned hit = __ballot_sync(0xffffffffu, first && rank == (int)blockIdx.y);
+            if (hit) e = __shfl_sync(0xffffffffu, v, __ffs(hit) - 1);
+            distinct += __popc(firsts);
         }
-        if (lane == 0) cnt_sh = min(run, 8);
+        int run = 0;
+        if (e >= 0) {
+            for (int base = 0; base < n_pairs; base += 32) {
+                const int i = base + lane;
+                const bool mine = i < n_pairs && topk_idx[i] == e;
+                const unsigned bal = __ballot_sync(0xffffffffu, mine);
+                const int at = run + __popc(bal & ((1u << lane) - 1u));
+                if (mine && at < 8) {
+                    pair_sh[at] = i;
+                    from_sh[at] = src_is_token ? i / K : i;
+                }
+                run += __popc(bal);
+            }
+        }
+        if (lane == 0) {
+            cnt_sh = min(run, 8);
+            if (COMPACT) e_sh = e;
+        }
     }
     __syncthreads();
-    const int cnt = cnt_sh;
+    const int cnt = cnt_sh, e = COMPACT ? e_sh : (int)blockIdx.y;
     if (cnt <= 0) return;
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     splitk_tile<MODE, 1>(A, from_sh, pair_sh, W + (int64_t)e * wrows * Kd, nullptr, C, cnt, blockIdx.x * 16, Nout, Kd);
@@ -438,13 +461,14 @@ int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void*
         return kBadShape;
     }
     if (T <= PAIR_SPLITK_MAX_TOKENS) {
-        const dim3 sgrid((Nout + 15) / 16, E);
-        if (mode == 1)
-            grouped_gemm_skinny_pairs_splitk_kernel<1><<<sgrid, 256, 0, stream>>>(
-                (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 1, Nout, Kd);
-        else
-            grouped_gemm_skinny_pairs_splitk_kernel<0><<<sgrid, 256, 0, stream>>>(
-                (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 0, Nout, Kd);
+        const bool compact = 4 * T * K <= E;
+        const dim3 sgrid((Nout + 15) / 16, compact ? T * K : E);
+#define MI_PAIRS_SPLITK(MODE, COMPACT)                                                                   \
+    grouped_gemm_skinny_pairs_splitk_kernel<MODE, COMPACT><<<sgrid, 256, 0, stream>>>(                   \
+        (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, MODE, Nout, Kd)
+        if (mode == 1) { if (compact) MI_PAIRS_SPLITK(1, true); else MI_PAIRS_SPLITK(1, false); }
+        else { if (compact) MI_PAIRS_SPLITK(0, true); else MI_PAIRS_SPLITK(0, false); }
+#undef MI_PAIRS_SPLITK
         return finish_launch("grouped_gemm_skinny_pairs");
     }
     const dim3 grid((Nout + 63) / 64, E);

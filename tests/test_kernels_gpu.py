@@ -669,8 +669,11 @@ def test_grouped_gemm_skinny_equals_plain(T, E, K, H, I):
 
 
 @pytest.mark.parametrize("T,E,K,H,I", [(1, 8, 2, 64, 32), (8, 60, 4, 256, 96), (32, 12, 4, 128, 160), (19, 6, 3, 96, 64),
-                                       (32, 5, 5, 64, 64), (128, 60, 4, 128, 64), (70, 3, 2, 64, 96)])
+                                       (32, 5, 5, 64, 64), (128, 60, 4, 128, 64), (70, 3, 2, 64, 96),
+                                       (3, 60, 4, 64, 32), (8, 300, 8, 64, 32), (2, 64, 8, 96, 64), (5, 130, 6, 64, 32)])
 def test_grouped_gemm_skinny_by_pair_equals_sorted(T, E, K, H, I):
+    # few pairs beside many experts (4 T K <= E) launch block rows only for the experts that were chosen;
+    # with more than 32 pairs their list is found in several rounds
     g = torch.Generator().manual_seed(E + T)
     idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
     offsets, sorted_token, inv_perm = F().moe_permute(idx, E)

@@ -171,12 +171,12 @@ grouped_gemm_skinny_pairs_kernel(const __nv_bfloat16* __restrict__ A, const int*
 // in warp order through shared memory: the order of additions depends on K only.
 // MODE 0 writes float; MODE 1 holds gate and up rows (W has 2 * Nout rows) and writes
 // silu(gate) * up as bfloat16.  Tile j of NT holds rows 8j .. 8j+7.
-template <int MODE, int NT>
+template <int MODE, int NT, int WARPS = 8>
 __device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A, const int* src, const int* dst,
                                             const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
                                             void* __restrict__ C, int rows, int f0, int Nout, int Kd) {
     constexpr int H = MODE == 1 ? 2 : 1;
-    __shared__ float red[8][NT * H * 4][32];
+    __shared__ float red[WARPS][NT * H * 4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int fa = min(f0 + g, Nout - 1), fb = min(f0 + g + 8, Nout - 1);
     const uint4* wa = reinterpret_cast<const uint4*>(W + (int64_t)fa * Kd) + t;
@@ -205,7 +205,7 @@ __device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A,
             for (int i = 0; i < 4; ++i) acc[j][h][i] = 0.f;
 
     const int chunks = Kd >> 5;
-    const int per = (chunks + 7) >> 3;
+    const int per = (chunks + WARPS - 1) / WARPS;
     const int c_begin = min(warp * per, chunks), c_end = min(c_begin + per, chunks);
 #pragma unroll 4
     for (int c = c_begin; c < c_end; ++c) {
@@ -239,7 +239,7 @@ __device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A,
         const int r = 8 * j + 2 * (l & 3) + (i & 1);
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             s0 += red[w][(j * H) * 4 + i][l];
             if (MODE == 1) s1 += red[w][(j * H + H - 1) * 4 + i][l];
         }
@@ -261,6 +261,16 @@ __global__ void __launch_bounds__(256)
 dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                     const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
     splitk_tile<MODE, NT>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
+}
+
+// The same with 16 warps to a block, for products with so few output features that their tiles do not
+// even fill the SMs (an output projection, the second product of a shared expert; mode 0 only): the
+// inner dimension is split 16 ways and a block keeps twice as many loads in flight.
+template <int MODE, int NT>
+__global__ void __launch_bounds__(512)
+dense_skinny_wide_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                         const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
+    splitk_tile<MODE, NT, 16>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
 }
 
 // The pair-indexed grouped product for the smallest steps (at most 8 tokens, so at most 8 rows per
@@ -503,6 +513,19 @@ int mi_dense_skinny(const void* A, const void* W, const float* bias, void* C, in
     const dim3 grid((Nout + 15) / 16), block(256);
     const __nv_bfloat16* a = (const __nv_bfloat16*)A;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    // the choice depends on the product's shape only, never on the number of rows
+    if (mode == 0 && (int)grid.x <= num_sms && Kd >= 1024) {
+        if (rows <= 8) dense_skinny_wide_kernel<0, 1><<<grid, 512, 0, stream>>>(a, w, bias, C, rows, Nout, Kd);
+        else if (rows <= 16) dense_skinny_wide_kernel<0, 2><<<grid, 512, 0, stream>>>(a, w, bias, C, rows, Nout, Kd);
+        else dense_skinny_wide_kernel<0, 4><<<grid, 512, 0, stream>>>(a, w, bias, C, rows, Nout, Kd);
+        return finish_launch("dense_skinny");
+    }
 #define MI_DENSE_SKINNY(MODE, NT) dense_skinny_kernel<MODE, NT><<<grid, block, 0, stream>>>(a, w, bias, C, rows, Nout, Kd)
     if (mode == 1) {
         if (rows <= 8) MI_DENSE_SKINNY(1, 1);

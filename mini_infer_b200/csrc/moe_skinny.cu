@@ -263,14 +263,14 @@ dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __
     splitk_tile<MODE, NT>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
 }
 
-// The same with 16 warps to a block, for products with so few output features that their tiles do not
+// The same with 32 warps to a block, for products with so few output features that their tiles do not
 // even fill the SMs (an output projection, the second product of a shared expert; mode 0 only): the
-// inner dimension is split 16 ways and a block keeps twice as many loads in flight.
+// inner dimension is split 32 ways and a block keeps four times as many loads in flight.
 template <int MODE, int NT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 dense_skinny_wide_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                          const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
-    splitk_tile<MODE, NT, 16>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
+    splitk_tile<MODE, NT, 32>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
 }
 
 // The pair-indexed grouped product for the smallest steps (at most 8 tokens, so at most 8 rows per
@@ -519,12 +519,16 @@ int mi_dense_skinny(const void* A, const void* W, const float* bias, void* C, in
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    // the choice depends on the product's shape only, never on the number of rows
+    // the choice depends on the product's shape only, never on the number of rows (more than 16 rows
+    // go in two launches: the partial sums of 32 rows x 32 warps would not fit the static shared memory)
     if (mode == 0 && (int)grid.x <= num_sms && Kd >= 1024) {
-        if (rows <= 8) dense_skinny_wide_kernel<0, 1><<<grid, 512, 0, stream>>>(a, w, bias, C, rows, Nout, Kd);
-        else if (rows <= 16) dense_skinny_wide_kernel<0, 2><<<grid, 512, 0, stream>>>(a, w, bias, C, rows, Nout, Kd);
-        else dense_skinny_wide_kernel<0, 4><<<grid, 512, 0, stream>>>(a, w, bias, C, rows, Nout, Kd);
-        return finish_launch("dense_skinny");
+        float* c = (float*)C;
+        if (rows <= 8) dense_skinny_wide_kernel<0, 1><<<grid, 1024, 0, stream>>>(a, w, bias, c, rows, Nout, Kd);
+        else dense_skinny_wide_kernel<0, 2><<<grid, 1024, 0, stream>>>(a, w, bias, c, rows < 16 ? rows : 16, Nout, Kd);
+        if (rows > 16)
+            dense_skinny_wide_kernel<0, 2><<<grid, 1024, 0, stream>>>(a + (int64_t)16 * Kd, w, bias,
+                                                                      c + (int64_t)16 * Nout, rows - 16, Nout, Kd);
+        return finish_launch("dense_skinny", rows > 16 ? 2 : 1);
     }
 #define MI_DENSE_SKINNY(MODE, NT) dense_skinny_kernel<MODE, NT><<<grid, block, 0, stream>>>(a, w, bias, C, rows, Nout, Kd)
     if (mode == 1) {

@@ -66,6 +66,7 @@ class SparseMoE(FeedForward):
     # is short, and in prefill its library products are bound by the tensor cores while the grouped
     # products of the routed experts are bound by memory (measured: 7 % off a 2,048-token prefill).
     OVERLAP_SHARED_EXPERT = True
+    PRIORITY_SIDE_STREAM_MIN_TOKENS = 128
     FORK_AFTER_ROUTING_MAX_TOKENS = 8
 
     def __init__(self, params, prefix):
@@ -82,6 +83,7 @@ class SparseMoE(FeedForward):
         self.last_routing = None
         self.keep_routing = False
         self._side_stream = None
+        self._side_stream_big = None
 
     def tensor_decls(self) -> List[TensorDecl]:
         p = self.prefix
@@ -137,9 +139,18 @@ class SparseMoE(FeedForward):
         it; larger steps, whose shared expert is a library product that would crowd the expert
         kernels off the device, fork first."""
         main = torch.cuda.current_stream()
-        if self._side_stream is None:
-            self._side_stream = torch.cuda.Stream(device=x.device)
-        side = self._side_stream
+        # Large steps run the shared expert as library products whose blocks fill an SM: on a stream of
+        # higher priority they take their SMs ahead of the routing's small kernels, which slip into what
+        # is left, whatever order the two streams' first kernels reach the device in.
+        big = x.shape[0] > self.PRIORITY_SIDE_STREAM_MIN_TOKENS
+        if big:
+            if self._side_stream_big is None:
+                self._side_stream_big = torch.cuda.Stream(device=x.device, priority=-1)
+            side = self._side_stream_big
+        else:
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=x.device)
+            side = self._side_stream
         side.wait_stream(main)
         with torch.cuda.stream(side):
             shared = self._shared_expert(x)

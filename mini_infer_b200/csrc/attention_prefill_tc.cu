@@ -314,17 +314,20 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // P over S in place: 64 keys are 32 columns of two bfloat16 each
-            tmem_st32(s_addr, pk);
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            mbar_arrive_after_tmem(&p_full[buf]);
-            // Follow the O += P V barrier phase by phase (a parity wait must not fall two phases behind):
-            // the one of tile j - 1 was issued a tile ago, so this seldom waits.
+            // Follow the O += P V barrier phase by phase, and do so BEFORE this tile's P is handed over:
+            // O += P V of tile j cannot complete before every thread has arrived below, so the barrier
+            // cannot run a second phase ahead of a thread that has not yet seen tile j - 1 complete (a
+            // parity wait that falls two phases behind never returns).  The product of tile j - 1 was
+            // issued a tile ago, so this seldom waits.
             if (j > 0) {
                 ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, 19);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
+            // P over S in place: 64 keys are 32 columns of two bfloat16 each
+            tmem_st32(s_addr, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            mbar_arrive_after_tmem(&p_full[buf]);
         }
         if (ok) {
             ok = mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag, 20);

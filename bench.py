@@ -318,11 +318,96 @@ def run_ours(args):
 
 
 def run_reference(args):
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "Deyu-Kong/mini-infer is a CMake/C++ project with no setup.py or pyproject.toml at its root "
-                       "('pip install' of its checkout fails: not installable); its binary targets sm_86, needs "
-                       "a real checkpoint with tokenizer.json and runs Qwen2-MoE in FP16 only"}))
+    """The reference arm: Deyu-Kong/mini-infer itself, unmodified, built out of tree for sm_100 by
+    ``baseline/build_reference.py`` and driven by ``baseline/reference_bench.cpp`` through its stock path
+    (``ModelConfig::load`` -> ``TransformerModel::load_weights`` -> ``Engine::generate_batched_paged``) on a
+    folder of the same layer sizes with random float16 weights (the reference computes in FP16 only) and
+    seeded synthetic token ids.  Nothing of this repository's engine or kernels runs in that process; this
+    function only writes the model folder, starts the program and reports what it measured."""
+    import shutil
+    import tempfile
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if args.gpus != 1:
+        return unavailable("the reference engine runs on one GPU only")
+    binary = os.path.join(ROOT, "baseline", "_ref", "reference_bench")
+    if not os.path.exists(binary):
+        source = os.environ.get("MINI_INFER_REFERENCE", "/root/reference")
+        if not os.path.isfile(os.path.join(source, "CMakeLists.txt")):
+            return unavailable("baseline/_ref/reference_bench is not built and no checkout of the reference is "
+                               "at hand to build it from (python baseline/build_reference.py --source DIR)")
+        p = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "build_reference.py"), "--source", source],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if p.returncode != 0 or not os.path.exists(binary):
+            tail = " | ".join(p.stdout.strip().splitlines()[-3:])
+            return unavailable(f"building the reference failed: {tail}")
+    import torch
+    from mini_infer_b200.weights.random_init import write_model_folder
+    model_name, named = SIZES[args.sizes]
+    cfg = dict(named)
+    full_layers = named["num_hidden_layers"]
+    if args.layers <= 0:
+        args.layers = full_layers
+    cfg["num_hidden_layers"] = args.layers
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context)
+    # the folder goes where there is room for it (about 29 GB at the headline sizes)
+    best = max((d for d in (tempfile.gettempdir(), "/dev/shm") if os.path.isdir(d)),
+               key=lambda d: shutil.disk_usage(d).free)
+    folder = tempfile.mkdtemp(prefix="mini_infer_reference_", dir=best)
+    try:
+        t0 = time.time()
+        write_model_folder(folder, cfg, seed=args.seed, dtype=torch.float16,
+                           device="cuda:0" if torch.cuda.is_available() else "cpu")
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        write_s = time.time() - t0
+        clock = ClockSampler()
+        clock.start()
+        try:
+            p = subprocess.run([binary, folder, str(args.batch), str(args.prompt_len), str(args.steps),
+                                str(max(args.warmup, 3))], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                               timeout=args.reference_timeout)
+        except subprocess.TimeoutExpired:
+            clock.stop()
+            return unavailable(f"the reference did not finish within {args.reference_timeout} s")
+        clocks = clock.stop()
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    result = None
+    for line in p.stdout.splitlines():
+        if line.startswith("RESULT "):
+            result = json.loads(line[len("RESULT "):])
+    if p.returncode != 0 or result is None:
+        tail = " | ".join((p.stderr.strip() or p.stdout.strip()).splitlines()[-2:])
+        return unavailable(f"the reference's program exited with {p.returncode}: {tail[:300]}")
+    d = cfg["hidden_size"] // cfg["num_attention_heads"]
+    out = {
+        "metric": f"decode tok/s at batch {args.batch} ({model_name} sizes, {args.prompt_len}-token prompts)",
+        "value": round(result["decode_tok_s"], 2), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(result["ms_per_step"], 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+        "data": "synthetic: random-init weights, seeded uniform-random token ids", "impl": "reference",
+        "config": {"model": f"{model_name} layer sizes (Qwen2MoeForCausalLM)", "global_batch": args.batch,
+                   "seq_len": args.prompt_len, "context": args.context, "parallelism": "single GPU",
+                   "layers": args.layers, "layers_of_named_config": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": d,
+                   "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"],
+                   "moe_intermediate": cfg["moe_intermediate_size"],
+                   "shared_intermediate": cfg["shared_expert_intermediate_size"], "vocab": cfg["vocab_size"],
+                   "page_size": 16, "l2": "every step reads GBs of weights (inputs larger than L2)",
+                   "timing": "the reference engine's own clock around its decode loop (decode_tokens_per_sec)"},
+        # the reference's loop uploads the token ids and reads every row of logits' arg-max back, each step
+        "e2e": {"value": round(result["decode_tok_s"], 2), "unit": "tok/s",
+                "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * (8 + 2 * cfg["vocab_size"])},
+        "gpu_launches": None, "clocks": clocks,
+        "reference": {"call_seconds": result["call_seconds"], "load_seconds": result["load_seconds"],
+                      "write_seconds": round(write_s, 1), "generated": result["generated"]},
+    }
+    print(json.dumps(out))
     return 0
 
 
@@ -348,6 +433,7 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="wrap the timed region in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--eager", action="store_true", help="launch decode steps kernel by kernel, without CUDA graphs")
+    ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -689,6 +689,20 @@ def check_tc_status() -> None:
                               f"results of that step are invalid")
 
 
+def random_fill(out: torch.Tensor, key: Tuple[int, int], scale: float, offset: float) -> torch.Tensor:
+    """Fill ``out`` (float32, bfloat16 or float16, contiguous) with the counter-based values of
+    ``weights.random_init``: element ``i`` depends on ``(key, i)`` only."""
+    _chk(out, "random_fill out")
+    codes = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+    if out.dtype not in codes:
+        raise TypeError(f"random_fill: dtype {out.dtype} is not float32, bfloat16 or float16")
+    with torch.cuda.device(out.device):
+        check(library().mi_random_fill(_ptr(out), codes[out.dtype], out.numel(), int(key[0]) & 0xFFFFFFFF,
+                                       int(key[1]) & 0xFFFFFFFF, float(scale), float(offset), _stream()),
+              "random_fill")
+    return out
+
+
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                 top_p: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
                 probs_scratch: Optional[torch.Tensor] = None,

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "mi_attn_prefill_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "mi_grouped_gemm_tc": [P, P, P, P, P, I, I, I, I, I, P],
     "mi_grouped_gemm_tc_form": [P, P, P, P, P, I, I, I, I, I, I, P],
+    "mi_random_fill": [P, I, L, ctypes.c_uint, ctypes.c_uint, F, F, P],
 }
 
 

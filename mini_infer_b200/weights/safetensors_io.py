@@ -193,6 +193,5 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, Tuple[int, ...], t
                     f"declared {list(shape)} {dtype}")
             t = t.detach().contiguous().cpu()
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dim() else
-                        t.reshape(1).view(torch.uint8).numpy().tobytes())
+                f.write((t if t.dim() else t.reshape(1)).view(torch.uint8).numpy())
     os.replace(tmp, path)

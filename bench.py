@@ -320,7 +320,7 @@ def run_ours(args):
 def run_reference(args):
     """The reference arm: Deyu-Kong/mini-infer itself, unmodified, built out of tree for sm_100 by
     ``baseline/build_reference.py`` and driven by ``baseline/reference_bench.cpp`` through its stock path
-    (``ModelConfig::load`` -> ``TransformerModel::load_weights`` -> ``Engine::generate_batched_paged``) on a
+    (``ModelConfig::load`` -> ``TransformerModel::load_weights`` -> ``Scheduler::submit`` / ``Scheduler::step``) on a
     folder of the same layer sizes with random float16 weights (the reference computes in FP16 only) and
     seeded synthetic token ids.  Nothing of this repository's engine or kernels runs in that process; this
     function only writes the model folder, starts the program and reports what it measured."""
@@ -369,7 +369,7 @@ def run_reference(args):
         clock.start()
         try:
             p = subprocess.run([binary, folder, str(args.batch), str(args.prompt_len), str(args.steps),
-                                str(max(args.warmup, 3))], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                                str(max(args.warmup, 3)), str(args.seed), str(args.reference_prefill_batch)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
                                timeout=args.reference_timeout)
         except subprocess.TimeoutExpired:
             clock.stop()
@@ -382,8 +382,8 @@ def run_reference(args):
         if line.startswith("RESULT "):
             result = json.loads(line[len("RESULT "):])
     if p.returncode != 0 or result is None:
-        tail = " | ".join((p.stderr.strip() or p.stdout.strip()).splitlines()[-2:])
-        return unavailable(f"the reference's program exited with {p.returncode}: {tail[:300]}")
+        tail = " | ".join((p.stderr.strip() or p.stdout.strip()).splitlines()[-3:])
+        return unavailable(f"the reference's program exited with {p.returncode}: {tail[:500]}")
     d = cfg["hidden_size"] // cfg["num_attention_heads"]
     out = {
         "metric": f"decode tok/s at batch {args.batch} ({model_name} sizes, {args.prompt_len}-token prompts)",
@@ -399,10 +399,13 @@ def run_reference(args):
                    "moe_intermediate": cfg["moe_intermediate_size"],
                    "shared_intermediate": cfg["shared_expert_intermediate_size"], "vocab": cfg["vocab_size"],
                    "page_size": 16, "l2": "every step reads GBs of weights (inputs larger than L2)",
-                   "timing": "the reference engine's own clock around its decode loop (decode_tokens_per_sec)"},
-        # the reference's loop uploads the token ids and reads every row of logits' arg-max back, each step
+                   "timing": "the reference scheduler's own clock (IterationStats.wall_ms) over iterations that "
+                             "decode one token for every request and prefill nothing",
+                   "reference_prefill_batch": result.get("prefill_batch")},
+        # every iteration of the reference's scheduler uploads the token ids (int64) and reads the sampled
+        # ids (int32) back, so its own clock is end to end already
         "e2e": {"value": round(result["decode_tok_s"], 2), "unit": "tok/s",
-                "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * (8 + 2 * cfg["vocab_size"])},
+                "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * 4},
         "gpu_launches": None, "clocks": clocks,
         "reference": {"call_seconds": result["call_seconds"], "load_seconds": result["load_seconds"],
                       "write_seconds": round(write_s, 1), "generated": result["generated"]},
@@ -434,6 +437,10 @@ def main():
                     help="wrap the timed region in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--eager", action="store_true", help="launch decode steps kernel by kernel, without CUDA graphs")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
+    ap.add_argument("--reference-prefill-batch", type=int, default=1,
+                    help="prompts the reference's scheduler prefills per iteration (its cuBLAS handles, one per "
+                         "expert, and its per-expert activation buffers leave room for one 2,048-token prompt at a "
+                         "time on 180 GB)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -51,13 +51,20 @@ class GPUExecutor:
         self.runner = runner
         self.sampler = sampler
         self.cache = runner.cache
-        self._ahead = None          # (request ids, sampler handle, token ids the step was fed | None)
+        self._ahead = None          # (request ids, sampler handle, token ids the step was fed | None, note)
         self.steps_adopted = 0
         self.steps_dropped = 0
+        # A debugging and testing hook: ``observer.after_forward(request ids, tokens of each, logits or
+        # None) -> note`` is called right after every forward pass (before anything can overwrite what the
+        # pass left behind), and ``observer.settled(note, kept)`` once it is known whether the step counts
+        # (a step launched ahead may be dropped).
+        self.observer = None
 
     def _drop_ahead(self) -> None:
         if self._ahead is not None:
             self.runner.drop_ahead(self._ahead[0])
+            if self.observer is not None:
+                self.observer.settled(self._ahead[3], False)
             self._ahead = None
             self.steps_dropped += 1
 
@@ -80,9 +87,14 @@ class GPUExecutor:
             self.runner.adopt_ahead(rids)
             self.steps_adopted += 1
             handle = ahead[1]
+            if self.observer is not None:
+                self.observer.settled(ahead[3], True)
         else:
             self._drop_ahead()
             res = self.runner.step(entries)
+            if self.observer is not None:
+                self.observer.settled(self.observer.after_forward([e.rid for e in entries],
+                                                                  [len(e.tokens) for e in entries], res.logits), True)
             if not sample_for:
                 return {}
             assert [rid for rid, _ in res.index] == rids
@@ -96,10 +108,11 @@ class GPUExecutor:
             else:
                 nxt = self.sampler.launch(logits, [r.params for r in sample_for], [r.stream for r in sample_for],
                                           [len(r.generated) + 1 for r in sample_for])
-                self._ahead = (rids, nxt, None)
+                note = self.observer.after_forward(rids, [1] * len(rids), logits) if self.observer is not None else None
+                self._ahead = (rids, nxt, None, note)
         toks = self.sampler.fetch(handle)
         if self._ahead is not None:
-            self._ahead = (rids, self._ahead[1], toks)
+            self._ahead = (rids, self._ahead[1], toks, self._ahead[3])
         return {r.rid: t for r, t in zip(sample_for, toks)}
 
 

@@ -88,7 +88,11 @@ class ModelRunner:
         # keep host-side state per step, or were not written with replay in mind, switch this off.
         self.cuda_graphs = bool(cuda_graphs) and not model.state_needs and \
             all(getattr(p, "graph_safe", False) for p in model.all_parts())
-        self._graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graphs: Dict[tuple, tuple] = {}
+        # parts with settings that change what a captured pass launches, or that leave side outputs
+        from ..parts.base import Part
+        self._keyed_parts = [p for p in model.all_parts() if type(p).capture_key is not Part.capture_key
+                             or type(p).side_outputs is not Part.side_outputs]
         self._graph_pool = None
         self.graph_replays = 0
         self.graph_kernel_launches = 0      # kernels of this library launched through graph replays
@@ -263,9 +267,7 @@ class ModelRunner:
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not self.cuda_graphs:
             return False
-        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
-            return False
-        return not any(getattr(p, "keep_routing", False) for p in self.model.all_parts())
+        return not any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries)
 
     def _decode_with_graph(self, ctx: StepContext, logit_rows: torch.Tensor) -> torch.Tensor:
         """Replay (or first capture) the forward pass for this batch size and context-length bucket.
@@ -279,7 +281,8 @@ class ModelRunner:
         while bucket < ctx.max_kv_len:
             bucket *= 2
         ctx.max_kv_len = min(bucket, self.max_context)
-        key = (B, ctx.max_kv_len)
+        parts = self._keyed_parts
+        key = (B, ctx.max_kv_len, tuple(p.capture_key() for p in parts))
         if key not in self._graphs:
             side = torch.cuda.Stream(device=self.rt.device)
             side.wait_stream(torch.cuda.current_stream())
@@ -294,9 +297,12 @@ class ModelRunner:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=self._graph_pool):
                 out = self.model.forward(ctx, logit_rows)
-            self._graphs[key] = (g, out, launch_count() - before)
-        g, out, kernels = self._graphs[key]
+            self._graphs[key] = (g, out, launch_count() - before, [p.side_outputs() for p in parts])
+        g, out, kernels, side = self._graphs[key]
         g.replay()
+        for p, outputs in zip(parts, side):
+            if outputs is not None:
+                p.adopt_side_outputs(outputs)
         self.graph_replays += 1
         self.graph_kernel_launches += kernels
         return out

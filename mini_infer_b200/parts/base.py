@@ -201,6 +201,22 @@ class Part:
         """Take the declared tensors (CPU or device, stored dtype) and keep what forward needs."""
         self.rt = rt
 
+    # -- a forward pass captured as a CUDA graph -------------------------------------------- #
+    def capture_key(self):
+        """A hashable value for every setting of this part that changes which kernels its forward
+        launches (a recording switch, say): a captured pass is replayed only under the same key."""
+        return None
+
+    def side_outputs(self):
+        """What forward leaves on the part beside its return value (recorded routing, say), or None.
+        Tensors made while a pass was captured are refreshed in place by every replay; the runner
+        keeps them with the graph and hands them back through :meth:`adopt_side_outputs` after a
+        replay, so that a reader finds them where an eager pass would have left them."""
+        return None
+
+    def adopt_side_outputs(self, outputs) -> None:
+        pass
+
 
 class Deferred:
     """A part's output that has not been written out yet.  A consumer that can fold the computation

@@ -85,6 +85,17 @@ class SparseMoE(FeedForward):
         self._side_stream = None
         self._side_stream_big = None
 
+    # recorded routing survives capture: the graph is keyed by the switch, and a replay refreshes the
+    # recorded tensors in place
+    def capture_key(self):
+        return bool(self.keep_routing)
+
+    def side_outputs(self):
+        return self.last_routing if self.keep_routing else None
+
+    def adopt_side_outputs(self, outputs) -> None:
+        self.last_routing = outputs
+
     def tensor_decls(self) -> List[TensorDecl]:
         p = self.prefix
         out = [TensorDecl(p + "gate.weight", (self.E, self.H))]

@@ -22,12 +22,12 @@ GAP_TOL = {"float32": 2e-6, "bfloat16": 4e-3}
 
 
 def make_runner(folder: str, dtype: str, *, page_size: int = 16, num_pages: int = 64, max_requests: int = 8,
-                max_tokens: int = 512, max_context: int = 512):
+                max_tokens: int = 512, max_context: int = 512, cuda_graphs: bool = True):
     from mini_infer_b200.engine.loading import load_model
     from mini_infer_b200.engine.step import ModelRunner
     model, rt, cfg = load_model(folder, dtype, "cuda:0")
     return ModelRunner(model, rt, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
-                       max_tokens_per_step=max_tokens, max_context=max_context)
+                       max_tokens_per_step=max_tokens, max_context=max_context, cuda_graphs=cuda_graphs)
 
 
 def _sparse_parts(runner):

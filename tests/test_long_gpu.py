@@ -26,6 +26,28 @@ def test_long_decoding(tmp_path, name, dtype):
     assert len(got) == n
 
 
+@pytest.mark.parametrize("name,dtype,prompt,decoded", [("D", "float32", 1000, 60), ("D", "bfloat16", 990, 1100),
+                                                       ("E", "bfloat16", 2030, 40)])
+def test_decoding_with_graphs_across_context_buckets(tmp_path, name, dtype, prompt, decoded):
+    """Decode steps are replays of passes captured per context bucket (1024, 2048, 4096 ...), each launched
+    for the longest context of its bucket: a request that decodes across 1,024 and 2,048 tokens changes graph
+    on the way, and every row must still be the plain model's."""
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=41, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    n = prompt + decoded
+    toks = tiny.pick_tokens(cfg, w, n, 6)
+    runner = make_runner(folder, dtype, page_size=16, num_pages=-(-n // 16) + 2, max_requests=2, max_tokens=2048,
+                         max_context=2304)
+    steps = traces.tail_decoded({"x": toks}, tail=decoded)
+    for st in steps[1:]:
+        st["entries"] = [(rid, t, want) for rid, t, want in st["entries"]]
+    run_and_compare(runner, steps, cfg, w, {"x": toks}, dtype, 2e-5 if dtype == "float32" else 3e-2)
+    assert runner.graph_replays == decoded
+    buckets = sorted({key[1] for key in runner._graphs})
+    assert len(buckets) >= 2, buckets
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(tmp_path, dtype):
     """Positions 0, 1, 2 ... one by one from an empty cache, for every configuration."""

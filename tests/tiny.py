@@ -60,7 +60,22 @@ CONFIG_D = {
     "mlp_only_layers": [], "use_sliding_window": False, "sliding_window": 0, "max_window_layers": 0,
 }
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+# A fifth shape whose sizes the tensor-core kernels of the bfloat16 path take inside the engine: expert and
+# shared widths that are multiples of 64 (grouped products on tcgen05 once a step brings more than
+# 8 * experts / top_k tokens), head size 64 (tcgen05 prefill attention, split-KV decode attention), and a
+# sliding window on the upper layers so that those kernels meet released pages.
+CONFIG_E = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "vocab_size": 777, "hidden_size": 192, "intermediate_size": 320, "num_hidden_layers": 3,
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 64, "rms_norm_eps": 1e-5,
+    "rope_theta": 300000.0, "max_position_embeddings": 4096, "tie_word_embeddings": True,
+    "hidden_act": "silu", "qkv_bias": True,
+    "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 128,
+    "shared_expert_intermediate_size": 64, "norm_topk_prob": True, "decoder_sparse_step": 1,
+    "mlp_only_layers": [], "use_sliding_window": True, "sliding_window": 80, "max_window_layers": 1,
+}
+
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
 
 
 def make_folder(tmp: str, cfg: dict, seed: int, dtype=torch.float32) -> str:

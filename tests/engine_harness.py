@@ -82,26 +82,30 @@ def run_trace(runner, steps: List[dict], routing: Optional[dict] = None) -> Dict
 
 
 def reference_logits(cfg: dict, weights, tokens: List[int], routing_of_request: Optional[dict], gap_tol: float,
-                     what: str = "") -> torch.Tensor:
-    """Plain logits for ``tokens``; if the engine's recorded routing differs somewhere, check that
-    the difference is a near-tie and return the plain logits under the engine's choice."""
+                     what: str = "", by_expert: bool = False, stats: Optional[dict] = None) -> torch.Tensor:
+    """Plain logits for ``tokens`` (float32 on the CPU; the plain model runs where ``weights`` lie); if the
+    engine's recorded routing differs somewhere, check that the difference is a near-tie and return the
+    plain logits under the engine's choice.  ``stats`` counts ``pairs`` (token, layer) and how many were
+    ``flipped``; ``by_expert`` takes the plain model's expert-by-expert loop, for real sizes."""
     rec: dict = {}
-    ref = plain_model.forward(cfg, weights, tokens, record=rec)
+    ref = plain_model.forward(cfg, weights, tokens, record=rec, by_expert=by_expert)
     if not routing_of_request:
-        return ref
+        return ref.float().cpu()
     S, K = len(tokens), cfg["num_experts_per_tok"]
-    forced, differs = {}, False
+    forced, differs = {}, 0
     for li, per in routing_of_request.items():
         idx_plain, probs = rec["routing"][li]
-        eng = torch.tensor([per[p] for p in range(S)], dtype=torch.long)
+        eng = torch.tensor([per[p] for p in range(S)], dtype=torch.long, device=idx_plain.device)
         forced[li] = eng
-        if not torch.equal(torch.sort(eng, dim=1).values, torch.sort(idx_plain, dim=1).values):
-            differs = True
+        differs += int((torch.sort(eng, dim=1).values != torch.sort(idx_plain, dim=1).values).any(dim=1).sum())
+    if stats is not None:
+        stats["pairs"] = stats.get("pairs", 0) + S * len(forced)
+        stats["flipped"] = stats.get("flipped", 0) + differs
     if not differs:
-        return ref
+        return ref.float().cpu()
     # legitimacy must be judged on the forced run: an earlier flip changes later probabilities
     rec2: dict = {}
-    ref2 = plain_model.forward(cfg, weights, tokens, forced_routing=forced, record=rec2)
+    ref2 = plain_model.forward(cfg, weights, tokens, forced_routing=forced, record=rec2, by_expert=by_expert)
     for li, eng in forced.items():
         _, probs = rec2["routing"][li]
         kth = torch.sort(probs, dim=1, descending=True).values[:, K - 1]
@@ -109,7 +113,7 @@ def reference_logits(cfg: dict, weights, tokens: List[int], routing_of_request: 
         short = (kth[:, None] - chosen).max()
         assert float(short) <= gap_tol, (f"{what}: layer {li} routes to an expert whose probability is "
                                          f"{float(short):.2e} below the K-th largest (tolerance {gap_tol:.1e})")
-    return ref2
+    return ref2.float().cpu()
 
 
 def compare(got: Dict[Tuple[str, int], torch.Tensor], ref: Dict[str, torch.Tensor], rel_tol: float) -> float:
@@ -129,10 +133,99 @@ def compare(got: Dict[Tuple[str, int], torch.Tensor], ref: Dict[str, torch.Tenso
     return worst
 
 
-def run_and_compare(runner, steps, cfg, weights, reqs: Dict[str, List[int]], dtype: str, rel_tol: float) -> float:
+def run_and_compare(runner, steps, cfg, weights, reqs: Dict[str, List[int]], dtype: str, rel_tol: float,
+                    by_expert: bool = False, stats: Optional[dict] = None) -> float:
     """Run a trace that feeds every request whole (in any cutting) and compare all returned rows."""
     routing: dict = {}
     got = run_trace(runner, steps, routing)
-    ref = {rid: reference_logits(cfg, weights, toks, routing.get(rid), GAP_TOL[dtype], rid)
+    ref = {rid: reference_logits(cfg, weights, toks, routing.get(rid), GAP_TOL[dtype], rid, by_expert, stats)
            for rid, toks in reqs.items()}
     return compare(got, ref, rel_tol), got
+
+
+class DictSource:
+    """A tensor source over tensors that are in memory already (same interface as a checkpoint folder)."""
+
+    def __init__(self, tensors):
+        self.t = tensors
+
+    def names(self):
+        return list(self.t)
+
+    def shape(self, n):
+        return tuple(self.t[n].shape)
+
+    def dtype(self, n):
+        return self.t[n].dtype
+
+    def read(self, n):
+        return self.t[n]
+
+    def describe(self):
+        return "tensors in memory"
+
+
+class GenerationObserver:
+    """An observer of ``GPUExecutor``: keeps, for every step that counted, the logits it was sampled from
+    and the experts every layer chose for every token it fed.  ``prompt_len[i]`` is the prompt length of
+    request ``i`` of the ``generate`` call (its id is ``(call number, i)``)."""
+
+    def __init__(self, runner, prompt_len):
+        self.prompt_len = prompt_len
+        self.sparse = _sparse_parts(runner)
+        for part in self.sparse.values():
+            part.keep_routing = True
+        self.fed, self.logits, self.routing = {}, {}, {}
+
+    def after_forward(self, rids, counts, logits):
+        return (list(rids), list(counts), None if logits is None else logits.clone(),
+                {li: part.last_routing[0].clone() for li, part in self.sparse.items()})
+
+    def settled(self, note, kept):
+        if not kept:
+            return
+        rids, counts, logits, routing = note
+        routing = {li: idx.cpu() for li, idx in routing.items()}
+        t = 0
+        for rid, n in zip(rids, counts):
+            start = self.fed.get(rid, 0)
+            for li, idx in routing.items():
+                per = self.routing.setdefault(rid, {}).setdefault(li, {})
+                for j in range(n):
+                    per[start + j] = idx[t + j].tolist()
+            t += n
+            self.fed[rid] = start + n
+        if logits is not None:
+            rows = logits.float().cpu()
+            # one row for every entry whose prompt has been fed to its end, in the order of the entries
+            r = 0
+            for rid in rids:
+                if self.fed[rid] >= self.prompt_len[rid[1]]:
+                    self.logits[(rid, self.fed[rid] - 1)] = rows[r]
+                    r += 1
+            assert r == rows.shape[0]
+
+    def close(self):
+        for part in self.sparse.values():
+            part.keep_routing = False
+
+
+def compare_generation(obs: "GenerationObserver", call: int, prompts, outs, cfg, weights, dtype: str, rel_tol: float,
+                       by_expert: bool = False, stats: Optional[dict] = None) -> float:
+    """Every row of logits that ``LLM.generate`` sampled from against the plain model's row for the same
+    position (under the engine's routing where a near-tie allows either), and every sampled token
+    against the arg-max of the engine's own row.  Returns the largest relative error."""
+    worst = 0.0
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        rid = (call, i)
+        fed = list(p) + list(o.token_ids[:-1])
+        ref = reference_logits(cfg, weights, fed, obs.routing[rid], GAP_TOL[dtype], f"request {i}", by_expert, stats)
+        scale = float(ref.abs().max())
+        for k, tok in enumerate(o.token_ids):
+            pos = len(p) - 1 + k
+            got = obs.logits[(rid, pos)]
+            err = float((got - ref[pos]).abs().max()) / scale
+            worst = max(worst, err)
+            assert err <= rel_tol, f"request {i}, generated token {k}: logits differ by {err:.2e} of the largest"
+            assert tok == int(torch.argmax(got)), f"request {i}, generated token {k} is not the arg-max of its row"
+    return worst

@@ -124,54 +124,13 @@ def test_steps_launched_ahead_change_nothing(folders, dtype):
     llm.runner.cache.check_invariants()
 
 
-class LogitsAndRouting:
-    """An observer of ``GPUExecutor``: keeps, for every step that counted, the logits it was sampled from
-    and the experts every layer chose for every token it fed."""
-
-    def __init__(self, runner, prompt_len):
-        self.prompt_len = prompt_len            # of request i of the call
-        self.sparse = {i: layer.feed_forward for i, layer in enumerate(runner.model.layers)
-                       if hasattr(layer.feed_forward, "keep_routing")}
-        for part in self.sparse.values():
-            part.keep_routing = True
-        self.fed, self.logits, self.routing = {}, {}, {}
-
-    def after_forward(self, rids, counts, logits):
-        return (list(rids), list(counts), None if logits is None else logits.clone(),
-                {li: part.last_routing[0].clone() for li, part in self.sparse.items()})
-
-    def settled(self, note, kept):
-        if not kept:
-            return
-        rids, counts, logits, routing = note
-        routing = {li: idx.cpu() for li, idx in routing.items()}
-        t = 0
-        for rid, n in zip(rids, counts):
-            start = self.fed.get(rid, 0)
-            for li, idx in routing.items():
-                per = self.routing.setdefault(rid, {}).setdefault(li, {})
-                for j in range(n):
-                    per[start + j] = idx[t + j].tolist()
-            t += n
-            self.fed[rid] = start + n
-        if logits is not None:
-            rows = logits.float().cpu()
-            # one row for every entry whose prompt has been fed to its end, in the order of the entries
-            r = 0
-            for rid in rids:
-                if self.fed[rid] >= self.prompt_len[rid[1]]:
-                    self.logits[(rid, self.fed[rid] - 1)] = rows[r]
-                    r += 1
-            assert r == rows.shape[0]
-
-
 @pytest.mark.parametrize("name,dtype", [("D", "float32"), ("D", "bfloat16"), ("E", "bfloat16")])
 def test_generation_as_the_product_runs_it_against_the_plain_model(tmp_path, name, dtype):
     """``LLM.generate`` with everything on that serving uses (prompts in portions beside decoding requests,
     decode steps as CUDA-graph replays, the next step launched before this one's tokens are on the host):
     the logits every token was sampled from are kept and compared with the plain model's, under the
     engine's routing where a near-tie allows either choice."""
-    from engine_harness import GAP_TOL, reference_logits
+    from engine_harness import GenerationObserver, compare_generation
     from mini_infer_b200.engine.llm import LLM
     from mini_infer_b200.sampling import SamplingParams
     cfg = tiny.CONFIGS[name]
@@ -180,25 +139,13 @@ def test_generation_as_the_product_runs_it_against_the_plain_model(tmp_path, nam
     prompts = [tiny.pick_tokens(cfg, w, n, 7 * n) for n in (40, 75, 130, 9)]
     new_tokens = 24
     llm = LLM(folder, dtype=dtype, max_seq_len=512, max_running=4, max_tokens_per_step=96, prefill_chunk=64)
-    obs = LogitsAndRouting(llm.runner, [len(p) for p in prompts])
+    obs = GenerationObserver(llm.runner, [len(p) for p in prompts])
     llm.executor.observer = obs
     outs = llm.generate(prompts, SamplingParams(greedy=True, max_new_tokens=new_tokens))
     assert llm.executor.steps_adopted > 0 and llm.runner.graph_replays > 0
     assert any(s.prefill_tokens and s.decode_tokens for s in llm.last_history)
-    tol = 2e-5 if dtype == "float32" else 2e-2
-    for i, (p, o) in enumerate(zip(prompts, outs)):
-        rid = (llm._calls, i)
-        assert len(o.token_ids) == new_tokens
-        fed = p + o.token_ids[:-1]
-        ref = reference_logits(cfg, w, fed, obs.routing[rid], GAP_TOL[dtype], f"request {i}")
-        scale = float(ref.abs().max())
-        for k in range(new_tokens):
-            pos = len(p) - 1 + k
-            got = obs.logits[(rid, pos)]
-            err = float((got - ref[pos]).abs().max()) / scale
-            assert err <= tol, f"request {i}, generated token {k}: logits differ by {err:.2e} of the largest"
-            # the token that was sampled is the arg-max of the engine's own logits
-            assert o.token_ids[k] == int(torch.argmax(got))
+    assert all(len(o.token_ids) == new_tokens for o in outs)
+    compare_generation(obs, llm._calls, prompts, outs, cfg, w, dtype, 2e-5 if dtype == "float32" else 2e-2)
 
 
 @pytest.mark.parametrize("dtype,new_tokens,margin", [("float32", 20, 1e-4), ("bfloat16", 6, 0.02)])

@@ -186,6 +186,15 @@ class CacheManager:
         if not 0 <= num_tokens <= r.num_tokens:
             raise ValueError("CacheManager.truncate: cannot grow")
         keep = -(-num_tokens // self.page_size)
+        # a window group has given back the pages its window had passed; going back further than that
+        # would leave the next query attending over keys that are gone
+        for g, spec in enumerate(self.groups):
+            if spec.window > 0 and num_tokens < r.num_tokens:
+                first_needed = max(0, num_tokens - spec.window + 1) // self.page_size
+                if any(p < 0 for p in r.tables[g][first_needed:keep]):
+                    raise ValueError(f"CacheManager.truncate: group {g} (window {spec.window}) has released pages "
+                                     f"that a query at position {num_tokens} would read; a request can go back "
+                                     f"only as far as its window has not moved on")
         for g, table in enumerate(r.tables):
             while len(table) > keep:
                 p = table.pop()

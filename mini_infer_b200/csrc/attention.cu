@@ -245,7 +245,9 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     const int pos = kvl - 1;
     int k_first = 0;
     if (window > 0) k_first = max(0, pos - window + 1);
-    const int n_splits = decode_splits<SPLIT>(kvl);
+    // never more splits than the caller's scratch holds (a caller whose max_splits is too small for its
+    // longest request gets a result over fewer keys, never an access outside the scratch)
+    const int n_splits = min(decode_splits<SPLIT>(kvl), max_splits);
     const int first_split = min(k_first / SPLIT, n_splits - 1);
     if (sp < first_split || sp >= n_splits) return;
     const int hk = h / (nh / nkv);
@@ -263,7 +265,7 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
     for (int i = 0; i < E; ++i) acc[i] = 0.f;
     constexpr int SPAN = SPLIT + SPLIT / 4;                   // the last split may hold a short tail too
     const int k_lo = max(sp * SPLIT, k_first);
-    const int k_hi = sp == n_splits - 1 ? kvl : (sp + 1) * SPLIT;
+    const int k_hi = sp == n_splits - 1 ? min(kvl, sp * SPLIT + SPAN) : (sp + 1) * SPLIT;
     const int span = k_hi - sp * SPLIT;
     // the pages of this split, looked up once
     __shared__ int64_t key_off[SPAN];
@@ -356,7 +358,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
     const int pos = kvl - 1;
     int k_first = 0;
     if (window > 0) k_first = max(0, pos - window + 1);
-    const int n_splits = decode_splits<SPLIT>(kvl);
+    const int n_splits = min(decode_splits<SPLIT>(kvl), max_splits);
     const int first_split = min(k_first / SPLIT, n_splits - 1);
     const int64_t base = ((int64_t)b * nh + h) * max_splits;
     const int t = q_start[b];

@@ -18,6 +18,9 @@
 // Rules of use
 //   * Sizes: B * nh * max_splits * (d + 2) floats must fit the array; a larger problem is refused
 //     with kBadShape (-2) and a message from mi_last_error(), never computed partially.
+//   * max_splits must be at least ceil(longest kv_len / mi_attn_decode_split_size()) (splits of 512
+//     keys).  The lengths are device data that the host cannot check: with a smaller max_splits the
+//     kernels stay inside the array but attend over fewer keys than the request has.
 //   * First call on a device: looks up the device address of the array (cudaGetSymbolAddress,
 //     with that device current) and remembers it.  Make that first call before any stream
 //     capture begins on that device; later calls only launch kernels.

@@ -50,7 +50,9 @@ template <int MODE, int TN, int STAGES, int BLOCKS>
 __global__ void __launch_bounds__(192, BLOCKS)
 grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
-                       int* __restrict__ status) {
+                       int* __restrict__ status, int skip_kb, uint32_t wait_limit) {
+    // skip_kb >= 0 (tests of the bounded waits only): the producer stops before the loads of that k block, so
+    // the wait for them runs out after `wait_limit` rounds, every role gives up and the status word says so.
     constexpr int NB = 2;                                 // weight tiles per stage: gate and up (MODE 1), or two
                                                           // neighbouring feature tiles sharing the row tile (MODE 0)
     constexpr int R_TILE_BYTES = TN * BK * 2;             // room for the row tile of one stage
@@ -105,7 +107,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
-                if (!mbar_wait(&empty_bar[s], parity, abort_flag, 1)) break;
+                if (!mbar_wait(&empty_bar[s], parity, abort_flag, 1, wait_limit)) break;
+                if (kb == skip_kb) break;                  // (tests only) this block's data never arrives
                 uint8_t* st = smem + (size_t)s * STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], NB * W_TILE_BYTES + row_bytes);
                 tma_load_2d(st, &map_w, kb * BK, e * wrows + n0, &full_bar[s]);
@@ -125,7 +128,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
             for (int kb = 0; kb < num_kb && ok; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t parity = (kb / STAGES) & 1;
-                ok = mbar_wait(&full_bar[s], parity, abort_flag, 2);
+                ok = mbar_wait(&full_bar[s], parity, abort_flag, 2, wait_limit);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t w_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -145,7 +148,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; a lane is a feature of a 128-feature tile
         const int quarter = warp & 3;
         const int fl = quarter * 32 + lane;
-        bool ok = mbar_wait(&accum_bar, 0, abort_flag, 3);
+        bool ok = mbar_wait(&accum_bar, 0, abort_flag, 3, wait_limit);
         ok = __all_sync(0xffffffffu, ok);                 // tcgen05.ld is warp-wide: all lanes or none
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // With whole 16-byte groups of features per row the tile is transposed through the (now
@@ -509,6 +512,17 @@ static size_t persistent_smem(int tn, int stages, int nw, int n_rows, int E) {
 }
 constexpr size_t kPersistentSmemLimit = 232448 - 8704;    // 227 KiB less the kernel's static shared memory
 
+// For the test of the bounded waits: the next launch of a one-block-per-tile form (form 0 or 1) stops loading
+// at k block `skip_kb` and gives every wait `wait_limit` rounds, so that a wait runs out, the
+// kernel returns by itself and the status word reports it.  Nothing else is changed; the launch after
+// that is a normal one again.
+static int g_test_skip_kb = -1;
+static uint32_t g_test_wait_limit = 0;
+void mi_grouped_gemm_tc_test_fault(int skip_kb, unsigned int wait_limit) {
+    g_test_skip_kb = skip_kb;
+    g_test_wait_limit = wait_limit;
+}
+
 // A: [n_rows, Kd] bfloat16, rows sorted by expert (offsets[E+1]); W: [E, wrows, Kd] bfloat16.
 // mode 1: C bfloat16 [n_rows, Nout] = silu(gate) * up with W holding 2*Nout rows per expert;
 // mode 0: C float [n_rows, Nout].  `status` (device int, zero before the first call) receives a
@@ -591,12 +605,17 @@ int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, vo
     }
     const int feats = mode == 1 ? tc::BF : 2 * tc::BF;
     const dim3 grid((Nout + feats - 1) / feats, max_tiles);
+    const int skip_kb = g_test_skip_kb;
+    const uint32_t wait_limit = g_test_wait_limit ? g_test_wait_limit : tc::WAIT_LIMIT;
+    g_test_skip_kb = -1;                                  // a test's fault holds for one launch
+    g_test_wait_limit = 0;
 #define MI_TC_LAUNCH(MODE, TN, STAGES, BLOCKS)                                                         \
     do {                                                                                               \
         const size_t smem = STAGES * (size_t)(2 * tc::W_TILE_BYTES + TN * tc::BK * 2) + 1024;          \
         auto kern = tc::grouped_gemm_tc_kernel<MODE, TN, STAGES, BLOCKS>;                              \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
-        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);             \
+        kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status, skip_kb,     \
+                                          wait_limit);                                                 \
     } while (0)
     if (form == 0) {
         if (mode == 1) MI_TC_LAUNCH(1, 128, 2, 2); else MI_TC_LAUNCH(0, 128, 2, 2);

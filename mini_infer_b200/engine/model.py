@@ -47,6 +47,10 @@ class Model:
         self.layers: List[BuiltLayer] = [build_layer(ls) for ls in spec.layers]
         self.final_norm = _make("norm", spec.final_norm, spec.final_norm_prefix)
         self.lm_head = _make("lm_head", spec.lm_head, spec.lm_head_prefix)
+        # debugging: ``layer_observer(schedule position, residual stream after that entry [T, H] float32)``
+        # is called after every schedule entry of an eager forward pass (the reference's counterpart is
+        # debug_print_tensor, src/model/transformer_model.cpp:24-61)
+        self.layer_observer = None
         self._plan_caches()
 
     # -- what the model keeps between steps --------------------------------- #
@@ -141,6 +145,9 @@ class Model:
             if not layer.block.accepts_deferred:
                 pending = resolve(pending)
             pending = layer.block.forward(layer, hidden, pending, ctx, self.bindings[pos])
+            if self.layer_observer is not None:
+                # the addition of a part's output is left to the next norm's kernel; form it here
+                self.layer_observer(pos, hidden if pending is None else hidden + resolve(pending))
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         x = apply_norm(self.final_norm, hidden, pending, rows=logit_rows)

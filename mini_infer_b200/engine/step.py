@@ -16,9 +16,11 @@ and the metadata crosses to the device once per step.
 
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -119,13 +121,15 @@ class ModelRunner:
             sec(f"slot_mapping{g}", T)
             sec(f"block_table{g}", B * self.max_pages)
         self._host = torch.zeros(off, dtype=torch.int32).pin_memory()
+        self._host_np = self._host.numpy()          # the same pinned memory, for whole-array writes
+        self.host_prepare_seconds = 0.0             # host time spent validating, reserving and staging
         self._dev = torch.zeros(off, dtype=torch.int32, device=self.rt.device)
         self._copied = torch.cuda.Event()
         self._copied.record()
 
-    def _hview(self, name: str, n: int) -> torch.Tensor:
+    def _hview_np(self, name: str, n: int) -> np.ndarray:
         o, cap = self._sec[name]
-        return self._host[o:o + n]
+        return self._host_np[o:o + n]
 
     def _dview(self, name: str, n: int) -> torch.Tensor:
         o, cap = self._sec[name]
@@ -151,13 +155,15 @@ class ModelRunner:
     # ------------------------------------------------------------------ #
     # the step
     # ------------------------------------------------------------------ #
-    def validate(self, entries: Sequence[StepEntry]) -> None:
+    def validate(self, entries: Sequence[StepEntry]) -> List[np.ndarray]:
+        """Refuse a bad batch before anything runs.  Returns every entry's token ids as an int64 array."""
         if not entries:
             raise StepError("step: empty batch")
         if len(entries) > self.max_requests:
             raise StepError(f"step: {len(entries)} requests exceed the limit {self.max_requests}")
         seen = set()
         total = 0
+        arrays = []
         for e in entries:
             if e.rid in seen:
                 raise StepError(f"step: request {e.rid!r} appears twice in one batch")
@@ -171,14 +177,19 @@ class ModelRunner:
             if self.cache.num_tokens(e.rid) + n > self.max_context:
                 raise StepError(f"step: request {e.rid!r} would reach {self.cache.num_tokens(e.rid) + n} "
                                 f"tokens, the context limit is {self.max_context}")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"step: token id {t} of request {e.rid!r} outside [0, {self.vocab_size})")
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.ndim != 1:
+                raise StepError(f"step: the tokens of request {e.rid!r} are not a flat list")
+            if int(toks.min()) < 0 or int(toks.max()) >= self.vocab_size:
+                bad = int(toks[(toks < 0) | (toks >= self.vocab_size)][0])
+                raise StepError(f"step: token id {bad} of request {e.rid!r} outside [0, {self.vocab_size})")
+            arrays.append(toks)
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"step: wanted place {w} of request {e.rid!r} outside its {n} tokens")
         if total > self.max_tokens:
             raise StepError(f"step: {total} tokens exceed the budget {self.max_tokens}")
+        return arrays
 
     def prepare(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
                 ahead: bool = False) -> Tuple[StepContext, Optional[torch.Tensor], List]:
@@ -186,8 +197,10 @@ class ModelRunner:
 
         With ``device_tokens`` (int32, one per row, on the device) the token ids of ``entries`` are
         placeholders and the step reads the given ones; ``ahead`` reserves through
-        :meth:`CacheManager.reserve_ahead`."""
-        self.validate(entries)
+        :meth:`CacheManager.reserve_ahead`.  Whatever goes wrong after pages were reserved, every
+        reservation of the step is undone before the error leaves."""
+        t_begin = time.perf_counter()
+        arrays = self.validate(entries)
         starts = []
         done = []
         try:
@@ -195,55 +208,58 @@ class ModelRunner:
                 starts.append(self.cache.reserve_ahead(e.rid, len(e.tokens)) if ahead
                               else self.cache.reserve(e.rid, len(e.tokens)))
                 done.append(e.rid)
-        except OutOfPages:
+            staged = self._stage(entries, arrays, starts, device_tokens)
+        except BaseException:
             for rid in done:
                 self.cache.cancel(rid)
             raise
+        self.host_prepare_seconds += time.perf_counter() - t_begin
+        return staged
+
+    def _stage(self, entries, arrays, starts, device_tokens):
+        """Fill the pinned staging buffer (whole arrays at a time, no per-token work on the host) and
+        queue its one copy to the device."""
         B = len(entries)
-        T = sum(len(e.tokens) for e in entries)
+        counts = np.fromiter((a.shape[0] for a in arrays), dtype=np.int64, count=B)
+        starts_np = np.asarray(starts, dtype=np.int64)
+        T = int(counts.sum())
         self._copied.synchronize()      # the previous step's upload has left the pinned buffer
-        h = self._hview
-        tok, pos, rot, rows = h("token_ids", T), h("positions", T), h("req_of_token", T), h("logit_rows", T)
-        qs, kvl, ss, fr = h("q_start", B + 1), h("kv_len", B), h("state_slot", B), h("fresh", B)
+        h = self._hview_np
+        first = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(counts, out=first[1:])
+        req_of_token = np.repeat(np.arange(B, dtype=np.int64), counts)
+        positions = np.arange(T, dtype=np.int64) - first[req_of_token] + starts_np[req_of_token]
+        kv_len = starts_np + counts
+        slots = np.fromiter((self.cache.slot_of(e.rid) for e in entries), dtype=np.int64, count=B)
+        h("token_ids", T)[:] = np.concatenate(arrays)
+        h("positions", T)[:] = positions
+        h("req_of_token", T)[:] = req_of_token
+        h("q_start", B + 1)[:] = first
+        h("kv_len", B)[:] = kv_len
+        h("state_slot", B)[:] = slots
+        h("fresh", B)[:] = starts_np == 0
         index: List[Tuple[Hashable, int]] = []
-        t0 = 0
-        max_q = max_kv = 0
-        host_kv, host_slot = [], []
-        tok_l, pos_l, rot_l, row_l = [], [], [], []
-        for b, (e, start) in enumerate(zip(entries, starts)):
-            n = len(e.tokens)
-            tok_l.extend(int(t) for t in e.tokens)
-            pos_l.extend(range(start, start + n))
-            rot_l.extend([b] * n)
-            qs[b] = t0
-            kvl[b] = start + n
-            ss[b] = self.cache.slot_of(e.rid)
-            fr[b] = 1 if start == 0 else 0
-            host_kv.append(start + n)
-            host_slot.append(self.cache.slot_of(e.rid))
+        row_l: List[int] = []
+        for b, e in enumerate(entries):
             for w in e.want:
-                row_l.append(t0 + int(w))
+                row_l.append(int(first[b]) + int(w))
                 index.append((e.rid, int(w)))
-            max_q = max(max_q, n)
-            max_kv = max(max_kv, start + n)
-            t0 += n
-        qs[B] = T
-        tok[:] = torch.tensor(tok_l, dtype=torch.int32)
-        pos[:] = torch.tensor(pos_l, dtype=torch.int32)
-        rot[:] = torch.tensor(rot_l, dtype=torch.int32)
         R = len(row_l)
         if R:
-            rows[:R] = torch.tensor(row_l, dtype=torch.int32)
+            h("logit_rows", R)[:] = row_l
+        ps = self.page_size
         for g in range(len(self.model.kv_groups)):
-            sm = h(f"slot_mapping{g}", T)
-            bt = h(f"block_table{g}", B * self.max_pages).view(B, self.max_pages)
-            bt.fill_(-1)
-            sm_l = []
-            for b, (e, start) in enumerate(zip(entries, starts)):
+            bt = h(f"block_table{g}", B * self.max_pages).reshape(B, self.max_pages)
+            bt.fill(-1)
+            for b, e in enumerate(entries):
                 table = self.cache.block_table(g, e.rid)
-                bt[b, :len(table)] = torch.tensor(table, dtype=torch.int32)
-                sm_l.extend(self.cache.slot_mapping(g, e.rid, start, len(e.tokens)))
-            sm[:] = torch.tensor(sm_l, dtype=torch.int32)
+                bt[b, :len(table)] = table
+            pages = bt[req_of_token, positions // ps]
+            if pages.size and int(pages.min()) < 0:
+                t = int(np.argmin(pages))
+                raise RuntimeError(f"step: position {int(positions[t])} of request {entries[int(req_of_token[t])].rid!r} "
+                                   f"lies in a released page of cache group {g}")
+            h(f"slot_mapping{g}", T)[:] = pages.astype(np.int64) * ps + positions % ps
         self._dev.copy_(self._host, non_blocking=True)
         self._copied.record()
         d = self._dview
@@ -255,17 +271,18 @@ class ModelRunner:
             views.append(KVGroupView(
                 block_table=d(f"block_table{g}", B * self.max_pages).view(B, self.max_pages),
                 slot_mapping=d(f"slot_mapping{g}", T), page_size=self.page_size, k=k, v=v))
+        max_q, max_kv = int(counts.max()), int(kv_len.max())
         ctx = StepContext(
             num_tokens=T, num_requests=B, max_q_len=max_q, max_kv_len=max_kv, all_decode=(max_q == 1),
             token_ids=d("token_ids", T), positions=d("positions", T), q_start=d("q_start", B + 1),
             kv_len=d("kv_len", B), req_of_token=d("req_of_token", T), state_slot=d("state_slot", B),
             fresh=d("fresh", B), kv_groups=views, states=self.state_tensors, scratch=self.scratch,
-            host_q_start=[int(x) for x in qs.tolist()], host_kv_len=host_kv, host_state_slot=host_slot)
+            host_q_start=first.tolist(), host_kv_len=kv_len.tolist(), host_state_slot=slots.tolist())
         logit_rows = d("logit_rows", R) if R else None
         return ctx, logit_rows, index
 
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
-        if not self.cuda_graphs:
+        if not self.cuda_graphs or self.model.layer_observer is not None:
             return False
         return not any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries)
 

@@ -7,6 +7,7 @@ error; nothing falls back to PyTorch.
 
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import Optional, Tuple
 
@@ -622,7 +623,9 @@ def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.
     return out
 
 
-def grouped_gemm_tc_supported(kd: int, nout: int) -> bool:
+def grouped_gemm_tc_supported(kd: int) -> bool:
+    """The tcgen05 grouped product takes any number of output features; its inner size must be a multiple
+    of 64 (one 128-byte swizzle row of bfloat16)."""
     return bool(library().mi_grouped_gemm_tc_supported(int(kd)))
 
 
@@ -669,6 +672,16 @@ def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tens
                                             -1 if form is None else int(form), _stream()), "grouped_gemm_tc")
     _tc_pending = True
     return out
+
+
+def grouped_gemm_tc_inject_wait_fault(skip_k_block: int, wait_limit: int) -> None:
+    """For the test of the bounded waits: the next :func:`grouped_gemm_tc` with ``form`` 0 or 1 leaves out
+    the loads of one k block and waits at most ``wait_limit`` rounds, so a wait runs out, the kernel
+    returns by itself, and :func:`check_tc_status` raises.  The launch after it is a normal one."""
+    lib = library()
+    lib.mi_grouped_gemm_tc_test_fault.argtypes = [ctypes.c_int, ctypes.c_uint]
+    lib.mi_grouped_gemm_tc_test_fault.restype = None
+    lib.mi_grouped_gemm_tc_test_fault(int(skip_k_block), int(wait_limit))
 
 
 def check_tc_status() -> None:

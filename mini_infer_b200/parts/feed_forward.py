@@ -136,8 +136,8 @@ class SparseMoE(FeedForward):
         self._route_small_max = F.route_small_max_tokens()
         self._route_ticket = torch.zeros(1 + self._route_small_max, dtype=torch.int32, device=dev)
         self._pairs_max = min(self._route_small_max, F.skinny_pairs_max_tokens())
-        self._tc = (rt.act == torch.bfloat16 and F.grouped_gemm_tc_supported(self.H, self.mI)
-                    and F.grouped_gemm_tc_supported(self.mI, self.H) and self.H % 8 == 0)
+        self._tc = (rt.act == torch.bfloat16 and F.grouped_gemm_tc_supported(self.H)
+                    and F.grouped_gemm_tc_supported(self.mI) and self.H % 8 == 0)
         self._skinny = (rt.act == torch.bfloat16 and F.grouped_gemm_skinny_supported(self.H)
                         and F.grouped_gemm_skinny_supported(self.mI))
 

@@ -341,14 +341,11 @@ def greedy(logits: Tensor) -> int:
     return int((logits == m).nonzero()[0, 0])
 
 
-def sample(logits: Tensor, temperature: float, top_p: float, u: float) -> int:
-    """``p = softmax(logits / T)``; with ``top_p < 1`` the nucleus is every token
-    whose probability is at least ``tau``, the largest probability value for
-    which the tokens at or above it hold a mass of at least ``top_p``; the token
-    is the first, in index order, whose cumulative nucleus mass exceeds
-    ``u * (nucleus mass)``."""
-    if temperature <= 0.0:
-        return greedy(logits)
+def nucleus_cdf(logits: Tensor, temperature: float, top_p: float) -> Tuple[Tensor, Tensor]:
+    """``p = softmax(logits / T)``; with ``top_p < 1`` the nucleus is every token whose probability is at
+    least ``tau``, the largest probability value for which the tokens at or above it hold a mass of at
+    least ``top_p``.  Returns the cumulative nucleus mass in index order (float64, not normalised) and
+    the nucleus as a mask."""
     p = torch.softmax(logits.to(torch.float32) / temperature, dim=-1)
     keep = torch.ones_like(p, dtype=torch.bool)
     if top_p < 1.0:
@@ -358,7 +355,15 @@ def sample(logits: Tensor, temperature: float, top_p: float, u: float) -> int:
         tau = vals[min(n, vals.numel()) - 1]
         keep = p >= tau
     pk = torch.where(keep, p, torch.zeros_like(p)).to(torch.float64)
-    cdf = torch.cumsum(pk, dim=0)
+    return torch.cumsum(pk, dim=0), keep
+
+
+def sample(logits: Tensor, temperature: float, top_p: float, u: float) -> int:
+    """The token is the first, in index order, whose cumulative nucleus mass (:func:`nucleus_cdf`)
+    exceeds ``u * (nucleus mass)``; arg-max at temperature 0."""
+    if temperature <= 0.0:
+        return greedy(logits)
+    cdf, keep = nucleus_cdf(logits, temperature, top_p)
     target = u * float(cdf[-1])
     hit = (cdf > target).nonzero()
     if hit.numel() == 0:

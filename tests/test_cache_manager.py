@@ -176,6 +176,24 @@ def test_errors():
         m.truncate("a", 3)
 
 
+def test_truncate_cannot_reach_into_pages_a_window_released():
+    """A window group gives pages back as the window moves on; going back to a length whose window needs
+    one of them is refused, going back inside what is still held is not."""
+    m = CacheManager([KVGroupSpec(1, 8, 0), KVGroupSpec(1, 8, 6)], [16, 16], 4, 2)
+    m.add_request("a")
+    m.reserve("a", 20)
+    m.commit("a")                                # window 6 at 20 tokens: keys from 15, pages 0..2 released
+    assert m.block_table(1, "a")[:3] == [-1, -1, -1] and m.block_table(1, "a")[3] >= 0
+    with pytest.raises(ValueError, match="released pages"):
+        m.truncate("a", 14)                      # a query at 14 reads keys 9..14: page 2 is gone
+    assert m.num_tokens("a") == 20
+    m.truncate("a", 18)                          # reads keys 13..18 -> from page 3 on: fine
+    assert m.num_tokens("a") == 18
+    m.check_invariants()
+    m.release("a")
+    m.check_invariants()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_of_requests(seed):
     rng = random.Random(seed)

@@ -73,3 +73,29 @@ def test_trace_run_mixed(tmp_path, name, dtype):
                 assert float((row - ref[rid][pos]).abs().max()) <= tol * float(ref[rid].abs().max()), (i, rid, pos)
         for rid, toks, _ in st["entries"]:
             fed[rid] += len(toks)
+
+
+def test_trace_run_dumps_the_residual_stream_after_every_layer(tmp_path):
+    """``--dump-intermediates``: the hidden rows after each layer, against the plain model's record, for a
+    prompt cut into two portions and a decoded token (float32, so that every layer must agree closely)."""
+    cfg = tiny.CONFIGS["B"]
+    folder = tiny.make_folder(str(tmp_path / "model"), cfg, seed=19, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    toks = tiny.pick_tokens(cfg, w, 30, 3, min_gap=1e-4)
+    cuts = [(0, 17), (17, 29), (29, 30)]
+    lines = [json.dumps({"step": i, "entries": [{"id": "x", "tokens": toks[a:b], "want": [b - a - 1]}], "end": []})
+             for i, (a, b) in enumerate(cuts)]
+    out = str(tmp_path / "out")
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out,
+                        "--max-tokens", "64", "--dump-intermediates"], input="\n".join(lines) + "\n",
+                       capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    rec = {}
+    pm.forward(cfg, w, toks, record=rec)
+    H = cfg["hidden_size"]
+    for i, (a, b) in enumerate(cuts):
+        for layer in range(cfg["num_hidden_layers"]):
+            got = np.fromfile(os.path.join(out, f"{i}.layer{layer}.f32"), dtype="<f4").reshape(b - a, H)
+            ref = rec["hidden"][layer][a:b]
+            err = float((torch.from_numpy(got.copy()) - ref).abs().max())
+            assert err <= 2e-5 * float(ref.abs().max()), (i, layer, err)

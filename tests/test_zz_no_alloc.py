@@ -5,7 +5,8 @@
 device-memory budget fixed at start-up, in a host without an allocator to hand scratch from): it keeps the decode kernel's per-split partials in an array built into the library.
 The test loads the shared library with ctypes, calls the symbol directly, twice in a row on
 different inputs (the array keeps the first call's contents), and compares each result with the
-existing entry point ``mi_attn_decode`` given caller scratch.  It is collected last so that a run
+existing entry point ``mi_attn_decode`` given caller scratch, and with the plain attention of
+``tests/plain_model.py`` over the keys and values unpacked from the pages.  It is collected last so that a run
 that stops at the first failure has already run every other test, and it passes alone in a fresh
 process as well.
 """
@@ -15,6 +16,8 @@ import random
 
 import pytest
 import torch
+
+import plain_model as pm
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -82,6 +85,16 @@ def test_no_alloc_entry_point_matches_the_existing_one_twice_in_a_row(dtype, cod
         tol = (3e-6 if dtype == torch.float32 else 1e-2) * float(out_b.float().abs().max())
         assert err <= tol, f"call with seed {seed}: {err} > {tol}"
         assert float(out_a.float().abs().max()) > 0.0
+        # and against the plain attention over the unpacked pages
+        for b, n in enumerate(kv_lens):
+            pages = table[b, :-(-n // ps)].long()
+            k = kc[pages].float().transpose(1, 2).reshape(-1, nkv, d)[:n].cpu()      # [n, nkv, d]
+            v = vc[pages].float().transpose(1, 2).reshape(-1, nkv, d)[:n].cpu()
+            q_all = torch.zeros(n, nh, d)
+            q_all[n - 1] = q[b].float().cpu()
+            ref = pm.attention_scores_softmax_pv(q_all, k, v, 0)[n - 1]
+            err = float((out_a[b].float().cpu() - ref).abs().max())
+            assert err <= (3e-6 if dtype == torch.float32 else 1e-2) * float(ref.abs().max()), (seed, b, err)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():

@@ -1,6 +1,8 @@
-"""Paged key/value cache management and per-request state slots (host side)."""
+"""Paged cache management and per-request state slots (host side)."""
 
-from .manager import CacheManager, KVGroupSpec, plan_groups
+from .manager import CacheGroupSpec, CacheManager, KVGroupSpec, plan_groups
+from .needs import KVNeed, PagedCacheNeed, StateNeed
 from .pages import OutOfPages, OutOfSlots, PagePool, SlotPool
 
-__all__ = ["CacheManager", "KVGroupSpec", "plan_groups", "OutOfPages", "OutOfSlots", "PagePool", "SlotPool"]
+__all__ = ["CacheGroupSpec", "CacheManager", "KVGroupSpec", "plan_groups", "KVNeed", "PagedCacheNeed", "StateNeed",
+           "OutOfPages", "OutOfSlots", "PagePool", "SlotPool"]

@@ -25,21 +25,37 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+from .needs import KVNeed, PagedCacheNeed
 from .pages import OutOfPages, OutOfSlots, PagePool, SlotPool
 
 
 @dataclass(frozen=True)
-class KVGroupSpec:
-    """Geometry and retention of one group; ``entries`` are the schedule positions it serves."""
+class CacheGroupSpec:
+    """One group: what its layers keep per token (``need``: tensors per page, retention, share of the
+    page budget) and the cache owners it serves (``entries``: anything hashable, the engine uses
+    ``(schedule position, role)``)."""
 
-    num_kv_heads: int
-    head_dim: int
-    window: int = 0
-    entries: Tuple[int, ...] = ()
+    need: PagedCacheNeed
+    entries: Tuple[Hashable, ...] = ()
 
     @property
     def num_layers(self) -> int:
         return len(self.entries)
+
+    @property
+    def window(self) -> int:
+        return int(self.need.window)
+
+    def __getattr__(self, name):
+        # geometry of the need (num_kv_heads, head_dim, ...) read through the group
+        if name in ("need", "entries"):
+            raise AttributeError(name)
+        return getattr(self.need, name)
+
+
+def KVGroupSpec(num_kv_heads: int, head_dim: int, window: int = 0, entries: Tuple[Hashable, ...] = ()) -> CacheGroupSpec:
+    """A group of key/value layers (the common case), as a :class:`CacheGroupSpec`."""
+    return CacheGroupSpec(KVNeed(num_kv_heads, head_dim, window), tuple(entries))
 
 
 @dataclass
@@ -52,7 +68,7 @@ class _Request:
 
 
 class CacheManager:
-    def __init__(self, groups: Sequence[KVGroupSpec], num_pages: Sequence[int], page_size: int,
+    def __init__(self, groups: Sequence[CacheGroupSpec], num_pages: Sequence[int], page_size: int,
                  num_slots: int):
         if page_size < 1 or page_size & (page_size - 1):
             raise ValueError(f"CacheManager: page size {page_size} must be a power of two")
@@ -252,18 +268,19 @@ class CacheManager:
             raise AssertionError("a state slot is lost")
 
 
-def plan_groups(needs: Sequence[Tuple[int, object]]) -> Tuple[List[KVGroupSpec], Dict[int, Tuple[int, int]]]:
-    """Sort schedule entries that keep keys and values into groups.
+def plan_groups(needs: Sequence[Tuple[Hashable, PagedCacheNeed]]) -> Tuple[List[CacheGroupSpec], Dict[Hashable, Tuple[int, int]]]:
+    """Sort cache owners into groups.
 
-    ``needs``: (schedule position, KVNeed) for every entry that owns a cache.
-    Returns the groups and ``position -> (group index, layer slot)``.
+    ``needs``: (owner, need) for everything that owns a paged cache.  Owners whose needs have the same
+    ``group_key()`` (tensors, window, share of the budget) share a group.  Returns the groups and
+    ``owner -> (group index, layer slot)``.
     """
-    keyed: Dict[Tuple[int, int, int], List[int]] = {}
-    for pos, need in needs:
-        keyed.setdefault((need.num_kv_heads, need.head_dim, need.window), []).append(pos)
+    keyed: Dict[tuple, Tuple[PagedCacheNeed, List[Hashable]]] = {}
+    for owner, need in needs:
+        keyed.setdefault(need.group_key(), (need, []))[1].append(owner)
     groups, where = [], {}
-    for gi, (key, entries) in enumerate(keyed.items()):
-        groups.append(KVGroupSpec(key[0], key[1], key[2], tuple(entries)))
-        for li, pos in enumerate(entries):
-            where[pos] = (gi, li)
+    for gi, (need, owners) in enumerate(keyed.values()):
+        groups.append(CacheGroupSpec(need, tuple(owners)))
+        for li, owner in enumerate(owners):
+            where[owner] = (gi, li)
     return groups, where

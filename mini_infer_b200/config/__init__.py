@@ -3,9 +3,9 @@
 from .model_config import ConfigError, Qwen2MoeConfig, architecture_name, read_config_json
 from .registry import (UnknownArchitecture, UnknownPart, build_model_spec, known_architectures, known_parts,
                        part_class, register_architecture, register_part)
-from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule
+from .spec import LayerPart, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule, prenorm_layer
 
 __all__ = ["ConfigError", "Qwen2MoeConfig", "architecture_name", "read_config_json", "UnknownArchitecture",
            "UnknownPart", "build_model_spec", "known_architectures", "known_parts", "part_class",
-           "register_architecture", "register_part", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
+           "register_architecture", "register_part", "LayerPart", "LayerSpec", "prenorm_layer", "ModelSpec", "PartSpec", "ScheduleEntry",
            "default_schedule"]

@@ -1,8 +1,9 @@
 """Data that describes a model as an arrangement of parts.
 
 A model is not a class hierarchy here but a :class:`ModelSpec`: a tuple of
-:class:`LayerSpec` (each naming, by *kind* and parameters, its mixer, its
-feed-forward, its two norms and the block arrangement that wires them) plus a
+:class:`LayerSpec` (each naming its block arrangement and, by *role*, the parts
+the arrangement wires together: for the usual pre-norm block a mixer, a
+feed-forward and two norms; another arrangement names other roles) plus a
 *schedule*, the order in which layers run.  The schedule is data as well: it
 may name a layer twice (the weights are shared, each run has a cache of its
 own) and an entry may read the cache that an earlier entry wrote instead of
@@ -32,29 +33,71 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
-class LayerSpec:
-    """One set of weights: a mixer, a feed-forward, their norms, a block kind.
+class LayerPart:
+    """One part of a layer: its registry category, its kind and constants, and its checkpoint
+    sub-prefix below the layer's name."""
 
-    ``name`` is the checkpoint prefix of the layer (``model.layers.3``).
+    category: str
+    spec: PartSpec
+    prefix: str = ""
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One set of weights: a block kind and the parts it arranges, by role.
+
+    ``name`` is the checkpoint prefix of the layer (``model.layers.3``).  Which roles there are is the
+    block kind's business (``Block.roles``): the pre-norm residual block wants ``mixer``, ``feed_forward``,
+    ``mixer_norm`` and ``feed_forward_norm``; a block with four norms, or without a feed-forward, is
+    another block class with other roles, and nothing else changes.  A role's ``PartSpec`` can be read as
+    an attribute (``layer.mixer``).
     """
 
     name: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    block: PartSpec = PartSpec("prenorm_residual")
-    # checkpoint sub-prefixes of the parts below ``name``
-    mixer_prefix: str = "self_attn."
-    feed_forward_prefix: str = "mlp."
-    mixer_norm_prefix: str = "input_layernorm."
-    feed_forward_norm_prefix: str = "post_attention_layernorm."
+    block: PartSpec
+    parts: Mapping[str, LayerPart]
+
+    def __getattr__(self, role: str) -> PartSpec:
+        if role in ("name", "block", "parts") or role.startswith("__"):
+            raise AttributeError(role)
+        try:
+            return self.parts[role].spec
+        except KeyError:
+            raise AttributeError(f"layer '{self.name}' has no part in the role '{role}' "
+                                 f"(roles: {', '.join(self.parts)})") from None
+
+    def with_part(self, role: str, spec: PartSpec, category: Optional[str] = None,
+                  prefix: Optional[str] = None) -> "LayerSpec":
+        """A copy with the part of ``role`` replaced (or added: then ``category`` is needed)."""
+        old = self.parts.get(role)
+        if old is None and category is None:
+            raise ValueError(f"layer '{self.name}': a new role '{role}' needs its category")
+        part = LayerPart(category or old.category, spec, prefix if prefix is not None else (old.prefix if old else ""))
+        return LayerSpec(self.name, self.block, {**self.parts, role: part})
+
+    def renamed(self, name: str) -> "LayerSpec":
+        return LayerSpec(name, self.block, dict(self.parts))
+
+
+def prenorm_layer(name: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                  feed_forward_norm: PartSpec, block: PartSpec = PartSpec("prenorm_residual"),
+                  mixer_prefix: str = "self_attn.", feed_forward_prefix: str = "mlp.",
+                  mixer_norm_prefix: str = "input_layernorm.",
+                  feed_forward_norm_prefix: str = "post_attention_layernorm.") -> LayerSpec:
+    """The usual layer: norm, mixer, norm, feed-forward around a residual stream, with the checkpoint
+    names of the LLaMA/Qwen family."""
+    return LayerSpec(name, block, {
+        "mixer_norm": LayerPart("norm", mixer_norm, mixer_norm_prefix),
+        "mixer": LayerPart("mixer", mixer, mixer_prefix),
+        "feed_forward_norm": LayerPart("norm", feed_forward_norm, feed_forward_norm_prefix),
+        "feed_forward": LayerPart("feed_forward", feed_forward, feed_forward_prefix),
+    })
 
 
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``cache_from`` names an earlier schedule position
-    whose cache this run reads (it then writes none of its own)."""
+    whose caches this run reads, role by role (it then writes none of its own)."""
 
     layer: int
     cache_from: Optional[int] = None

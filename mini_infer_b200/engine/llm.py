@@ -140,7 +140,7 @@ class LLM:
         if num_pages is None:
             num_pages = max_running * pages_per_req
             item = 4 if self.rt.precision.name == "float32" else 2
-            per_page = sum(2 * g.num_layers * g.num_kv_heads * g.head_dim * page_size * item
+            per_page = sum(g.num_layers * g.need.bytes_per_page(page_size, item) * float(g.need.pages_fraction)
                            for g in self.model.kv_groups)
             free, _ = torch.cuda.mem_get_info(self.rt.device)
             if per_page:

@@ -14,11 +14,11 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..cache.manager import KVGroupSpec, plan_groups
+from ..cache.manager import plan_groups
 from ..config.registry import part_class
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import (BuiltLayer, CacheBinding, KVNeed, Part, Runtime, StateNeed, StepContext, TensorDecl,
-                          apply_norm, resolve)
+from ..parts.base import (BuiltLayer, CacheBinding, PagedCacheNeed, Part, Runtime, StateNeed, StepContext,
+                          TensorDecl, apply_norm, resolve)
 
 
 def _make(category: str, spec: PartSpec, prefix: str) -> Part:
@@ -26,15 +26,20 @@ def _make(category: str, spec: PartSpec, prefix: str) -> Part:
 
 
 def build_layer(ls: LayerSpec) -> BuiltLayer:
+    """Instantiate the block and every part the layer names; the block kind says which roles it wires,
+    and a description that lacks one, or brings one the block does not know, is refused."""
     base = ls.name + "." if ls.name else ""
-    return BuiltLayer(
-        name=ls.name,
-        mixer=_make("mixer", ls.mixer, base + ls.mixer_prefix),
-        feed_forward=_make("feed_forward", ls.feed_forward, base + ls.feed_forward_prefix),
-        mixer_norm=_make("norm", ls.mixer_norm, base + ls.mixer_norm_prefix),
-        feed_forward_norm=_make("norm", ls.feed_forward_norm, base + ls.feed_forward_norm_prefix),
-        block=_make("block", ls.block, base),
-    )
+    block = _make("block", ls.block, base)
+    wanted = dict(getattr(block, "roles", {}) or {})
+    if wanted:
+        missing = [r for r in wanted if r not in ls.parts]
+        extra = [r for r in ls.parts if r not in wanted]
+        wrong = [r for r in wanted if r in ls.parts and ls.parts[r].category != wanted[r]]
+        if missing or extra or wrong:
+            raise ValueError(f"layer '{ls.name}': block '{ls.block.kind}' arranges the roles {sorted(wanted)}; "
+                             f"missing {missing}, unknown {extra}, of another category {wrong}")
+    parts = {role: _make(lp.category, lp.spec, base + lp.prefix) for role, lp in ls.parts.items()}
+    return BuiltLayer(ls.name, block, parts)
 
 
 class Model:
@@ -55,45 +60,56 @@ class Model:
 
     # -- what the model keeps between steps --------------------------------- #
     def _plan_caches(self) -> None:
-        kv_needs: List[Tuple[int, KVNeed]] = []
-        self.state_needs: List[Tuple[int, StateNeed]] = []
-        needs = []
+        """Every part of a layer may keep something between steps (``cache_need()``): entries per token in
+        pages, or a fixed-size state per request.  An owner is a (schedule position, role) pair; owners
+        with the same paged need share a group (a pool and block tables of its own).  ``bindings[pos]``
+        maps the roles of schedule entry ``pos`` that keep a cache to where they find it."""
+        paged: List[Tuple[Tuple[int, str], PagedCacheNeed]] = []
+        self.state_needs: List[Tuple[Tuple[int, str], StateNeed]] = []
+        needs: List[Dict[str, object]] = []
         for pos, e in enumerate(self.spec.schedule):
-            need = self.layers[e.layer].mixer.cache_need()
-            needs.append(need)
-            if e.cache_from is not None:
-                src = needs[e.cache_from]
-                if not isinstance(need, KVNeed) or not isinstance(src, KVNeed) or \
-                        (need.num_kv_heads, need.head_dim) != (src.num_kv_heads, src.head_dim):
-                    raise ValueError(f"schedule[{pos}] reads the cache of schedule[{e.cache_from}], "
-                                     f"whose geometry differs")
-                continue
-            if isinstance(need, KVNeed):
-                kv_needs.append((pos, need))
-            elif isinstance(need, StateNeed):
-                self.state_needs.append((pos, need))
-            elif need is not None:
-                raise TypeError(f"schedule[{pos}]: cache_need() returned {type(need).__name__}")
-        self.kv_groups, where = plan_groups(kv_needs)
-        self.bindings: List[CacheBinding] = []
-        state_index = {pos: i for i, (pos, _) in enumerate(self.state_needs)}
+            mine: Dict[str, object] = {}
+            for role, part in self.layers[e.layer].parts.items():
+                fn = getattr(part, "cache_need", None)
+                need = fn() if fn else None
+                if need is None:
+                    continue
+                if not isinstance(need, (PagedCacheNeed, StateNeed)):
+                    raise TypeError(f"schedule[{pos}] {role}: cache_need() returned {type(need).__name__}")
+                mine[role] = need
+            needs.append(mine)
+            for role, need in mine.items():
+                if e.cache_from is not None and isinstance(need, PagedCacheNeed):
+                    src = needs[e.cache_from].get(role)
+                    if not isinstance(src, PagedCacheNeed) or src.geometry() != need.geometry():
+                        raise ValueError(f"schedule[{pos}] reads the cache of schedule[{e.cache_from}], "
+                                         f"whose geometry differs")
+                    continue
+                if isinstance(need, PagedCacheNeed):
+                    paged.append(((pos, role), need))
+                else:
+                    self.state_needs.append(((pos, role), need))
+        self.kv_groups, where = plan_groups(paged)
+        state_index = {owner: i for i, (owner, _) in enumerate(self.state_needs)}
+        self.bindings: List[Dict[str, CacheBinding]] = []
         for pos, e in enumerate(self.spec.schedule):
-            if e.cache_from is not None:
-                g, li = where[e.cache_from]
-                self.bindings.append(CacheBinding("kv", g, li, writes=False))
-            elif pos in where:
-                g, li = where[pos]
-                self.bindings.append(CacheBinding("kv", g, li, writes=True))
-            elif pos in state_index:
-                self.bindings.append(CacheBinding("state", state_index[pos], -1, True))
-            else:
-                self.bindings.append(CacheBinding("none"))
+            found: Dict[str, CacheBinding] = {}
+            for role, need in needs[pos].items():
+                if isinstance(need, StateNeed):
+                    found[role] = CacheBinding("state", state_index[(pos, role)], -1, True)
+                elif e.cache_from is not None:
+                    g, li = where[(e.cache_from, role)]
+                    found[role] = CacheBinding("kv", g, li, writes=False)
+                else:
+                    g, li = where[(pos, role)]
+                    found[role] = CacheBinding("kv", g, li, writes=True)
+            self.bindings.append(found)
 
     # -- weights ------------------------------------------------------------ #
     def all_parts(self) -> List[Part]:
         parts: List[Part] = [self.embedding]
         for layer in self.layers:
-            parts.extend(layer.parts())
+            parts.extend(layer.all_parts())
         parts += [self.final_norm, self.lm_head]
         return parts
 
@@ -127,8 +143,8 @@ class Model:
 
     def scratch_need(self, max_requests: int, max_context: int) -> Dict[str, int]:
         need: Dict[str, int] = {}
-        for layer in self.layers:
-            fn = getattr(layer.mixer, "scratch_need", None)
+        for part in self.all_parts():
+            fn = getattr(part, "scratch_need", None)
             if fn:
                 for k, v in fn(max_requests, max_context).items():
                     need[k] = max(need.get(k, 0), v)

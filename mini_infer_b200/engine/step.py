@@ -72,24 +72,34 @@ class ModelRunner:
         self.max_context = int(max_context)
         self.vocab_size = model.spec.vocab_size
         groups = model.kv_groups
-        self.cache = CacheManager(groups, [num_pages] * len(groups), page_size, max_requests)
         dev, act = rt.device, rt.act
-        self.kv_tensors = []
+        # Pages per group: the budget times the need's own share; a group behind a window never holds more
+        # than its window and one step's tokens per request, so it is not given more than that.
+        pages = []
         for g in groups:
-            shape = (g.num_layers, num_pages, g.num_kv_heads, page_size, g.head_dim)
-            self.kv_tensors.append((torch.zeros(shape, dtype=act, device=dev),
-                                    torch.zeros(shape, dtype=act, device=dev)))
-        self.state_tensors = [torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype, device=dev)
-                              for _, need in model.state_needs]
+            n = max(1, int(num_pages * float(g.need.pages_fraction)))
+            if g.window > 0:
+                per_request = -(-(g.window + self.max_tokens) // self.page_size) + 2
+                n = min(n, max_requests * min(per_request, -(-self.max_context // self.page_size)))
+            pages.append(n)
+        self.cache = CacheManager(groups, pages, page_size, max_requests)
+        # the tensors every group's need names: [layers of the group, pages, *shape of one page]
+        self.kv_tensors: List[Dict[str, torch.Tensor]] = []
+        for g, n in zip(groups, pages):
+            self.kv_tensors.append({name: torch.zeros((g.num_layers, n) + tuple(shape), dtype=dtype or act, device=dev)
+                                    for name, shape, dtype in g.need.tensors(page_size)})
+        self.state_tensors = [torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype or torch.float32,
+                                          device=dev) for _, need in model.state_needs]
         self.scratch = {k: torch.empty(n, dtype=torch.float32, device=dev)
                         for k, n in model.scratch_need(max_requests, max_context).items()}
         self.max_pages = -(-self.max_context // self.page_size)
         self._layout_staging()
         # Decode steps (one token per request, logits wanted for each) are launch-bound: their
         # forward pass is captured once per batch size as a CUDA graph and replayed.  Parts that
-        # keep host-side state per step, or were not written with replay in mind, switch this off.
-        self.cuda_graphs = bool(cuda_graphs) and not model.state_needs and \
-            all(getattr(p, "graph_safe", False) for p in model.all_parts())
+        # read host-side data of the step, or were not written with replay in mind, switch this off
+        # by not declaring ``graph_safe``; a part with a state of its own may declare it (its state
+        # tensor is static memory that a captured pass updates in place).
+        self.cuda_graphs = bool(cuda_graphs) and all(getattr(p, "graph_safe", False) for p in model.all_parts())
         self._graphs: Dict[tuple, tuple] = {}
         # parts with settings that change what a captured pass launches, or that leave side outputs
         from ..parts.base import Part
@@ -267,10 +277,9 @@ class ModelRunner:
             d("token_ids", T).copy_(device_tokens[:T], non_blocking=True)
         views = []
         for g in range(len(self.model.kv_groups)):
-            k, v = self.kv_tensors[g]
             views.append(KVGroupView(
                 block_table=d(f"block_table{g}", B * self.max_pages).view(B, self.max_pages),
-                slot_mapping=d(f"slot_mapping{g}", T), page_size=self.page_size, k=k, v=v))
+                slot_mapping=d(f"slot_mapping{g}", T), page_size=self.page_size, tensors=self.kv_tensors[g]))
         max_q, max_kv = int(counts.max()), int(kv_len.max())
         ctx = StepContext(
             num_tokens=T, num_requests=B, max_q_len=max_q, max_kv_len=max_kv, all_decode=(max_q == 1),
@@ -301,11 +310,17 @@ class ModelRunner:
         parts = self._keyed_parts
         key = (B, ctx.max_kv_len, tuple(p.capture_key() for p in parts))
         if key not in self._graphs:
+            # The warm-up pass (library workspaces, lazy initialisation) runs the step for real: what it
+            # writes into the paged caches is written again by the replay, but a per-request state would
+            # be advanced twice, so states are put back after it.
+            kept = [st.clone() for st in self.state_tensors]
             side = torch.cuda.Stream(device=self.rt.device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self.model.forward(ctx, logit_rows)          # warm-up: library workspaces, lazy init
+                self.model.forward(ctx, logit_rows)
             torch.cuda.current_stream().wait_stream(side)
+            for st, old in zip(self.state_tensors, kept):
+                st.copy_(old)
             torch.cuda.synchronize(self.rt.device)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
@@ -327,6 +342,13 @@ class ModelRunner:
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> StepResult:
         ctx, logit_rows, index = self.prepare(entries)
+        # What a failed step wrote into the paged caches lies beyond every request's committed tokens and
+        # is written again; a per-request state is updated in place, so the entries' slots are kept aside
+        # and put back if the forward pass fails.
+        saved = None
+        if self.state_tensors:
+            slots = torch.as_tensor(ctx.host_state_slot, dtype=torch.long, device=self.rt.device)
+            saved = (slots, [st.index_select(0, slots) for st in self.state_tensors])
         try:
             if self._graph_eligible(entries):
                 logits = self._decode_with_graph(ctx, logit_rows)
@@ -337,6 +359,9 @@ class ModelRunner:
         except Exception:
             for e in entries:
                 self.cache.cancel(e.rid)
+            if saved is not None:
+                for st, rows in zip(self.state_tensors, saved[1]):
+                    st.index_copy_(0, saved[0], rows)
             raise
         for e in entries:
             self.cache.commit(e.rid)
@@ -346,7 +371,11 @@ class ModelRunner:
     # a decode step launched ahead of the scheduler's decision
     # ------------------------------------------------------------------ #
     def can_step_ahead(self, rids: Sequence[Hashable]) -> bool:
-        """A step of one token per request can be launched ahead only as a graph replay."""
+        """A step of one token per request can be launched ahead only as a graph replay, and only by a
+        model without per-request state: a dropped step's cache writes lie beyond the committed tokens
+        and are overwritten, but a state updated in place could not be taken back."""
+        if self.state_tensors:
+            return False
         return self._graph_eligible([StepEntry(r, [0], [0]) for r in rids])
 
     @torch.no_grad()

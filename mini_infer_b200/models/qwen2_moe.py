@@ -20,7 +20,7 @@ from typing import Any, Dict
 
 from ..config.model_config import Qwen2MoeConfig
 from ..config.registry import register_architecture
-from ..config.spec import LayerSpec, ModelSpec, PartSpec, default_schedule
+from ..config.spec import ModelSpec, PartSpec, default_schedule, prenorm_layer
 
 
 def build_qwen2_moe(config_json: Dict[str, Any]) -> ModelSpec:
@@ -42,8 +42,7 @@ def build_qwen2_moe(config_json: Dict[str, Any]) -> ModelSpec:
         else:
             ffn = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": c.intermediate_size})
         norm = PartSpec("rmsnorm", {"size": H, "eps": c.rms_norm_eps})
-        layers.append(LayerSpec(name=name, mixer=mixer, feed_forward=ffn, mixer_norm=norm,
-                                feed_forward_norm=norm, block=PartSpec("prenorm_residual")))
+        layers.append(prenorm_layer(name, mixer, ffn, norm, norm))
     return ModelSpec(
         architecture=c.architecture,
         hidden_size=H,

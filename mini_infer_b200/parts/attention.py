@@ -18,6 +18,7 @@ from ..config.registry import part_class, register_part
 from ..config.spec import PartSpec
 from ..ops import functional as F
 from .base import CacheBinding, KVNeed, Mixer, Runtime, StepContext, TensorDecl, linear
+from .tuning import TUNING
 
 
 class GQAttention(Mixer):
@@ -111,8 +112,11 @@ class GQAttention(Mixer):
                            view.slot_mapping if nkv_in else None, kc if nkv_in else None, vc if nkv_in else None,
                            self.nh, nkv_in, self.d, view.page_size, self.rt.act)
         if ctx.all_decode and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d):
-            # one or two requests alone cannot fill the device with splits of 512 keys
-            split = 128 if ctx.num_requests <= 2 else (256 if ctx.num_requests <= 4 else F.decode_split_size())
+            # one or two requests alone cannot fill the device with splits of 512 keys (bfloat16 path only:
+            # the float32 path keeps one split size, so that a request's logits do not depend on its batch)
+            split = F.decode_split_size()
+            if self.rt.act == torch.bfloat16:
+                split = TUNING.decode_split(ctx.num_requests, split)
             splits = -(-ctx.max_kv_len // split)
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
                                    ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window,

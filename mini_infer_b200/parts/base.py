@@ -112,25 +112,10 @@ def configure_matmul_exactness() -> None:
 
 
 # --------------------------------------------------------------------------- #
-# what a mixer keeps
+# what a part keeps between steps: see cache/needs.py
 # --------------------------------------------------------------------------- #
 
-@dataclass(frozen=True)
-class KVNeed:
-    """Keys and values per token: ``window = 0`` keeps all of them, ``window = W``
-    only the last ``W`` (older pages are given back)."""
-
-    num_kv_heads: int
-    head_dim: int
-    window: int = 0
-
-
-@dataclass(frozen=True)
-class StateNeed:
-    """A fixed-size state per request (``shape`` per slot), zeroed when a request starts."""
-
-    shape: Tuple[int, ...]
-    dtype: torch.dtype = torch.float32
+from ..cache.needs import KVNeed, PagedCacheNeed, StateNeed  # noqa: E402  (re-exported for part authors)
 
 
 # --------------------------------------------------------------------------- #
@@ -139,13 +124,22 @@ class StateNeed:
 
 @dataclass
 class KVGroupView:
-    """Device metadata of one cache group for the current step."""
+    """Device metadata of one cache group for the current step, and the group's tensors: for every
+    tensor its need names, ``[layers_in_group, pages, *shape of one page]`` (for keys and values:
+    ``k`` and ``v`` of ``[layers, pages, nkv, page_size, d]``)."""
 
     block_table: torch.Tensor      # [B, max_pages] int32, -1 = no page
     slot_mapping: torch.Tensor     # [T] int32: page * page_size + offset of each new token
     page_size: int
-    k: torch.Tensor                # [layers_in_group, pages, nkv, page_size, d]
-    v: torch.Tensor
+    tensors: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.tensors["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.tensors["v"]
 
 
 @dataclass
@@ -318,37 +312,50 @@ class LMHead(Part):
 
 
 class Block(Part):
+    """The arrangement of a layer's parts around the residual stream.
+
+    ``roles`` maps every role the arrangement wires to its registry category; a layer description must
+    provide exactly these (it is checked when the layer is built).  ``forward`` gets the built layer
+    (parts by role: ``layer.mixer`` or ``layer.parts["mixer"]``), the float32 residual stream, the output
+    of the part before that has not been added yet (``pending``), and ``caches``: for every role that
+    keeps a cache, where it finds it."""
+
     category = "block"
     accepts_deferred = False    # True: ``forward`` takes a Deferred as ``pending`` and may return one
+    roles: Mapping[str, str] = {}
 
     def forward(self, layer: "BuiltLayer", hidden: torch.Tensor, pending: Optional[torch.Tensor],
-                ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+                ctx: StepContext, caches: Mapping[str, CacheBinding]) -> torch.Tensor:
         raise NotImplementedError
 
 
-@dataclass
 class BuiltLayer:
-    """The instantiated parts of one :class:`LayerSpec`."""
+    """The instantiated parts of one ``LayerSpec``: ``block`` and ``parts`` by role (a role can be read
+    as an attribute: ``layer.mixer``)."""
 
-    name: str
-    mixer: Mixer
-    feed_forward: FeedForward
-    mixer_norm: Norm
-    feed_forward_norm: Norm
-    block: Block
+    def __init__(self, name: str, block: Block, parts: Dict[str, Part]):
+        self.name = name
+        self.block = block
+        self.parts = dict(parts)
 
-    def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.block]
+    def __getattr__(self, role: str) -> Part:
+        parts = self.__dict__.get("parts")
+        if parts is not None and role in parts:
+            return parts[role]
+        raise AttributeError(f"layer '{self.__dict__.get('name')}' has no part in the role '{role}'")
+
+    def all_parts(self) -> List[Part]:
+        return list(self.parts.values()) + [self.block]
 
 
-SKINNY_MAX_TOKENS = 8   # steps up to this size run the dense products on the engine's own decode kernel
+from .tuning import TUNING  # noqa: E402
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
     """``silu(x @ w_gate.T) * (x @ w_up.T)`` in the activation dtype; ``w_gate_up`` holds the gate
     rows then the up rows (src/layers/mlp.cpp:255-279 runs two products and an elementwise kernel)."""
     from ..ops import functional as F
-    if x.is_cuda and x.shape[0] <= SKINNY_MAX_TOKENS and F.dense_skinny_takes(x, w_gate_up):
+    if x.is_cuda and x.shape[0] <= TUNING.dense_skinny_max_tokens and F.dense_skinny_takes(x, w_gate_up):
         return F.dense_skinny(x, w_gate_up, swiglu_pair=True)
     return F.swiglu(linear(x, w_gate_up, act_dtype))
 
@@ -357,7 +364,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
     """``x @ w.T`` through the library product the reference also uses for every dense
     projection (cuBLAS, src/layers/attention.cpp:45-55, src/layers/mlp.cpp:120-130),
     accumulating in float32; ``w`` is ``[out, in]`` as stored in checkpoints."""
-    if out_dtype == torch.float32 and x.is_cuda and x.shape[0] <= SKINNY_MAX_TOKENS:
+    if out_dtype == torch.float32 and x.is_cuda and x.shape[0] <= TUNING.dense_skinny_max_tokens:
         from ..ops import functional as F
         if F.dense_skinny_takes(x, w):
             return F.dense_skinny(x, w)

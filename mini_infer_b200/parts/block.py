@@ -24,10 +24,11 @@ from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, 
 class PreNormResidual(Block):
     graph_safe = True
     accepts_deferred = True
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
-    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, cache: CacheBinding):
+    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, caches):
         x = apply_norm(layer.mixer_norm, hidden, pending)
-        y = layer.mixer.forward(x, ctx, cache)
+        y = layer.mixer.forward(x, ctx, caches.get("mixer"))
         return layer.feed_forward.forward_from_residual(hidden, y, layer.feed_forward_norm, ctx)
 
 

@@ -16,6 +16,7 @@ import torch
 from ..config.registry import register_part
 from ..ops import functional as F
 from .base import FeedForward, Runtime, StepContext, TensorDecl, WeightedRowSum, linear, linear_swiglu
+from .tuning import TUNING
 
 
 class SwiGLUMLP(FeedForward):
@@ -60,14 +61,8 @@ class SparseMoE(FeedForward):
     """
 
     graph_safe = True
-    # up to this many rows per expert on average, the decode-sized grouped product is used
-    SKINNY_ROWS_PER_EXPERT = 8
-    # The shared expert runs on a second stream beside the routed path: in decode-sized steps every kernel
-    # is short, and in prefill its library products are bound by the tensor cores while the grouped
-    # products of the routed experts are bound by memory (measured: 7 % off a 2,048-token prefill).
-    OVERLAP_SHARED_EXPERT = True
-    PRIORITY_SIDE_STREAM_MIN_TOKENS = 128
-    FORK_AFTER_ROUTING_MAX_TOKENS = 8
+    # which kernel a step of a given size takes, and where the shared expert is forked, are measured
+    # thresholds: parts/tuning.py
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -153,7 +148,7 @@ class SparseMoE(FeedForward):
         # Large steps run the shared expert as library products whose blocks fill an SM: on a stream of
         # higher priority they take their SMs ahead of the routing's small kernels, which slip into what
         # is left, whatever order the two streams' first kernels reach the device in.
-        big = x.shape[0] > self.PRIORITY_SIDE_STREAM_MIN_TOKENS
+        big = x.shape[0] > TUNING.shared_expert_priority_stream_min_tokens
         if big:
             if self._side_stream_big is None:
                 self._side_stream_big = torch.cuda.Stream(device=x.device, priority=-1)
@@ -181,8 +176,8 @@ class SparseMoE(FeedForward):
         (the routing's blocks read the row anyway); the others take the norm's own kernel."""
         T = hidden.shape[0]
         rms = norm.rms_parameters()
-        if (rms is not None and self._skinny and T <= min(self._pairs_max, self.FORK_AFTER_ROUTING_MAX_TOKENS)
-                and T * self.K <= self.SKINNY_ROWS_PER_EXPERT * self.E and F.norm_route_small_takes(self.H)
+        if (rms is not None and self._skinny and T <= min(self._pairs_max, TUNING.shared_expert_fork_after_routing_max_tokens)
+                and T * self.K <= TUNING.expert_skinny_rows_per_expert * self.E and F.norm_route_small_takes(self.H)
                 and (delta is None or isinstance(delta, torch.Tensor))):
             x, idx, w, gate, probs, _, _, _ = F.moe_norm_route_small(
                 hidden, delta, rms[0], rms[1], self.rt.act, self.w_router, self.w_shared_gate, self.K,
@@ -193,12 +188,12 @@ class SparseMoE(FeedForward):
     def _run(self, x: torch.Tensor, ctx: StepContext, routed) -> WeightedRowSum:
         T = x.shape[0]
         shared = side = inv_perm = None
-        overlap = self.sI > 0 and self.OVERLAP_SHARED_EXPERT
+        overlap = self.sI > 0 and TUNING.shared_expert_overlap
         n = T * self.K
-        if self._skinny and T <= self._pairs_max and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
+        if self._skinny and T <= self._pairs_max and n <= TUNING.expert_skinny_rows_per_expert * self.E:
             # decode-sized step: routing in one launch, no permutation; every used expert's weights
             # are read once and result rows are indexed by (token, slot) pair
-            fork_first = T > self.FORK_AFTER_ROUTING_MAX_TOKENS
+            fork_first = T > TUNING.shared_expert_fork_after_routing_max_tokens
             if overlap and fork_first:
                 side, shared = self._fork_shared_expert(x)
             if routed is not None:
@@ -222,7 +217,7 @@ class SparseMoE(FeedForward):
                 idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
                                                    want_probs=self.keep_routing)
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
-            if self._skinny and n <= self.SKINNY_ROWS_PER_EXPERT * self.E:
+            if self._skinny and n <= TUNING.expert_skinny_rows_per_expert * self.E:
                 # a few rows per expert: bound by reading each used expert once
                 act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
                 y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)

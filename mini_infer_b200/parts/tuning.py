@@ -1,0 +1,57 @@
+"""Thresholds that were found by measurement, in one place.
+
+Each of them chooses between kernels that compute the same thing, so a wrong value costs time, never
+correctness.  They were measured on one B200 with the layer sizes of Qwen1.5-MoE-A2.7B (hidden 2048,
+60 experts of 1408 with top-4 routing, shared expert 5632, 16 heads of 128) and checked at
+Qwen2-57B-A14B sizes; another width, expert count or GPU should re-measure them (``bench.py
+--point-batches`` walks the batch sizes around each threshold) rather than inherit them silently.
+``TUNING`` is the instance the parts read; a host program may replace its fields before it loads a model.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Tuple
+
+
+@dataclass
+class Tuning:
+    # Dense products (o_proj, shared expert, dense MLP, output head) of steps with at most this many tokens
+    # run on the engine's own decode kernel, which streams the weights once with 16 features per block;
+    # above it the library product is used.  Checked by decoding at batch 2, 4, 8, 16 and 32: throughput
+    # rises steadily across the threshold (no cliff between 8 and 16 tokens).
+    dense_skinny_max_tokens: int = 8
+
+    # Grouped expert products: up to this many rows per expert on average (tokens * top_k / experts) the
+    # decode-sized mma.sync kernel reads every used expert once; above it the tcgen05 kernel's row tiles
+    # pay.  Checked at 60 experts with top-4 routing by decoding at batch 16, 32, 64 and 128 (1 to 8.5 rows
+    # per expert): throughput rises steadily, no cliff where the kernels change.
+    expert_skinny_rows_per_expert: int = 8
+
+    # The shared expert runs on a second stream beside the routed experts: in decode-sized steps every
+    # kernel is short, and in prefill its library products are bound by the tensor cores while the grouped
+    # products of the routed experts are bound by memory (7 % off a 2,048-token prefill when introduced).
+    shared_expert_overlap: bool = True
+    # Steps above this size run the shared expert as library products whose blocks fill an SM; on a stream
+    # of higher priority they take their SMs ahead of the routing's small kernels, which slip into what is
+    # left, whatever order the two streams' first kernels reach the device in.
+    shared_expert_priority_stream_min_tokens: int = 128
+    # In the smallest steps the routing is a chain of short dependent loads that a concurrent weight
+    # stream slows down, so there the shared expert is forked after the routing, not before it.
+    shared_expert_fork_after_routing_max_tokens: int = 8
+
+    # Split-KV decode attention: keys per split by the number of requests in the step, as (up to this
+    # many requests, keys per split) pairs, then the kernel's default of 512.  One or two requests alone
+    # cannot fill 148 SMs with splits of 512 keys; splits of 256 for every batch size gained 4 % at batch 1
+    # and lost 6 % at batch 8, hence the steps.  Only the bfloat16 path uses it: the float32 path keeps one
+    # split size, so that a request's logits do not depend on its batch.
+    decode_split_by_requests: Tuple[Tuple[int, int], ...] = ((2, 128), (4, 256))
+
+    def decode_split(self, num_requests: int, default: int) -> int:
+        for limit, split in self.decode_split_by_requests:
+            if num_requests <= limit:
+                return split
+        return default
+
+
+TUNING = Tuning()

@@ -120,8 +120,8 @@ def test_schedule_plans_caches():
     twice = dataclasses.replace(spec, schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
                                                 ScheduleEntry(1, cache_from=1)))
     m2 = Model(twice)
-    assert [b.layer_slot for b in m2.bindings] == [0, 1, 2, 1]
-    assert [b.writes for b in m2.bindings] == [True, True, True, False]
+    assert [b["mixer"].layer_slot for b in m2.bindings] == [0, 1, 2, 1]
+    assert [b["mixer"].writes for b in m2.bindings] == [True, True, True, False]
     assert m2.kv_groups[0].num_layers == 3
 
 

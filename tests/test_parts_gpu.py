@@ -33,7 +33,7 @@ def whole_sequence_ctx(S, nkv, d, page_size, act, n_layers=1, prefix_len=0):
     slot = torch.tensor([order[p // page_size] * page_size + p % page_size for p in range(prefix_len, S)],
                         dtype=torch.int32, device=DEV)
     k = torch.zeros(n_layers, pages, nkv, page_size, d, dtype=act, device=DEV)
-    view = KVGroupView(table, slot, page_size, k, torch.zeros_like(k))
+    view = KVGroupView(table, slot, page_size, {"k": k, "v": torch.zeros_like(k)})
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     return StepContext(num_tokens=n, num_requests=1, max_q_len=n, max_kv_len=S, all_decode=(n == 1),
                        token_ids=i32([0] * n), positions=pos, q_start=i32([0, n]), kv_len=i32([S]),
@@ -104,7 +104,7 @@ def _with_cache(k, v, ps, lo, hi):
     n = hi - lo
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     slot = i32([order[p // ps] * ps + p % ps for p in range(lo, hi)])
-    view = KVGroupView(table, slot, ps, k, v)
+    view = KVGroupView(table, slot, ps, {"k": k, "v": v})
     return StepContext(num_tokens=n, num_requests=1, max_q_len=n, max_kv_len=hi, all_decode=(n == 1),
                        token_ids=i32([0] * n), positions=i32(list(range(lo, hi))), q_start=i32([0, n]),
                        kv_len=i32([hi]), req_of_token=i32([0] * n), state_slot=i32([0]),

@@ -144,8 +144,8 @@ def test_toy_routing_feed_forward_and_toy_position_encoding(dtype):
     toy_pos = PartSpec("toy_scaled_partial_rotary", {"rot_dim": d // 2, "theta": 500.0, "scale": 4.0})
     mixer0 = PartSpec(base.layers[0].mixer.kind, dict(base.layers[0].mixer.params, position=toy_pos))
     toy_ffn = PartSpec("toy_sigmoid_top1", {"hidden_size": cfg["hidden_size"], "intermediate_size": 40, "num_experts": 5})
-    spec = dataclasses.replace(base, layers=(dataclasses.replace(base.layers[0], mixer=mixer0),
-                                             dataclasses.replace(base.layers[1], feed_forward=toy_ffn)))
+    spec = dataclasses.replace(base, layers=(base.layers[0].with_part("mixer", mixer0),
+                                             base.layers[1].with_part("feed_forward", toy_ffn)))
     runner, weights = build(spec, dtype)
     assert "model.layers.1.mlp.experts.4.w2.weight" in weights and "model.layers.1.mlp.gate.weight" not in weights
     g = torch.Generator().manual_seed(3)

@@ -130,12 +130,12 @@ def test_toy_mixer_with_state_of_its_own(dtype):
     _register_toy()
     cfg = tiny.CONFIG_A
     base = build_model_spec(cfg)
-    toy_layer = dataclasses.replace(base.layers[1], mixer=PartSpec(
+    toy_layer = base.layers[1].with_part("mixer", PartSpec(
         "toy_decaying_sum", {"hidden_size": cfg["hidden_size"], "state_size": 24, "decay": 0.9}))
     spec = dataclasses.replace(base, layers=(base.layers[0], toy_layer))
     runner, weights = build(spec, dtype)
     assert len(runner.state_tensors) == 1 and runner.state_tensors[0].shape == (4, 24)
-    assert [b.kind for b in runner.model.bindings] == ["kv", "state"]
+    assert [b["mixer"].kind for b in runner.model.bindings] == ["kv", "state"]
     g = torch.Generator().manual_seed(0)
     reqs = {f"t{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
             for i, n in enumerate([30, 7, 45, 18, 26, 11])}
@@ -158,7 +158,7 @@ def test_layer_named_twice_and_shared_cache():
     base = build_model_spec(cfg)
     # layer 2: attention without k/v projections of its own, reading the cache of schedule entry 1
     shared_mixer = PartSpec("gqa_attention", dict(base.layers[1].mixer.params, shares_cache=True))
-    layer2 = dataclasses.replace(base.layers[1], name="model.layers.2", mixer=shared_mixer)
+    layer2 = base.layers[1].renamed("model.layers.2").with_part("mixer", shared_mixer)
     spec = dataclasses.replace(base, layers=base.layers + (layer2,),
                                schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
                                          ScheduleEntry(2, cache_from=1)))

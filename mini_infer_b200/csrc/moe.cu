@@ -728,7 +728,9 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
         set_last_error("router: %d experts exceed the grid limit", E);
         return kBadShape;
     }
-    if (T <= 4 * RT_TOK) {
+    // Float activations (the true 32-bit path) take this form at every size: it adds a token's products in
+    // one fixed order, so that a token's logits do not depend on how many tokens share its step.
+    if (T <= 4 * RT_TOK || (adtype == kF32 && token_tiles <= 65535)) {
         const dim3 sgrid(ncols, token_tiles);
         MI_DISPATCH_2(adtype, AT, wdtype, WT,
             moe_router_logits_small_kernel<AT, WT><<<sgrid, 256, 0, stream>>>(

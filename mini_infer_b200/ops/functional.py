@@ -509,6 +509,19 @@ def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch
     return out
 
 
+def dense_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` in true float32 (``x [T, K]``, ``w [N, K]``): every output element is one chain of
+    fused multiply-adds over ``k`` in ascending order, so a row's result does not depend on how many rows
+    there are.  The dense product of the float32 path."""
+    _chk(x, "dense_f32 x", F32)
+    T, K = x.shape
+    _chk(w, "dense_f32 w", F32, (None, K))
+    N = w.shape[0]
+    out = torch.empty(T, N, dtype=F32, device=x.device)
+    check(library().mi_dense_f32(_ptr(x), _ptr(w), _ptr(out), T, N, K, _stream()), "dense_f32")
+    return out
+
+
 def grouped_gemm_skinny_supported(kd: int) -> bool:
     return bool(library().mi_grouped_gemm_skinny_supported(int(kd)))
 

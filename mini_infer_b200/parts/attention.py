@@ -111,12 +111,14 @@ class GQAttention(Mixer):
             q = F.qkv_post(qkv, self.b_qkv, ctx.positions, self.inv_freq, self.rot_dim,
                            view.slot_mapping if nkv_in else None, kc if nkv_in else None, vc if nkv_in else None,
                            self.nh, nkv_in, self.d, view.page_size, self.rt.act)
-        if ctx.all_decode and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d):
-            # one or two requests alone cannot fill the device with splits of 512 keys (bfloat16 path only:
-            # the float32 path keeps one split size, so that a request's logits do not depend on its batch)
-            split = F.decode_split_size()
-            if self.rt.act == torch.bfloat16:
-                split = TUNING.decode_split(ctx.num_requests, split)
+        # The float32 path takes one attention kernel for every step (key tiles at absolute positions: a
+        # query's sums run in the same order however its step was cut or batched); the bfloat16 path picks
+        # the fastest kernel for the step's shape.
+        if self.rt.act == torch.float32:
+            a = F.attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
+        elif ctx.all_decode and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d):
+            # one or two requests alone cannot fill the device with splits of 512 keys
+            split = TUNING.decode_split(ctx.num_requests, F.decode_split_size())
             splits = -(-ctx.max_kv_len // split)
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
                                    ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window,

@@ -361,11 +361,17 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dty
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """``x @ w.T`` through the library product the reference also uses for every dense
-    projection (cuBLAS, src/layers/attention.cpp:45-55, src/layers/mlp.cpp:120-130),
-    accumulating in float32; ``w`` is ``[out, in]`` as stored in checkpoints."""
+    """``x @ w.T``; ``w`` is ``[out, in]`` as stored in checkpoints.
+
+    bfloat16 path: the library product the reference also uses for every dense projection (cuBLAS,
+    src/layers/attention.cpp:45-55, src/layers/mlp.cpp:120-130), accumulating in float32, or the engine's
+    own decode kernel for the smallest steps.  float32 path (both operands float32): the engine's own
+    CUDA-core kernel, which adds in one fixed order whatever the number of rows, so that this path gives
+    the same bits however the work is cut and batched."""
+    from ..ops import functional as F
+    if x.is_cuda and x.dtype == torch.float32 and w.dtype == torch.float32 and out_dtype == torch.float32:
+        return F.dense_f32(x, w)
     if out_dtype == torch.float32 and x.is_cuda and x.shape[0] <= TUNING.dense_skinny_max_tokens:
-        from ..ops import functional as F
         if F.dense_skinny_takes(x, w):
             return F.dense_skinny(x, w)
     if x.dtype == out_dtype:

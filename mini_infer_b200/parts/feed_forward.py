@@ -209,7 +209,8 @@ class SparseMoE(FeedForward):
         else:
             if overlap:
                 side, shared = self._fork_shared_expert(x)
-            if T <= self._route_small_max:
+            # (the float32 path routes every step with the same kernel: same bits however the work is cut)
+            if T <= self._route_small_max and self.rt.act == torch.bfloat16:
                 idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
                     want_probs=self.keep_routing)

@@ -43,8 +43,8 @@ class Tuning:
     # Split-KV decode attention: keys per split by the number of requests in the step, as (up to this
     # many requests, keys per split) pairs, then the kernel's default of 512.  One or two requests alone
     # cannot fill 148 SMs with splits of 512 keys; splits of 256 for every batch size gained 4 % at batch 1
-    # and lost 6 % at batch 8, hence the steps.  Only the bfloat16 path uses it: the float32 path keeps one
-    # split size, so that a request's logits do not depend on its batch.
+    # and lost 6 % at batch 8, hence the steps.  (bfloat16 path only: the float32 path runs one attention
+    # kernel for every step, so that a request's logits do not depend on its batch.)
     decode_split_by_requests: Tuple[Tuple[int, int], ...] = ((2, 128), (4, 256))
 
     def decode_split(self, num_requests: int, default: int) -> int:

@@ -110,6 +110,19 @@ def test_mixed_with_pages_used_again(engine, checkpoint):
     assert runner.graph_replays == sum(1 for st in steps if all(len(t) == 1 for _, t, _ in st["entries"]))
 
 
+def test_float32_cuttings_agree_bit_for_bit(engine, checkpoint):
+    """At real sizes too, the float32 path gives the same bits whole, in portions and mixed with others."""
+    if engine["dtype"] != "float32":
+        pytest.skip("bit-for-bit agreement is the float32 path's property")
+    from engine_harness import run_trace
+    reqs = checkpoint["reqs"]
+    a = run_trace(_runner(engine, 96), traces.whole(reqs))
+    b = run_trace(_runner(engine, 96), traces.portions(reqs, (7, 2, 129, 3, 64, 250, 2, 33)))
+    c = run_trace(_runner(engine, 96), traces.mixed(reqs, max_live=3, seed=2, decode_tail=20, max_portion=160))
+    for key in a:
+        assert torch.equal(a[key], b[key]) and torch.equal(a[key], c[key]), key
+
+
 def test_scheduler_workload(engine, checkpoint):
     """Eight requests with prompts of 1 to 1,500 tokens, prefilled in portions of 512 beside decoding
     requests, 64 greedy tokens each, through ``LLM.generate`` as serving runs it; every row of logits that

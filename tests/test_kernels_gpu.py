@@ -161,6 +161,20 @@ def test_combine_add_rmsnorm_is_the_two_kernels(adt, wdt, T, K, H, indexed, with
     assert torch.equal(got, ref) and torch.equal(h_got, h0)
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 7, 5), (70, 130, 96), (333, 515, 200), (64, 64, 2048), (5, 151936, 72)])
+def test_dense_float32_product_and_its_fixed_order(T, N, K):
+    """The float32 path's dense product against a float64 product, and the property it exists for: a
+    row's result is the same bits whether it is computed alone, among others, or at another place."""
+    x, w = rnd(T, K, seed=T), rnd(N, K, seed=N, scale=0.1)
+    out = F().dense_f32(x, w)
+    ref = (x.double() @ w.double().T).float()
+    close(out, ref, 2e-6, "dense_f32")
+    alone = F().dense_f32(x[T - 1:].contiguous(), w)
+    assert torch.equal(alone[0], out[T - 1])
+    shifted = F().dense_f32(torch.cat([rnd(37, K, seed=1), x]), w)
+    assert torch.equal(shifted[37:], out)
+
+
 # --------------------------------------------------------------------------- #
 # attention
 # --------------------------------------------------------------------------- #

@@ -28,7 +28,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE configs[2]: Qwen1.5-MoE-A2.7B layer sizes
+# the headline configuration: Qwen1.5-MoE-A2.7B layer sizes
 A27B = {
     "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
     "vocab_size": 151936, "hidden_size": 2048, "intermediate_size": 5632, "num_hidden_layers": 24,

@@ -95,12 +95,24 @@ def run_generate(argv: List[str]) -> int:
               max_tokens_per_step=args.max_tokens_per_step, prefill_chunk=args.prefill_chunk)
     sp = SamplingParams(greedy=args.greedy, temperature=args.temperature, top_p=args.top_p, seed=args.seed,
                         max_new_tokens=args.max_new_tokens, stop_token_ids=tuple(stop_ids))
+    # The text appears between the two marker lines as it is generated (a reader of the pipe can show it
+    # line by line, as the reference's SDK does): each token's text is printed when its step has ended.
     t0 = time.perf_counter()
-    out = llm.generate([prompt_ids], sp)[0]
+    print("\n--- generated ---", flush=True)
+    gen: List[int] = []
+    shown = ""
+    for _, token in llm.generate_iter([prompt_ids], sp):
+        gen.append(token)
+        text = tok.decode(gen) if tok is not None else " ".join(str(t) for t in gen)
+        if tok is not None and text.endswith("\ufffd"):
+            continue                                   # half of a character: wait for the rest
+        sys.stdout.write(text[len(shown):])
+        sys.stdout.flush()
+        shown = text
+    out = llm.last_outputs[0]
     secs = time.perf_counter() - t0
-    gen = out.token_ids
     text = tok.decode(gen) if tok is not None else " ".join(str(t) for t in gen)
-    print(f"\n--- generated ---\n{text}\n--- end ---")
+    print(f"{text[len(shown):]}\n--- end ---")
     print(f"[mini-infer] {len(gen)} tokens in {secs:.2f}s ({len(gen) / max(secs, 1e-9):.2f} tok/s)")
     if args.json:
         print(json.dumps({"prompt_tokens": len(prompt_ids), "token_ids": gen, "finish_reason": out.finish_reason,

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence, Union
+from typing import Dict, Hashable, Iterator, List, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -156,9 +156,7 @@ class LLM:
         self.last_history: List[IterationStats] = []
         self._calls = 0
 
-    def generate(self, prompts: Sequence[Sequence[int]],
-                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[GenerationOutput]:
-        """Token ids in, token ids out; request ``i`` samples from random stream ``i``."""
+    def _submit(self, prompts, params):
         if params is None:
             params = SamplingParams()
         plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
@@ -172,14 +170,48 @@ class LLM:
         sched = Scheduler(self.executor, self.sched_cfg)
         self._calls += 1
         reqs = [Request((self._calls, i), list(p), sp, stream=i) for i, (p, sp) in enumerate(zip(prompts, plist))]
-        t0 = time.perf_counter()
         for r in reqs:
             sched.submit(r)
+        return sched, reqs
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[GenerationOutput]:
+        """Token ids in, token ids out; request ``i`` samples from random stream ``i``."""
+        t0 = time.perf_counter()
+        sched, reqs = self._submit(prompts, params)
         sched.run_until_done()
         self.last_history = sched.history
-        out = []
-        for r in reqs:
-            out.append(GenerationOutput(r.prompt, list(r.generated), r.finish_reason, r.metrics.ttft,
-                                        (r.metrics.finished or time.perf_counter()) - t0,
-                                        r.metrics.preemptions))
-        return out
+        return [self._output(r, t0) for r in reqs]
+
+    @staticmethod
+    def _output(r: Request, t0: float) -> GenerationOutput:
+        return GenerationOutput(r.prompt, list(r.generated), r.finish_reason, r.metrics.ttft,
+                                (r.metrics.finished or time.perf_counter()) - t0, r.metrics.preemptions)
+
+    def generate_iter(self, prompts: Sequence[Sequence[int]],
+                      params: Union[SamplingParams, Sequence[SamplingParams], None] = None
+                      ) -> Iterator[Tuple[int, int]]:
+        """As :meth:`generate`, but yields ``(request index, token id)`` as soon as the scheduler's step
+        that sampled the token has ended (the reference streams the lines its binary prints,
+        sdk/mini_infer_sdk/backends/local.py:218-254).  The outputs are in ``self.last_outputs`` when the
+        iterator is exhausted; a consumer that stops early ends the requests and frees their pages."""
+        t0 = time.perf_counter()
+        sched, reqs = self._submit(prompts, params)
+        seen = [0] * len(reqs)
+        try:
+            while not sched.done():
+                before = (len(sched.running), len(sched.waiting), len(sched.finished))
+                st = sched.step()
+                for i, r in enumerate(reqs):
+                    while seen[i] < len(r.generated):
+                        yield i, r.generated[seen[i]]
+                        seen[i] += 1
+                if st.num_tokens == 0 and st.preempted == 0 and \
+                        (len(sched.running), len(sched.waiting), len(sched.finished)) == before:
+                    raise RuntimeError("Scheduler: no progress is possible (no tokens scheduled, nothing finished)")
+        finally:
+            for r in list(sched.running):
+                sched._finish(r, "cancelled")
+            sched.waiting.clear()
+            self.last_history = sched.history
+            self.last_outputs = [self._output(r, t0) for r in reqs]

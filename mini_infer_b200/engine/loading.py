@@ -31,7 +31,12 @@ def _runtime(dtype: str, device) -> Runtime:
 
 
 def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> Tuple[Model, Runtime, Dict[str, Any]]:
-    """Read ``config.json``, pick the architecture from the registry, load ``model.safetensors``."""
+    """Read ``config.json``, pick the architecture from the registry, load ``model.safetensors``.
+
+    Side effect on the whole process: PyTorch's matrix-product switches are set so that library products
+    accumulate in true float32 (no TF32, no reduced-precision reductions for bfloat16 or float16 inputs;
+    :func:`configure_matmul_exactness`).  Both precision paths need them, and everything else that runs
+    PyTorch products in the same process afterwards inherits them."""
     cj = read_config_json(folder)
     spec = build_model_spec(cj)
     rt = _runtime(dtype, device)

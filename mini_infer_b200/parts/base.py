@@ -103,7 +103,9 @@ class Runtime:
 
 
 def configure_matmul_exactness() -> None:
-    """No TF32, no reduced-precision split-k reductions: library products accumulate in float32."""
+    """No TF32, no reduced-precision split-k reductions: library products accumulate in float32.  These are
+    process-wide PyTorch switches: whatever else multiplies matrices in this process afterwards runs under
+    them as well."""
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False

@@ -185,6 +185,42 @@ def test_sdk_entry_point(folders):
         MiniInfer(endpoint="http://localhost:8000")
 
 
+def test_sdk_streams_tokens_as_the_scheduler_produces_them(folders):
+    """``stream`` yields after every scheduler step (the scheduler has run exactly as many decode steps as
+    tokens have been yielded), not once generation is over; stopping early ends the request and frees it."""
+    from mini_infer_sdk import InferenceConfig, MiniInfer
+    folder, cfg, w = folders["A"]
+    toks, gen = clear_prompt(cfg, w, 12, 900, 6)
+    eng = MiniInfer(model_path=folder, config=InferenceConfig(max_new_tokens=6, max_seq_len=64, dtype="float32",
+                                                              max_running=2))
+    seen, replays = [], []
+    for piece in eng.stream(toks):
+        seen.append(int(piece))
+        replays.append(eng.llm.runner.graph_replays)
+    assert seen == gen
+    assert replays == sorted(replays) and replays[0] < replays[-1]      # steps ran between the yields
+    it = eng.stream(toks)
+    assert int(next(it)) == gen[0]
+    it.close()                                                            # the consumer walks away
+    assert eng.llm.runner.cache.used_pages() == [0] and eng.llm.last_outputs[0].finish_reason == "cancelled"
+    assert eng.generate(toks).generated_ids == gen                        # and the engine is as before
+
+
+def test_sdk_subprocess_backend(folders):
+    """``binary=``: every call runs the command-line program and reads its printed contract, as the
+    reference's local backend does."""
+    from mini_infer_sdk import InferenceConfig, MiniInfer
+    folder, cfg, w = folders["A"]
+    toks, gen = clear_prompt(cfg, w, 12, 900, 6)
+    eng = MiniInfer(model_path=folder, binary=os.path.join(ROOT, "bin", "mini_infer"),
+                    config=InferenceConfig(max_new_tokens=6, max_seq_len=64, dtype="float32"))
+    assert eng.llm is None and "subprocess" in repr(eng)
+    r = eng.generate(toks)
+    assert r.generated_ids == gen and r.prompt_tokens == 12 and r.finish_reason == "length"
+    assert r.text == " ".join(str(t) for t in gen) and r.tokens_per_sec > 0 and r.wall_sec >= r.elapsed_sec
+    assert [int(t) for t in "".join(eng.stream(toks)).split()] == gen
+
+
 def test_command_line_contract(folders):
     folder, cfg, w = folders["A"]
     toks, gen = clear_prompt(cfg, w, 9, 333, 5)

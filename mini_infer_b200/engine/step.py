@@ -293,6 +293,9 @@ class ModelRunner:
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
         if not self.cuda_graphs or self.model.layer_observer is not None:
             return False
+        from ..ops import functional as F
+        if F.DEBUG_BOUNDS:           # the debug checks read indices back on the host: not inside a capture
+            return False
         return not any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries)
 
     def _decode_with_graph(self, ctx: StepContext, logit_rows: torch.Tensor) -> torch.Tensor:

@@ -54,6 +54,72 @@ def _chk(t: Optional[torch.Tensor], what: str, dtype=None, shape=None) -> None:
             raise ValueError(f"{what}: expected shape {list(shape)}, got {list(actual)}")
 
 
+# --------------------------------------------------------------------------- #
+# Debug mode: with MINI_INFER_DEBUG_BOUNDS=1 in the environment every index that a kernel will follow
+# (token ids, row lists, cache slots, block tables, lengths, expert choices and offsets, permutations) is
+# checked on the host before the launch, and a bad one raises a KernelError that names the tensor, the
+# first bad place and its value, instead of becoming an access outside a buffer.  It synchronises the
+# device at every op, so it is for chasing a fault, not for serving.  (The reference checks none of these;
+# its kernels return silently on a size they do not take, src/kernels/paged_attn_kernel.cu:313-315.)
+# --------------------------------------------------------------------------- #
+import os as _os
+
+DEBUG_BOUNDS = _os.environ.get("MINI_INFER_DEBUG_BOUNDS", "0") not in ("", "0")
+debug_checks_run = 0
+
+
+def _bad(what: str, msg: str):
+    from .library import KernelError
+    raise KernelError(f"{what}: {msg} (found by MINI_INFER_DEBUG_BOUNDS before the launch)")
+
+
+def _dbg_range(t: Optional[torch.Tensor], lo: int, hi: int, what: str) -> None:
+    """Every element of ``t`` lies in ``[lo, hi)``."""
+    global debug_checks_run
+    if t is None or t.numel() == 0:
+        return
+    debug_checks_run += 1
+    flat = t.reshape(-1)
+    bad = ((flat < lo) | (flat >= hi)).nonzero()
+    if bad.numel():
+        i = int(bad[0, 0])
+        _bad(what, f"element {i} is {int(flat[i])}, outside [{lo}, {hi})")
+
+
+def _dbg_offsets(offsets: torch.Tensor, n_rows: int, what: str) -> None:
+    """Expert offsets rise from 0 to the number of rows."""
+    global debug_checks_run
+    debug_checks_run += 1
+    o = offsets.cpu().tolist()
+    if o[0] != 0 or o[-1] != n_rows or any(b < a for a, b in zip(o, o[1:])):
+        _bad(what, f"offsets {o[:8]}... do not rise from 0 to {n_rows}")
+
+
+def _dbg_batch(what: str, q_start: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor, T: int,
+               num_pages: int, page_size: int, window: int, max_q_len: Optional[int] = None) -> None:
+    """The layout of a ragged batch over a paged cache: ``q_start`` rises from 0 to T, every request's
+    length covers its new tokens and fits its table, and every page that a query of this step reads
+    (all of them, or those its window reaches) is a real page."""
+    global debug_checks_run
+    debug_checks_run += 1
+    qs, kv, bt = q_start.cpu().tolist(), kv_len.cpu().tolist(), block_table.cpu()
+    B, max_pages = bt.shape
+    if qs[0] != 0 or qs[-1] != T or any(b <= a for a, b in zip(qs, qs[1:])):
+        _bad(what, f"q_start {qs} does not rise from 0 to {T}")
+    for b in range(B):
+        n_q, n = qs[b + 1] - qs[b], kv[b]
+        if max_q_len is not None and n_q > max_q_len:
+            _bad(what, f"request {b} brings {n_q} tokens, max_q_len says {max_q_len}")
+        if n < n_q or n > max_pages * page_size:
+            _bad(what, f"request {b}: kv_len {n} with {n_q} new tokens and a table of {max_pages} pages of {page_size}")
+        first = 0 if window <= 0 else max(0, n - n_q - window + 1)
+        row = bt[b]
+        for i in range(first // page_size, -(-n // page_size)):
+            p = int(row[i])
+            if not 0 <= p < num_pages:
+                _bad(what, f"request {b} reads page entry {i} = {p}, the cache has {num_pages} pages")
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
@@ -75,6 +141,8 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
     if out is None:
         out = torch.empty(T, H, dtype=F32, device=table.device)
     _chk(out, "embed_gather out", F32, (T, H))
+    if DEBUG_BOUNDS:
+        _dbg_range(ids, 0, V, "embed_gather ids")
     check(library().mi_embed_gather(_ptr(ids), _ptr(table), _code(table, "embed_gather table"), _ptr(out),
                                     T, H, V, _stream()), "embed_gather")
     return out
@@ -97,6 +165,8 @@ def add_rmsnorm(hidden: torch.Tensor, delta: Optional[torch.Tensor], weight: tor
     if out is None:
         out = torch.empty(n, H, dtype=out_dtype, device=hidden.device)
     _chk(out, "add_rmsnorm out", out_dtype, (n, H))
+    if DEBUG_BOUNDS:
+        _dbg_range(rows, 0, T, "add_rmsnorm rows")
     check(library().mi_add_rmsnorm(_ptr(hidden), _ptr(delta), _ptr(rows), _ptr(weight),
                                    _code(weight, "add_rmsnorm weight"), _ptr(out), _code(out, "add_rmsnorm out"),
                                    n, H, float(eps), _stream()), "add_rmsnorm")
@@ -132,6 +202,8 @@ def qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.T
         q_out = torch.empty(T, nh, d, dtype=out_dtype, device=qkv.device)
     _chk(q_out, "qkv_post q_out", out_dtype, (T, nh, d))
     wcode = _code(bias, "qkv_post bias") if bias is not None else 0
+    if DEBUG_BOUNDS and nkv > 0:
+        _dbg_range(slot_mapping, -1, k_cache.shape[0] * page_size, "qkv_post slot_mapping")     # -1: not cached
     check(library().mi_qkv_post(_ptr(qkv), _ptr(bias), wcode, _ptr(positions), _ptr(inv_freq),
                                 _ptr(slot_mapping), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
                                 _code(q_out, "qkv_post q_out"), T, nh, nkv, d, rot_dim, page_size, _stream()),
@@ -170,6 +242,8 @@ def moe_combine(y: torch.Tensor, inv_perm: Optional[torch.Tensor], weights: torc
     if out is None:
         out = torch.empty(T, H, dtype=F32, device=y.device)
     _chk(out, "moe_combine out", F32, (T, H))
+    if DEBUG_BOUNDS:
+        _dbg_range(inv_perm, 0, T * K, "moe_combine inv_perm")
     check(library().mi_moe_combine(_ptr(y), _ptr(inv_perm), _ptr(weights), _ptr(shared), _ptr(gate), _ptr(out),
                                    T, H, K, _stream()), "moe_combine")
     return out
@@ -198,6 +272,9 @@ def combine_add_rmsnorm(hidden: torch.Tensor, y: torch.Tensor, inv_perm: Optiona
     _chk(rows, "combine_add_rmsnorm rows", I32)
     n = T if rows is None else rows.numel()
     out = torch.empty(n, H, dtype=out_dtype, device=hidden.device)
+    if DEBUG_BOUNDS:
+        _dbg_range(inv_perm, 0, T * K, "combine_add_rmsnorm inv_perm")
+        _dbg_range(rows, 0, T, "combine_add_rmsnorm rows")
     check(library().mi_combine_add_rmsnorm(_ptr(hidden), _ptr(y), _ptr(inv_perm), _ptr(weights), _ptr(shared),
                                            _ptr(gate), K, _ptr(rows), _ptr(norm_weight),
                                            _code(norm_weight, "combine_add_rmsnorm weight"), _ptr(out),
@@ -226,6 +303,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, blo
     _chk(out, "attention out", q.dtype, (T, nh, d))
     if scale is None:
         scale = 1.0 / math.sqrt(d)
+    if DEBUG_BOUNDS:
+        _dbg_batch("attention", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window), int(max_q_len))
     check(library().mi_attn_tiled(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention q"),
                                   _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len),
                                   nh, nkv, d, page_size, max_pages, int(window), float(scale), _stream()),
@@ -257,6 +336,9 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     _chk(out, "prefill_attention out", BF16, (T, nh, d))
     if scale is None:
         scale = 1.0 / math.sqrt(d)
+    if DEBUG_BOUNDS:
+        _dbg_batch("prefill_attention", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window),
+                   int(max_q_len))
     check(library().mi_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(q_start),
                                     _ptr(kv_len), _ptr(out), B, int(max_q_len), nh, nkv, d, page_size, max_pages,
                                     int(window), float(scale), _stream()), "prefill_attention")
@@ -293,6 +375,9 @@ def prefill_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     dev = q.device
     if dev not in _tc_status:
         _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
+    if DEBUG_BOUNDS:
+        _dbg_batch("prefill_attention_tc", q_start, kv_len, block_table, T, num_pages, page_size, int(window),
+                   int(max_q_len))
     check(library().mi_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(q_start),
                                        _ptr(kv_len), _ptr(out), _ptr(_tc_status[dev]), T, B, int(max_q_len), nh, nkv,
                                        d, page_size, num_pages, max_pages, int(window), float(scale), _stream()),
@@ -348,6 +433,11 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         scale = 1.0 / math.sqrt(d)
     if split is None:
         split = decode_split_size()
+    if DEBUG_BOUNDS:
+        _dbg_batch("decode_attention", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window), 1)
+        longest = int(kv_len.max())
+        if max_splits * int(split) < longest - int(split) // 4:
+            _bad("decode_attention", f"{max_splits} splits of {split} keys cannot hold the longest request ({longest})")
     check(library().mi_attn_decode_split(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "decode_attention q"),
                                          _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), _ptr(part_o),
                                          _ptr(part_ml), B, nh, nkv, d, page_size, max_pages, int(max_splits),
@@ -392,6 +482,8 @@ def moe_permute(topk_idx: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor,
     sorted_token = torch.empty(T * K, dtype=I32, device=dev)
     inv_perm = torch.empty(T * K, dtype=I32, device=dev)
     counts = torch.empty(num_experts, dtype=I32, device=dev)
+    if DEBUG_BOUNDS:
+        _dbg_range(topk_idx, 0, int(num_experts), "moe_permute expert indices")
     check(library().mi_moe_permute(_ptr(topk_idx), _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), _ptr(counts), T,
                                    int(num_experts), K, _stream()), "moe_permute")
     return offsets, sorted_token, inv_perm
@@ -502,6 +594,11 @@ def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch
     _chk(gather, "grouped_gemm gather", I32)
     _chk(offsets, "grouped_gemm offsets", I32, (E + 1,))
     out = torch.empty(n_rows, nout, dtype=out_dtype, device=a.device)
+    if DEBUG_BOUNDS:
+        _dbg_offsets(offsets, int(n_rows), "grouped_gemm_plain")
+        _dbg_range(gather, 0, a.shape[0], "grouped_gemm_plain gather")
+        if gather is None and a.shape[0] < n_rows:
+            _bad("grouped_gemm_plain", f"{n_rows} rows wanted, the input has {a.shape[0]}")
     check(library().mi_grouped_gemm_plain(_ptr(a), _code(a, "grouped_gemm a"), _ptr(gather), _ptr(w),
                                           _code(w, "grouped_gemm w"), _ptr(offsets), _ptr(out),
                                           _code(out, "grouped_gemm out"), int(n_rows), E, nout, Kd,
@@ -541,6 +638,11 @@ def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torc
     _chk(gather, "grouped_gemm_skinny gather", I32)
     _chk(offsets, "grouped_gemm_skinny offsets", I32, (E + 1,))
     out = torch.empty(n_rows, nout, dtype=BF16 if swiglu_pair else F32, device=a.device)
+    if DEBUG_BOUNDS:
+        _dbg_offsets(offsets, int(n_rows), "grouped_gemm_skinny")
+        _dbg_range(gather, 0, a.shape[0], "grouped_gemm_skinny gather")
+        if gather is None and a.shape[0] < n_rows:
+            _bad("grouped_gemm_skinny", f"{n_rows} rows wanted, the input has {a.shape[0]}")
     check(library().mi_grouped_gemm_skinny(_ptr(a), _ptr(gather), _ptr(w), _ptr(offsets), _ptr(out), E, nout, Kd,
                                            1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny")
     return out
@@ -604,6 +706,8 @@ def qkv_skinny(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor
     _chk(k_cache, "qkv_skinny k_cache", BF16, (None, nkv, page_size, d))
     _chk(v_cache, "qkv_skinny v_cache", BF16, tuple(k_cache.shape))
     q = torch.empty(T, nh, d, dtype=BF16, device=x.device)
+    if DEBUG_BOUNDS:
+        _dbg_range(slot_mapping, -1, k_cache.shape[0] * page_size, "qkv_skinny slot_mapping")   # -1: not cached
     check(library().mi_qkv_skinny(_ptr(x), _ptr(w_qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq),
                                   _ptr(slot_mapping), _ptr(q), _ptr(k_cache), _ptr(v_cache), T, Kd, nh, nkv, d,
                                   page_size, _stream()), "qkv_skinny")
@@ -631,6 +735,8 @@ def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.
     E, wrows, _ = w.shape
     nout = wrows // 2 if swiglu_pair else wrows
     out = torch.empty(T * K, nout, dtype=BF16 if swiglu_pair else F32, device=a.device)
+    if DEBUG_BOUNDS:
+        _dbg_range(topk_idx, 0, E, "grouped_gemm_skinny_pairs expert indices")
     check(library().mi_grouped_gemm_skinny_pairs(_ptr(a), _ptr(topk_idx), _ptr(w), _ptr(out), T, K, E, nout, Kd,
                                                  1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny_pairs")
     return out
@@ -647,6 +753,8 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     _chk(x, "gather_rows x", BF16)
     _chk(rows, "gather_rows rows", I32)
     out = torch.empty(rows.numel(), x.shape[1], dtype=BF16, device=x.device)
+    if DEBUG_BOUNDS:
+        _dbg_range(rows, 0, x.shape[0], "gather_rows rows")
     check(library().mi_gather_rows_bf16(_ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1], _stream()),
           "gather_rows")
     return out
@@ -680,6 +788,8 @@ def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tens
     if dev not in _tc_status:
         _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
     out = torch.empty(n_rows, nout, dtype=BF16 if swiglu_pair else F32, device=dev)
+    if DEBUG_BOUNDS:
+        _dbg_offsets(offsets, int(n_rows), "grouped_gemm_tc")
     check(library().mi_grouped_gemm_tc_form(_ptr(a_sorted), _ptr(w), _ptr(offsets), _ptr(out), _ptr(_tc_status[dev]),
                                             n_rows, E, nout, Kd, 1 if swiglu_pair else 0,
                                             -1 if form is None else int(form), _stream()), "grouped_gemm_tc")

@@ -204,16 +204,20 @@ class MiniInfer:
             return
         gen: List[int] = []
         shown = ""
-        for _, token in self.llm.generate_iter([ids], self._params(cfg, stop)):
-            gen.append(token)
-            if self.tokenizer is None:
-                yield str(token)
-                continue
-            text = self.tokenizer.decode(gen)
-            if text.endswith("\ufffd"):
-                continue                               # half of a character: wait for the rest
-            yield text[len(shown):]
-            shown = text
+        tokens = self.llm.generate_iter([ids], self._params(cfg, stop))
+        try:
+            for _, token in tokens:
+                gen.append(token)
+                if self.tokenizer is None:
+                    yield str(token)
+                    continue
+                text = self.tokenizer.decode(gen)
+                if text.endswith("\ufffd"):
+                    continue                           # half of a character: wait for the rest
+                yield text[len(shown):]
+                shown = text
+        finally:
+            tokens.close()                             # a consumer that walks away ends the request at once
 
     # -- subprocess backend --------------------------------------------------- #
     def _command(self, ids: Sequence[int], cfg: InferenceConfig) -> List[str]:

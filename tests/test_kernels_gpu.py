@@ -878,3 +878,43 @@ def test_sampling_frequencies_follow_the_distribution():
     assert float((freq - torch.softmax(logits[0].cpu(), -1)).abs().max()) < 0.03
     out2 = F().sample_rows(logits, t, torch.full((4000,), 0.8, device=DEV), us)   # nucleus {2, 4}
     assert set(out2.cpu().tolist()) == {2, 4}
+
+
+# --------------------------------------------------------------------------- #
+# debug mode: indices checked on the host before a kernel can follow them
+# --------------------------------------------------------------------------- #
+
+def test_debug_bounds_mode_names_the_bad_index(monkeypatch):
+    """With the debug switch on, an index outside its buffer raises before the launch and names the tensor,
+    the place and the value; nothing runs.  (No bad index ever reaches the device in this test.)"""
+    from mini_infer_b200.ops.library import KernelError
+    f = F()
+    monkeypatch.setattr(f, "DEBUG_BOUNDS", True)
+    table = rnd(50, 16)
+    ids = torch.tensor([3, 49, 50], dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match=r"embed_gather ids: element 2 is 50, outside \[0, 50\)"):
+        f.embed_gather(ids, table)
+    case = paged_case([40, 9], [3, 1], 4, 2, 64, 8, torch.bfloat16)
+    f.attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 3)     # a good call passes
+    bad = case["table"].clone()
+    bad[0, 2] = case["kc"].shape[0]                                    # one past the last page
+    with pytest.raises(KernelError, match="request 0 reads page entry 2"):
+        f.attention(case["q"], case["kc"], case["vc"], bad, case["q_start"], case["kv_len"], 3)
+    with pytest.raises(KernelError, match="request 0 reads page entry 2"):
+        f.prefill_attention_tc(case["q"], case["kc"], case["vc"], bad, case["q_start"], case["kv_len"], 3)
+    long = torch.tensor([40, 200], dtype=torch.int32, device=DEV)      # longer than the table can hold
+    with pytest.raises(KernelError, match="request 1: kv_len 200"):
+        f.attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], long, 3)
+    x = rnd(6, 64, dtype=torch.bfloat16)
+    w = rnd(3, 32, 64, dtype=torch.bfloat16)
+    off = torch.tensor([0, 4, 3, 6], dtype=torch.int32, device=DEV)    # not rising
+    with pytest.raises(KernelError, match="do not rise from 0 to 6"):
+        f.grouped_gemm_plain(x, None, w, off, 6, False, torch.float32)
+    idx = torch.tensor([[0, 3]], dtype=torch.int32, device=DEV)        # expert 3 of 3
+    with pytest.raises(KernelError, match="expert indices: element 1 is 3"):
+        f.moe_permute(idx, 3)
+    dec = paged_case([700], [1], 2, 1, 64, 16, torch.bfloat16)
+    po, pml, _ = decode_scratch(1, 2, 700, 64)
+    with pytest.raises(KernelError, match="1 splits of 512 keys cannot hold"):
+        f.decode_attention(dec["q"], dec["kc"], dec["vc"], dec["table"], dec["q_start"], dec["kv_len"], po, pml, 1)
+    assert f.debug_checks_run > 0

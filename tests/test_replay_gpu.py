@@ -92,7 +92,7 @@ def test_tail_decoded_one_by_one(case, dtype, graphs, monkeypatch):
     one_token = sum(1 for st in steps if all(len(t) == 1 for _, t, _ in st["entries"]))
     assert one_token >= sum(min(32, len(t) - 1) for t in case["reqs"].values())
     assert runner.graph_replays == (one_token if graphs else 0)
-    if case["name"] in ("D", "E"):
+    if case["name"] in ("D", "E") and dtype == "bfloat16":
         assert calls.count["decode_attention"] > 0          # head size 64: the split-KV kernel
 
 

@@ -426,7 +426,7 @@ def test_attention_refuses_bad_shapes():
     with pytest.raises(KernelError, match="multiple"):
         F().attention(case["q"], case["kc"], case["vc"], case["table"], case["q_start"], case["kv_len"], 1)
     q = torch.zeros(1, 1, 300, device=DEV)
-    kc = torch.zeros(1, 1, 16, 300, device=DEV)
+    kc = torch.zeros(case["kc"].shape[0], 1, 16, 300, device=DEV)      # as many pages as the table names
     with pytest.raises(KernelError, match="head_dim"):
         F().attention(q, kc, kc.clone(), case["table"], case["q_start"], case["kv_len"], 1)
     with pytest.raises(RuntimeError, match="CUDA only"):

@@ -156,14 +156,23 @@ class Model:
         token indices), or None when no logits are wanted (the cache is still written)."""
         hidden = self.embedding.forward(ctx.token_ids)
         pending = None
-        for pos, e in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for pos, e in enumerate(schedule):
             layer = self.layers[e.layer]
             if not layer.block.accepts_deferred:
                 pending = resolve(pending)
+            if ctx.prefetch is not None:
+                # what the layer after this one reads first, for this layer's last part to ask L2 for
+                ctx.prefetch_upcoming = None
+                if pos + 1 < len(schedule):
+                    nxt, nxt_caches = self.layers[schedule[pos + 1].layer], self.bindings[pos + 1]
+                    ctx.prefetch_upcoming = lambda n=nxt, c=nxt_caches: n.block.prefetch_layer(n, ctx, c)
             pending = layer.block.forward(layer, hidden, pending, ctx, self.bindings[pos])
             if self.layer_observer is not None:
                 # the addition of a part's output is left to the next norm's kernel; form it here
                 self.layer_observer(pos, hidden if pending is None else hidden + resolve(pending))
+        if ctx.prefetch is not None:
+            ctx.prefetch.join()
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         x = apply_norm(self.final_norm, hidden, pending, rows=logit_rows)

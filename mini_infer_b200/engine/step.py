@@ -52,6 +52,38 @@ class StepError(ValueError):
     """The batch was refused before anything ran."""
 
 
+class WeightPrefetcher:
+    """Runs L2 prefetch requests on a stream of its own: a request starts once the kernels queued on the
+    calling stream so far have finished, beside whatever is queued next.  ``join`` ties the stream back
+    in (a captured pass has to end with every forked stream joined)."""
+
+    def __init__(self, device):
+        self.stream = torch.cuda.Stream(device=device)
+        self.forked = False
+
+    def __call__(self, what) -> None:
+        from ..ops import functional as F
+        if what is None:
+            return
+        if not callable(what):
+            what = [t for t in what if t is not None]
+            if not what:
+                return
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            if callable(what):
+                what()
+            else:
+                for t in what:
+                    F.l2_prefetch(t)
+        self.forked = True
+
+    def join(self) -> None:
+        if self.forked:
+            torch.cuda.current_stream().wait_stream(self.stream)
+            self.forked = False
+
+
 class ModelRunner:
     """Owns the device side of the cache and runs steps.
 
@@ -101,6 +133,7 @@ class ModelRunner:
         # tensor is static memory that a captured pass updates in place).
         self.cuda_graphs = bool(cuda_graphs) and all(getattr(p, "graph_safe", False) for p in model.all_parts())
         self._graphs: Dict[tuple, tuple] = {}
+        self._prefetcher = WeightPrefetcher(rt.device)
         # parts with settings that change what a captured pass launches, or that leave side outputs
         from ..parts.base import Part
         self._keyed_parts = [p for p in model.all_parts() if type(p).capture_key is not Part.capture_key
@@ -287,6 +320,9 @@ class ModelRunner:
             kv_len=d("kv_len", B), req_of_token=d("req_of_token", T), state_slot=d("state_slot", B),
             fresh=d("fresh", B), kv_groups=views, states=self.state_tensors, scratch=self.scratch,
             host_q_start=first.tolist(), host_kv_len=kv_len.tolist(), host_state_slot=slots.tolist())
+        from ..parts.tuning import TUNING
+        if self.rt.act == torch.bfloat16 and T <= TUNING.l2_prefetch_max_tokens:
+            ctx.prefetch = self._prefetcher
         logit_rows = d("logit_rows", R) if R else None
         return ctx, logit_rows, index
 

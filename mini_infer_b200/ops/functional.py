@@ -606,6 +606,16 @@ def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch
     return out
 
 
+def l2_prefetch(t: torch.Tensor, max_bytes: Optional[int] = None) -> None:
+    """Ask L2 for the first ``max_bytes`` bytes (all, if None) of a contiguous tensor; a hint, on the
+    current stream, that returns at once."""
+    _chk(t, "l2_prefetch tensor")
+    n = t.numel() * t.element_size()
+    if max_bytes is not None:
+        n = min(n, int(max_bytes))
+    check(library().mi_l2_prefetch(_ptr(t), n, _stream()), "l2_prefetch")
+
+
 def dense_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` in true float32 (``x [T, K]``, ``w [N, K]``): every output element is one chain of
     fused multiply-adds over ``k`` in ascending order, so a row's result does not depend on how many rows

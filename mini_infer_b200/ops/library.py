@@ -46,6 +46,7 @@ _SIGNATURES = {
     "mi_grouped_gemm_tc_form": [P, P, P, P, P, I, I, I, I, I, I, P],
     "mi_random_fill": [P, I, L, ctypes.c_uint, ctypes.c_uint, F, F, P],
     "mi_dense_f32": [P, P, P, I, I, I, P],
+    "mi_l2_prefetch": [P, ctypes.c_ulonglong, P],
 }
 
 

@@ -86,6 +86,11 @@ class GQAttention(Mixer):
             self._fused_qkv_rows = F.qkv_skinny_max_rows()
             self._b_qkv_f32 = None if self.b_qkv is None else self.b_qkv.float()
 
+    def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
+        """The q/k/v weights.  (Asking for the cache pages of the batch as well was measured and not kept:
+        the split-KV kernel is bound by the latency of its one wave, not by where its lines come from.)"""
+        F.l2_prefetch(self.w_qkv)
+
     # -- cache ------------------------------------------------------------- #
     def cache_need(self):
         return KVNeed(self.nkv, self.d, self.window)
@@ -105,6 +110,8 @@ class GQAttention(Mixer):
         if ctx.num_tokens <= self._fused_qkv_rows:
             q = F.qkv_skinny(x, self.w_qkv, self._b_qkv_f32, ctx.positions, self.inv_freq, view.slot_mapping,
                              kc, vc, self.nh, self.nkv, self.d, view.page_size)
+            if ctx.prefetch is not None:
+                ctx.prefetch((self.w_o,))       # arrives while the attention over the cache runs
         else:
             qkv = linear(x, self.w_qkv, torch.float32)
             nkv_in = 0 if self.shares_cache else self.nkv

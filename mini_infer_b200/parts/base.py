@@ -173,6 +173,13 @@ class StepContext:
     kv_groups: List[KVGroupView] = field(default_factory=list)
     states: List[torch.Tensor] = field(default_factory=list)   # [slots, *shape] per state user
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
+    # Hints for decode-sized steps (None when switched off).  ``prefetch(what)``: once the kernels queued so
+    # far have finished, ask L2 on a second stream, beside whatever is queued next, for ``what``: a sequence
+    # of weight tensors, or a function that issues the requests itself.  ``prefetch_upcoming``: a function
+    # that asks for what the layer after this one reads first (set by the model before each layer), so
+    # that a layer's last part can call ``ctx.prefetch(ctx.prefetch_upcoming)`` while its own tail runs.
+    prefetch: Optional[Any] = None
+    prefetch_upcoming: Optional[Any] = None
     # host copies, for parts written in plain PyTorch (tests' toy parts)
     host_q_start: Sequence[int] = ()
     host_kv_len: Sequence[int] = ()
@@ -196,6 +203,11 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         """Take the declared tensors (CPU or device, stored dtype) and keep what forward needs."""
         self.rt = rt
+
+    def prefetch_first(self, ctx: "StepContext", cache: Optional["CacheBinding"]) -> None:
+        """Ask L2 (``ops.functional.l2_prefetch*``, on the current stream) for what this part reads first
+        in a decode-sized step: called on a second stream while the part before it runs its last,
+        latency-bound kernels.  Default: nothing."""
 
     # -- a forward pass captured as a CUDA graph -------------------------------------------- #
     def capture_key(self):
@@ -329,6 +341,9 @@ class Block(Part):
     def forward(self, layer: "BuiltLayer", hidden: torch.Tensor, pending: Optional[torch.Tensor],
                 ctx: StepContext, caches: Mapping[str, CacheBinding]) -> torch.Tensor:
         raise NotImplementedError
+
+    def prefetch_layer(self, layer: "BuiltLayer", ctx: StepContext, caches: Mapping[str, CacheBinding]) -> None:
+        """``prefetch_first`` of whichever part of ``layer`` this arrangement runs first."""
 
 
 class BuiltLayer:

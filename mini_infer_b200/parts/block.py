@@ -31,6 +31,9 @@ class PreNormResidual(Block):
         y = layer.mixer.forward(x, ctx, caches.get("mixer"))
         return layer.feed_forward.forward_from_residual(hidden, y, layer.feed_forward_norm, ctx)
 
+    def prefetch_layer(self, layer: BuiltLayer, ctx: StepContext, caches) -> None:
+        layer.mixer.prefetch_first(ctx, caches.get("mixer"))
+
 
 class TokenEmbedding(Embedding):
     """params: ``vocab_size``, ``hidden_size``.  Tensor: ``<prefix>weight [V, H]``; no scaling

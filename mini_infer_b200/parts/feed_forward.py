@@ -176,6 +176,9 @@ class SparseMoE(FeedForward):
         (the routing's blocks read the row anyway); the others take the norm's own kernel."""
         T = hidden.shape[0]
         rms = norm.rms_parameters()
+        if ctx.prefetch is not None and self.sI > 0:
+            # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
+            ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
         if (rms is not None and self._skinny and T <= min(self._pairs_max, TUNING.shared_expert_fork_after_routing_max_tokens)
                 and T * self.K <= TUNING.expert_skinny_rows_per_expert * self.E and F.norm_route_small_takes(self.H)
                 and (delta is None or isinstance(delta, torch.Tensor))):
@@ -206,6 +209,9 @@ class SparseMoE(FeedForward):
                 side, shared = self._fork_shared_expert(x)
             act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True)
             y = F.grouped_gemm_skinny_pairs(act, idx, self.w_down, False)
+            if ctx.prefetch is not None:
+                # while the experts' rows are summed and normalised, the next layer's first weights arrive
+                ctx.prefetch(ctx.prefetch_upcoming)
         else:
             if overlap:
                 side, shared = self._fork_shared_expert(x)

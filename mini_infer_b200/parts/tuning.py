@@ -47,6 +47,10 @@ class Tuning:
     # kernel for every step, so that a request's logits do not depend on its batch.)
     decode_split_by_requests: Tuple[Tuple[int, int], ...] = ((2, 128), (4, 256))
 
+    # Steps of at most this many tokens ask L2 for the next dense weights (q/k/v, o_proj, shared expert)
+    # on a second stream while a latency-bound kernel runs (0 = off).
+    l2_prefetch_max_tokens: int = 8
+
     def decode_split(self, num_requests: int, default: int) -> int:
         for limit, split in self.decode_split_by_requests:
             if num_requests <= limit:
@@ -54,4 +58,18 @@ class Tuning:
         return default
 
 
-TUNING = Tuning()
+def _from_environment(t: Tuning) -> Tuning:
+    """``MINI_INFER_TUNING="name=value,name=value"`` overrides integer and boolean fields, for re-measuring a
+    threshold without editing this file."""
+    import os
+    text = os.environ.get("MINI_INFER_TUNING", "")
+    for item in filter(None, (x.strip() for x in text.split(","))):
+        name, _, value = item.partition("=")
+        if not hasattr(t, name) or isinstance(getattr(t, name), tuple):
+            raise ValueError(f"MINI_INFER_TUNING: no integer or boolean threshold called '{name}'")
+        old = getattr(t, name)
+        setattr(t, name, (value.lower() in ("1", "true", "yes")) if isinstance(old, bool) else int(value))
+    return t
+
+
+TUNING = _from_environment(Tuning())

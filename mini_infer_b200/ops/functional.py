@@ -13,7 +13,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from .library import check, library
+from .library import KernelError, check, library
 
 F32 = torch.float32
 BF16 = torch.bfloat16

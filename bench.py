@@ -130,6 +130,86 @@ def prefill_flops(cfg, layers, T):
     return layers * (per_tok * T + attn) + 2 * V * H
 
 
+def run_timeline(args):
+    """``--timeline``: the kernels of one step as they run inside the engine (CUPTI through torch.profiler:
+    real overlap between streams, CUDA-graph replays for decode), aggregated by kernel and, for one layer,
+    in time order.  Prints text, not the JSON line; nothing here is a benchmark value."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from mini_infer_b200.engine.defaults import DEFAULT_PAGE_SIZE
+    from mini_infer_b200.engine.loading import random_model
+    from mini_infer_b200.engine.step import ModelRunner, StepEntry
+
+    model_name, named = SIZES[args.sizes]
+    cfg = dict(named)
+    cfg["num_hidden_layers"] = args.layers if args.layers > 0 else 4
+    model, rt = random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0")
+    page, B, T = DEFAULT_PAGE_SIZE, args.batch, args.prompt_len
+    decode = args.only != "prefill"
+    runner = ModelRunner(model, rt, page_size=page, num_pages=(B if decode else 2) * (T // page + 8),
+                         max_requests=max(B, 2), max_tokens_per_step=max(T, B), max_context=args.context,
+                         cuda_graphs=not args.eager)
+    g = torch.Generator().manual_seed(args.seed)
+
+    def prompt():
+        return torch.randint(0, cfg["vocab_size"], (T,), generator=g).tolist()
+
+    if decode:
+        for b in range(B):
+            runner.add_request(b)
+            runner.step([StepEntry(b, prompt(), [])])
+        state = {"toks": [1] * B}
+
+        def step():
+            res = runner.step([StepEntry(b, [state["toks"][b]], [0]) for b in range(B)])
+            state["toks"] = res.logits.argmax(-1).tolist()
+        first_kernel, layer_mark = "embed_gather", ("qkv_skinny", "qkv_post")
+    else:
+        count = {"n": 0}
+
+        def step():
+            count["n"] += 1
+            runner.add_request(("p", count["n"]))
+            runner.step([StepEntry(("p", count["n"]), prompt(), [T - 1])])
+            runner.release(("p", count["n"]))
+        first_kernel, layer_mark = "embed_gather", ("qkv_post", "qkv_skinny")
+    for _ in range(4):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.name
+           and "Memcpy" not in e.name and "Memset" not in e.name]
+    evs.sort(key=lambda e: e.time_range.start)
+    starts = [i for i, e in enumerate(evs) if first_kernel in e.name]
+    sel = evs[starts[-1]:]
+    t0, last_end, idle = sel[0].time_range.start, sel[0].time_range.start, 0.0
+    agg = collections.OrderedDict()
+    for e in sel:
+        s_, e_ = e.time_range.start, e.time_range.end
+        idle += max(0.0, s_ - last_end)
+        last_end = max(last_end, e_)
+        a = agg.setdefault(e.name[:90], [0, 0.0])
+        a[0] += 1
+        a[1] += e_ - s_
+    what = f"decode step, batch {B}, context {T}" if decode else f"prefill of {T} tokens"
+    print(f"{what}, {cfg['num_hidden_layers']} layers of {model_name} size: {last_end - t0:.1f} us from the first "
+          f"kernel's start to the last one's end, {idle:.1f} us with no kernel running, {len(sel)} kernels")
+    for n, (c, d) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f"{d:9.1f} us x{c:<4} {n}")
+    marks = [i for i, e in enumerate(sel) if any(m in e.name for m in layer_mark)]
+    if len(marks) >= 3:
+        a, b = marks[1] - 1, marks[2] - 1
+        base = sel[a].time_range.start
+        print("one layer in time order (start, duration):")
+        for e in sel[a:b]:
+            print(f"  +{e.time_range.start - base:7.1f}  {e.time_range.end - e.time_range.start:6.1f} us  {e.name[:80]}")
+    return 0
+
+
 def run_ours(args):
     import torch
     from mini_infer_b200.engine.llm import LLM, GPUExecutor
@@ -436,6 +516,9 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="wrap the timed region in cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--eager", action="store_true", help="launch decode steps kernel by kernel, without CUDA graphs")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the kernels of one step as they run inside the engine (with --only decode or "
+                         "--only prefill; --layers defaults to 4) instead of benchmarking")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     ap.add_argument("--reference-prefill-batch", type=int, default=1,
                     help="prompts the reference's scheduler prefills per iteration (its cuBLAS handles, one per "
@@ -449,6 +532,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.timeline:
+        return run_timeline(args)
     return run_ours(args)
 
 

@@ -53,17 +53,30 @@ def checkpoint():
     torch.cuda.empty_cache()
 
 
+_ENGINES = {}
+
+
+def _engine(dtype, checkpoint):
+    if dtype not in _ENGINES:
+        from mini_infer_b200.config import build_model_spec
+        from mini_infer_b200.engine.loading import _runtime
+        from mini_infer_b200.engine.model import Model
+        rt = _runtime(dtype, "cuda:0")
+        model = Model(build_model_spec(checkpoint["cfg"]))
+        model.load(DictSource(checkpoint["weights"]), rt)
+        _ENGINES[dtype] = {"model": model, "rt": rt, "dtype": dtype}
+    return _ENGINES[dtype]
+
+
 @pytest.fixture(scope="module", params=["float32", "bfloat16"])
 def engine(request, checkpoint):
-    from mini_infer_b200.config import build_model_spec
-    from mini_infer_b200.engine.loading import _runtime
-    from mini_infer_b200.engine.model import Model
-    dtype = request.param
-    rt = _runtime(dtype, "cuda:0")
-    model = Model(build_model_spec(checkpoint["cfg"]))
-    model.load(DictSource(checkpoint["weights"]), rt)
-    yield {"model": model, "rt": rt, "dtype": dtype}
-    del model
+    return _engine(request.param, checkpoint)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _free_engines():
+    yield
+    _ENGINES.clear()
     torch.cuda.empty_cache()
 
 
@@ -110,10 +123,9 @@ def test_mixed_with_pages_used_again(engine, checkpoint):
     assert runner.graph_replays == sum(1 for st in steps if all(len(t) == 1 for _, t, _ in st["entries"]))
 
 
-def test_float32_cuttings_agree_bit_for_bit(engine, checkpoint):
+def test_float32_cuttings_agree_bit_for_bit(checkpoint):
     """At real sizes too, the float32 path gives the same bits whole, in portions and mixed with others."""
-    if engine["dtype"] != "float32":
-        pytest.skip("bit-for-bit agreement is the float32 path's property")
+    engine = _engine("float32", checkpoint)
     from engine_harness import run_trace
     reqs = checkpoint["reqs"]
     a = run_trace(_runner(engine, 96), traces.whole(reqs))

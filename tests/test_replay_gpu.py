@@ -25,15 +25,24 @@ LENGTHS = {"A": [5, 41, 70, 17, 33, 64, 49, 9], "B": [1, 9, 23, 40, 77, 48, 65, 
            "C": [3, 90, 25, 57, 48, 31, 72, 12], "D": [37, 300, 129, 64], "E": [150, 41, 333, 96, 200]}
 
 
+_CASES = {}
+
+
+def _case(name, tmp_path_factory):
+    """The model folder, weights and requests of one tiny configuration (made once per test session)."""
+    if name not in _CASES:
+        cfg = tiny.CONFIGS[name]
+        folder = str(tmp_path_factory.mktemp(f"model_{name}"))
+        tiny.make_folder(folder, cfg, seed=11 + ord(name), dtype=torch.bfloat16)
+        weights = tiny.read_weights(folder)
+        reqs = {f"r{i}": tiny.pick_tokens(cfg, weights, n, seed=1000 * (i + 1)) for i, n in enumerate(LENGTHS[name])}
+        _CASES[name] = {"name": name, "cfg": cfg, "folder": folder, "reqs": reqs, "weights": weights}
+    return _CASES[name]
+
+
 @pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def case(request, tmp_path_factory):
-    name = request.param
-    cfg = tiny.CONFIGS[name]
-    folder = str(tmp_path_factory.mktemp(f"model_{name}"))
-    tiny.make_folder(folder, cfg, seed=11 + ord(name), dtype=torch.bfloat16)
-    weights = tiny.read_weights(folder)
-    reqs = {f"r{i}": tiny.pick_tokens(cfg, weights, n, seed=1000 * (i + 1)) for i, n in enumerate(LENGTHS[name])}
-    return {"name": name, "cfg": cfg, "folder": folder, "reqs": reqs, "weights": weights}
+    return _case(request.param, tmp_path_factory)
 
 
 @pytest.fixture(scope="module", params=["float32", "bfloat16"])
@@ -104,10 +113,7 @@ def test_portions_of_changing_size(case, dtype, monkeypatch):
         assert calls.count["grouped_gemm_tc"] > 0 and calls.count["prefill_attention_tc"] > 0
 
 
-@pytest.mark.parametrize("page_size", [16, 4, 64])
-def test_mixed_with_pages_used_again(case, dtype, page_size, monkeypatch):
-    if page_size == 64 and case["name"] != "E":
-        pytest.skip("pages of 64 tokens only for the configuration that takes the tensor-core kernels")
+def _mixed(case, dtype, page_size, monkeypatch):
     calls = KernelCalls(monkeypatch)
     # the tensor-core configuration gets portions large enough for the tcgen05 grouped product
     steps = traces.mixed(case["reqs"], max_live=4, seed=3, max_portion=60 if case["name"] == "E" else 11)
@@ -125,6 +131,17 @@ def test_mixed_with_pages_used_again(case, dtype, page_size, monkeypatch):
         assert calls.count["grouped_gemm_tc"] > 0
         # the tcgen05 attention takes pages of 8 to 64 tokens; pages of 4 go to the mma.sync kernel
         assert (calls.count["prefill_attention_tc"] > 0) == (page_size >= 8)
+
+
+@pytest.mark.parametrize("page_size", [16, 4])
+def test_mixed_with_pages_used_again(case, dtype, page_size, monkeypatch):
+    _mixed(case, dtype, page_size, monkeypatch)
+
+
+def test_mixed_with_pages_of_64_tokens(dtype, tmp_path_factory, monkeypatch):
+    """The largest page the tcgen05 attention takes (one TMA box per page fills a whole key tile), with the
+    configuration whose sizes the tensor-core kernels take."""
+    _mixed(_case("E", tmp_path_factory), dtype, 64, monkeypatch)
 
 
 def test_cuttings_agree_with_each_other(case):

@@ -23,6 +23,7 @@ from .request import Request
 from .scheduler import IterationStats, Scheduler, SchedulerConfig
 from ..cache.pages import OutOfPages
 from .step import ModelRunner, StepEntry
+from ..parts.tuning import TUNING
 
 
 @dataclass
@@ -148,7 +149,11 @@ class LLM:
         max_tokens_per_step = max(max_tokens_per_step, max_running)
         self.runner = ModelRunner(self.model, self.rt, page_size=page_size, num_pages=num_pages,
                                   max_requests=max_running, max_tokens_per_step=max_tokens_per_step,
-                                  max_context=max_seq_len, cuda_graphs=cuda_graphs)
+                                  max_context=max_seq_len, cuda_graphs=cuda_graphs,
+                                  graph_chunk_tokens=min(prefill_chunk or max_tokens_per_step, max_tokens_per_step)
+                                  if TUNING.prefill_chunk_graph_min_tokens > 0 and
+                                  min(prefill_chunk or max_tokens_per_step, max_tokens_per_step)
+                                  >= TUNING.prefill_chunk_graph_min_tokens else 0)
         self.sampler = Sampler(self.rt.device, self.model.spec.vocab_size, max_running)
         self.executor = GPUExecutor(self.runner, self.sampler)
         self.sched_cfg = SchedulerConfig(max_tokens_per_step=max_tokens_per_step, max_running=max_running,

@@ -93,7 +93,7 @@ class ModelRunner:
     """
 
     def __init__(self, model: Model, rt: Runtime, *, page_size: int, num_pages: int, max_requests: int,
-                 max_tokens_per_step: int, max_context: int, cuda_graphs: bool = True):
+                 max_tokens_per_step: int, max_context: int, cuda_graphs: bool = True, graph_chunk_tokens: int = 0):
         if rt.device.type != "cuda":
             raise RuntimeError("ModelRunner: the engine runs on a CUDA device only; there is no CPU path")
         self.model = model
@@ -132,6 +132,9 @@ class ModelRunner:
         # by not declaring ``graph_safe``; a part with a state of its own may declare it (its state
         # tensor is static memory that a captured pass updates in place).
         self.cuda_graphs = bool(cuda_graphs) and all(getattr(p, "graph_safe", False) for p in model.all_parts())
+        # steps of exactly this many tokens of one request (the scheduler's full prompt portions) are replayed
+        # from a captured pass as well (0: only decode steps are)
+        self.graph_chunk_tokens = int(graph_chunk_tokens)
         self._graphs: Dict[tuple, tuple] = {}
         self._prefetcher = WeightPrefetcher(rt.device)
         # parts with settings that change what a captured pass launches, or that leave side outputs
@@ -326,28 +329,47 @@ class ModelRunner:
         logit_rows = d("logit_rows", R) if R else None
         return ctx, logit_rows, index
 
-    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+    def _graphs_allowed(self) -> bool:
         if not self.cuda_graphs or self.model.layer_observer is not None:
             return False
         from ..ops import functional as F
-        if F.DEBUG_BOUNDS:           # the debug checks read indices back on the host: not inside a capture
-            return False
-        return not any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries)
+        return not F.DEBUG_BOUNDS    # the debug checks read indices back on the host: not inside a capture
 
-    def _decode_with_graph(self, ctx: StepContext, logit_rows: torch.Tensor) -> torch.Tensor:
+    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+        """A decode step: one token per request, logits wanted for each."""
+        return self._graphs_allowed() and not any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries)
+
+    def _chunk_graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+        """A full portion of one prompt: with chunked prefill every full chunk of a long prompt has the same
+        shape (one request, ``graph_chunk_tokens`` tokens, logits at the last place or nowhere), and how
+        much context lies before it is device data, so its forward pass is captured once and replayed: the
+        gaps between the dependent launches of an eager pass shrink to a graph's."""
+        if self.graph_chunk_tokens <= 0 or len(entries) != 1 or not self._graphs_allowed():
+            return False
+        e = entries[0]
+        n = len(e.tokens)
+        return n == self.graph_chunk_tokens and list(e.want) in ([], [n - 1])
+
+    def _decode_with_graph(self, ctx: StepContext, logit_rows: Optional[torch.Tensor],
+                           chunk: bool = False) -> Optional[torch.Tensor]:
         """Replay (or first capture) the forward pass for this batch size and context-length bucket.
         The captured pass reads the same staging views every time and is launched for the longest
         context of its bucket, so only the data in the staging buffer changes between replays."""
         B = ctx.num_requests
-        # launch shapes that follow the context length (the splits of the decode attention) are captured
-        # for the next power of two, at least 1024: a few graphs per batch size, and a short context is
-        # not launched with the grid of the longest one
-        bucket = 1024
-        while bucket < ctx.max_kv_len:
-            bucket *= 2
-        ctx.max_kv_len = min(bucket, self.max_context)
+        if chunk:
+            # no launch shape of a prompt portion follows the context length
+            ctx.max_kv_len = self.max_context
+        else:
+            # launch shapes that follow the context length (the splits of the decode attention) are captured
+            # for the next power of two, at least 1024: a few graphs per batch size, and a short context is
+            # not launched with the grid of the longest one
+            bucket = 1024
+            while bucket < ctx.max_kv_len:
+                bucket *= 2
+            ctx.max_kv_len = min(bucket, self.max_context)
         parts = self._keyed_parts
-        key = (B, ctx.max_kv_len, tuple(p.capture_key() for p in parts))
+        key = (B, ctx.max_kv_len, tuple(p.capture_key() for p in parts),
+               (ctx.num_tokens, logit_rows is not None) if chunk else None)
         if key not in self._graphs:
             # The warm-up pass (library workspaces, lazy initialisation) runs the step for real: what it
             # writes into the paged caches is written again by the replay, but a per-request state would
@@ -391,6 +413,10 @@ class ModelRunner:
         try:
             if self._graph_eligible(entries):
                 logits = self._decode_with_graph(ctx, logit_rows)
+            elif self._chunk_graph_eligible(entries):
+                logits = self._decode_with_graph(ctx, logit_rows, chunk=True)
+                from ..ops.functional import check_tc_status
+                check_tc_status()
             else:
                 logits = self.model.forward(ctx, logit_rows)
                 from ..ops.functional import check_tc_status

@@ -47,6 +47,12 @@ class Tuning:
     # kernel for every step, so that a request's logits do not depend on its batch.)
     decode_split_by_requests: Tuple[Tuple[int, int], ...] = ((2, 128), (4, 256))
 
+    # Chunked prefill: every full portion of a long prompt has the same shape, so its forward pass is replayed
+    # from a CUDA graph too, if a portion has at least this many tokens (0: never).  Below a few hundred
+    # tokens a portion's kernels are too short for the saved launch gaps to matter against the memory a
+    # captured pass holds.
+    prefill_chunk_graph_min_tokens: int = 512
+
     # Steps of at most this many tokens ask L2 for the next dense weights (q/k/v, o_proj, shared expert)
     # on a second stream while a latency-bound kernel runs (0 = off).
     l2_prefetch_max_tokens: int = 8

@@ -148,6 +148,31 @@ def test_generation_as_the_product_runs_it_against_the_plain_model(tmp_path, nam
     compare_generation(obs, llm._calls, prompts, outs, cfg, w, dtype, 2e-5 if dtype == "float32" else 2e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_prompt_portions_are_graph_replays_too(tmp_path, dtype, monkeypatch):
+    """With chunked prefill every full portion of a long prompt has the same shape; its pass is captured once
+    and replayed with whatever context lies before it.  A prompt of 5 full portions and a rest, then decoding:
+    the logits of every sampled token against the plain model."""
+    from engine_harness import GenerationObserver, compare_generation
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.parts.tuning import TUNING
+    from mini_infer_b200.sampling import SamplingParams
+    monkeypatch.setattr(TUNING, "prefill_chunk_graph_min_tokens", 64)
+    cfg = tiny.CONFIGS["E"]
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=59, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    prompts = [tiny.pick_tokens(cfg, w, 5 * 64 + 37, 11)]
+    llm = LLM(folder, dtype=dtype, max_seq_len=512, max_running=2, max_tokens_per_step=64, prefill_chunk=64)
+    assert llm.runner.graph_chunk_tokens == 64
+    obs = GenerationObserver(llm.runner, [len(p) for p in prompts])
+    llm.executor.observer = obs
+    outs = llm.generate(prompts, SamplingParams(greedy=True, max_new_tokens=6))
+    chunk_keys = [k for k in llm.runner._graphs if k[3] is not None]
+    assert chunk_keys == [(1, 512, chunk_keys[0][2], (64, False))]           # one captured pass, replayed 5 times
+    assert llm.runner.graph_replays >= 5 + 4
+    compare_generation(obs, llm._calls, prompts, outs, cfg, w, dtype, 2e-5 if dtype == "float32" else 2e-2)
+
+
 @pytest.mark.parametrize("dtype,new_tokens,margin", [("float32", 20, 1e-4), ("bfloat16", 6, 0.02)])
 def test_preemption_recomputes_the_same_tokens(folders, dtype, new_tokens, margin):
     """So few pages that decoding requests are preempted and recomputed; tokens must not change.

@@ -10,6 +10,8 @@
 // float accumulation), the (token, slot) pairs are sorted by expert with a stable
 // counting sort, and each expert multiplies only its own rows.
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace mi {
@@ -280,19 +282,14 @@ moe_router_logits_small_kernel(const AT* __restrict__ x, const WT* __restrict__ 
 }
 
 // Softmax over all experts, K rounds of arg-max (lowest index among equals), weights; one warp per
-// token.  `p` is the warp's E floats of shared memory; the logits are read around L1 (they may have
-// been written by other blocks of the same launch).
-__device__ __forceinline__ void router_select_token(const float* __restrict__ z, int has_gate,
-                                                    int* __restrict__ topk_idx, float* __restrict__ topk_w,
-                                                    float* __restrict__ gate, float* __restrict__ probs_out,
-                                                    float* p, int* idx_copy, int t, int E, int K,
-                                                    int norm_topk) {
+// token.  `p` is the warp's E floats of shared memory and holds the token's logits, `mx` the largest
+// of the lane's own, `gate_logit` (lane 0) the shared expert's.
+__device__ __forceinline__ void router_select_loaded(float mx, float gate_logit, int has_gate,
+                                                     int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                     float* __restrict__ gate, float* __restrict__ probs_out,
+                                                     float* p, int* idx_copy, int t, int E, int K, int norm_topk) {
     const int lane = threadIdx.x & 31;
-    const int ncols = E + (has_gate ? 1 : 0);
-    const float* zr = z + (int64_t)t * ncols;
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) { const float v = __ldcg(zr + e); p[e] = v; mx = fmaxf(mx, v); }
-    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-__ldcg(zr + E)));
+    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-gate_logit));
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
@@ -333,6 +330,34 @@ __device__ __forceinline__ void router_select_token(const float* __restrict__ z,
         __syncwarp();
     }
     if (lane < K) topk_w[(int64_t)t * K + lane] = norm_topk ? my_w / wsum : my_w;
+}
+
+// the logits of token t in global memory, read around L1 (other blocks of the same launch may have written them)
+__device__ __forceinline__ void router_select_token(const float* __restrict__ z, int has_gate,
+                                                    int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                    float* __restrict__ gate, float* __restrict__ probs_out,
+                                                    float* p, int* idx_copy, int t, int E, int K,
+                                                    int norm_topk) {
+    const int lane = threadIdx.x & 31;
+    const int ncols = E + (has_gate ? 1 : 0);
+    const float* zr = z + (int64_t)t * ncols;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) { const float v = __ldcg(zr + e); p[e] = v; mx = fmaxf(mx, v); }
+    const float gl = (has_gate && lane == 0) ? __ldcg(zr + E) : 0.f;
+    router_select_loaded(mx, gl, has_gate, topk_idx, topk_w, gate, probs_out, p, idx_copy, t, E, K, norm_topk);
+}
+
+// the logits of ONE token in this block's shared memory
+__device__ __forceinline__ void router_select_logits(const float* zs, int has_gate,
+                                                     int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                     float* __restrict__ gate, float* __restrict__ probs_out,
+                                                     float* p, int* idx_copy, int t, int E, int K,
+                                                     int norm_topk) {
+    const int lane = threadIdx.x & 31;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) { const float v = zs[e]; p[e] = v; mx = fmaxf(mx, v); }
+    const float gl = (has_gate && lane == 0) ? zs[E] : 0.f;
+    router_select_loaded(mx, gl, has_gate, topk_idx, topk_w, gate, probs_out, p, idx_copy, t, E, K, norm_topk);
 }
 
 __global__ void __launch_bounds__(256)
@@ -438,12 +463,15 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
     permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + TOK * E, T * K, E, K, 3);
 }
 
-// The same with the residual addition and RMSNorm that precede the router folded in, for the
-// smallest steps: every block of a token forms v = hidden[t] + delta[t] and its RMS itself (the
-// additions in the order of add_rmsnorm's vector kernel), takes its logit from the normalised row
-// rounded to the activation type, and the block that finishes the token last writes hidden[t] and
-// the normalised row x_out[t] for the kernels that follow: by then no block reads hidden[t] any more.
-// H is a multiple of 4 of at most 4 * 8 * 256.
+// The residual addition and RMSNorm that precede the router and the routing itself in one launch, for the
+// smallest steps: a CLUSTER of NR_CLUSTER blocks per token.  Every block first asks for its share of the
+// router's rows (asynchronous copies into shared memory: all of them in flight at once), then forms
+// v = hidden[t] + delta[t] and its RMS itself (thread i holds the float4s i, i + 256, ...: the additions run
+// in the order of add_rmsnorm's vector kernel, so the normalised row has that kernel's bits), keeps the
+// normalised row, rounded to the activation type, in shared memory, and takes its rows' logits from there;
+// the logits go to the first block's shared memory over the cluster's network.  After one cluster barrier
+// the first block writes hidden[t] (no block reads it any more) and selects the token's experts.  Nothing
+// waits on a counter in memory.  H is a multiple of 4 of at most 4 * 8 * 256.
 // four consecutive elements of a row, held as loaded and widened when used
 template <typename T4> struct Row4;
 template <> struct Row4<float> {
@@ -472,28 +500,73 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
 
 constexpr int NR_VMAX = 8;
 
+constexpr int NR_CLUSTER = 8;
+
+template <typename WT> struct AsyncRow4;
+template <> struct AsyncRow4<float> {
+    static __device__ __forceinline__ void copy(float* dst, const float* src) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+    }
+};
+template <> struct AsyncRow4<__nv_bfloat16> {
+    static __device__ __forceinline__ void copy(__nv_bfloat16* dst, const __nv_bfloat16* src) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+    }
+};
+__device__ __forceinline__ void load4_shared(const float* p, float (&o)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    o[0] = r.x; o[1] = r.y; o[2] = r.z; o[3] = r.w;
+}
+__device__ __forceinline__ void load4_shared(const __nv_bfloat16* p, float (&o)[4]) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+
+// shared memory of a block: the normalised row [H] floats, the block's router rows [rows][H] of WT, and (used
+// by the cluster's first block) the token's logits [ncols] and the selection's scratch [E]
+__host__ __device__ inline size_t norm_route_small_smem(int H, int E, int ncols, size_t wbytes) {
+    const int rows = (ncols + NR_CLUSTER - 1) / NR_CLUSTER;
+    return sizeof(float) * (size_t)H + wbytes * (size_t)rows * H + sizeof(float) * ((size_t)ncols + E + 4);
+}
+
 template <typename AT, typename WT, typename NT>
 __global__ void __launch_bounds__(256)
 moe_norm_route_small_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
                             const NT* __restrict__ norm_w, float eps, AT* __restrict__ x_out,
-                            const WT* __restrict__ wr, const WT* __restrict__ wsg, float* __restrict__ z,
-                            unsigned* __restrict__ tickets, int* __restrict__ topk_idx, float* __restrict__ topk_w,
-                            float* __restrict__ gate, float* __restrict__ probs_out, int* __restrict__ offsets,
-                            int* __restrict__ sorted_token, int* __restrict__ inv_perm, int T, int H, int E, int K,
-                            int norm_topk) {
-    extern __shared__ int route_sh[];  // select: [E] floats; then permute: [E+1] + [T*K] ints
-    __shared__ bool last;
-    __shared__ float scratch[32], part[8];
-    const int t = blockIdx.y, e = blockIdx.x;
+                            const WT* __restrict__ wr, const WT* __restrict__ wsg,
+                            int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ gate,
+                            float* __restrict__ probs_out, int T, int H, int E, int K, int norm_topk) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ __align__(16) unsigned char nr_raw[];
+    __shared__ float scratch[32];
+    const int ncols = E + (wsg ? 1 : 0);
+    const int rows = (ncols + NR_CLUSTER - 1) / NR_CLUSTER;
+    float* xs = reinterpret_cast<float*>(nr_raw);
+    WT* wrows = reinterpret_cast<WT*>(nr_raw + sizeof(float) * (size_t)H);
+    float* zs = reinterpret_cast<float*>(nr_raw + sizeof(float) * (size_t)H + sizeof(WT) * (size_t)rows * H);
+    float* sel = zs + ncols;
+    const int rank = blockIdx.x;                              // the grid is (NR_CLUSTER, T): the rank in the cluster
+    const int t = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nv = H >> 2;
+    const int r0 = min(ncols, rank * rows), r1 = min(ncols, r0 + rows);
+    // first half of a barrier that is completed before the first write into another block's shared memory:
+    // that block has to have started by then
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    for (int r = r0; r < r1; ++r) {
+        const WT* src = r < E ? wr + (int64_t)r * H : wsg;
+        WT* dst = wrows + (size_t)(r - r0) * H;
+        for (int i = threadIdx.x; i < nv; i += 256) AsyncRow4<WT>::copy(dst + 4 * i, src + 4 * i);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
     float4* h4 = reinterpret_cast<float4*>(hidden + (int64_t)t * H);
     const float4* d4 = delta ? reinterpret_cast<const float4*>(delta + (int64_t)t * H) : nullptr;
-    const int ncols = E + (wsg ? 1 : 0);
-    const WT* w = e < E ? wr + (int64_t)e * H : wsg;
     float4 v[NR_VMAX];
     Row4<NT> nrow[NR_VMAX];                                  // fetched before the sum of squares is known
-    Row4<WT> wrow[NR_VMAX];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < NR_VMAX; ++j) {
@@ -501,7 +574,6 @@ moe_norm_route_small_kernel(float* __restrict__ hidden, const float* __restrict_
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < nv) {
             nrow[j].load(norm_w + 4 * i);
-            wrow[j].load(w + 4 * i);
             v[j] = h4[i];
             if (d4) {
                 const float4 dv = d4[i];
@@ -515,62 +587,52 @@ moe_norm_route_small_kernel(float* __restrict__ hidden, const float* __restrict_
     }
     ss = block_sum(ss, scratch);
     const float rrms = rsqrtf(ss / (float)H + eps);
-    float acc = 0.f;
-#pragma unroll
-    for (int j = 0; j < NR_VMAX; ++j) {
-        const int i = threadIdx.x + 256 * j;
-        if (i < nv) {
-            float nw[4], ww[4];
-            nrow[j].get(nw);
-            wrow[j].get(ww);
-            // the row as the following kernels will read it: rounded to the activation type
-            acc += to_float(from_float<AT>(v[j].x * rrms * nw[0])) * ww[0];
-            acc += to_float(from_float<AT>(v[j].y * rrms * nw[1])) * ww[1];
-            acc += to_float(from_float<AT>(v[j].z * rrms * nw[2])) * ww[2];
-            acc += to_float(from_float<AT>(v[j].w * rrms * nw[3])) * ww[3];
-        }
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) part[warp] = acc;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float zz = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < 8; ++wv) zz += part[wv];
-        z[(int64_t)t * ncols + e] = zz;
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(&tickets[1 + t], 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    if (threadIdx.x == 0) tickets[1 + t] = 0u;
     AT* xo = x_out + (int64_t)t * H;
 #pragma unroll
     for (int j = 0; j < NR_VMAX; ++j) {
         const int i = threadIdx.x + 256 * j;
         if (i < nv) {
-            if (d4) h4[i] = v[j];
             float nw[4];
             nrow[j].get(nw);
-            const float xs[4] = {v[j].x * rrms * nw[0], v[j].y * rrms * nw[1], v[j].z * rrms * nw[2],
+            const float xv[4] = {v[j].x * rrms * nw[0], v[j].y * rrms * nw[1], v[j].z * rrms * nw[2],
                                  v[j].w * rrms * nw[3]};
-            store4(xo + 4 * i, xs);
+            if (rank == 0) store4(xo + 4 * i, xv);
+            // the row as the following kernels will read it: rounded to the activation type
+            *reinterpret_cast<float4*>(xs + 4 * i) =
+                make_float4(to_float(from_float<AT>(xv[0])), to_float(from_float<AT>(xv[1])),
+                            to_float(from_float<AT>(xv[2])), to_float(from_float<AT>(xv[3])));
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+    float* zs0 = cluster.map_shared_rank(zs, 0);
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    for (int r = r0 + warp; r < r1; r += 8) {
+        const WT* w = wrows + (size_t)(r - r0) * H;
+        float acc = 0.f;
+        for (int i = lane; i < nv; i += 32) {
+            float ww[4];
+            load4_shared(w + 4 * i, ww);
+            const float4 x = *reinterpret_cast<const float4*>(xs + 4 * i);
+            acc += x.x * ww[0];
+            acc += x.y * ww[1];
+            acc += x.z * ww[2];
+            acc += x.w * ww[3];
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) zs0[r] = acc;
+    }
+    cluster.sync();                                           // the logits have arrived; nobody reads hidden[t] any more
+    if (rank != 0) return;
+    if (d4) {
+#pragma unroll
+        for (int j = 0; j < NR_VMAX; ++j) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < nv) h4[i] = v[j];
         }
     }
     if (threadIdx.x < 32)
-        router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, reinterpret_cast<float*>(route_sh),
-                            nullptr, t, E, K, norm_topk);
-    if (!offsets) return;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(&tickets[0], 1u) == (unsigned)T - 1;
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    if (threadIdx.x == 0) tickets[0] = 0u;
-    permute_block(topk_idx, offsets, sorted_token, inv_perm, route_sh + E, T * K, E, K, 3);
+        router_select_logits(zs, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out, sel, nullptr, t, E, K, norm_topk);
 }
 
 // For many rows: one block per expert, no atomics and no scratch.  A warp owns a contiguous run of
@@ -812,11 +874,16 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
 // hidden [T, H] float (+= delta if given), x_out [T, H] of type `adtype` receives the normalised rows.
 // ndtype: type of the norm's weights.  Takes H % 4 == 0, H <= mi_moe_norm_route_small_max_width().
 int mi_moe_norm_route_small_max_width() { return 4 * NR_VMAX * 256; }
+// whether the launch below takes a router of E rows (one more with a shared-expert gate) of width H whose
+// weights have `wbytes` bytes an element: its blocks keep their rows in shared memory
+int mi_moe_norm_route_small_takes(int H, int E, int gated, int wbytes) {
+    return H > 0 && H % 4 == 0 && H <= mi_moe_norm_route_small_max_width() && E > 0 &&
+           norm_route_small_smem(H, E, E + (gated ? 1 : 0), (size_t)wbytes) <= 200 * 1024;
+}
 
 int mi_moe_norm_route_small(float* hidden, const float* delta, const void* norm_w, int ndtype, float eps,
-                            void* x_out, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
-                            unsigned* tickets, int* topk_idx, float* topk_w, float* gate, float* probs_out,
-                            int* offsets, int* sorted_token, int* inv_perm, int T, int H, int E, int K,
+                            void* x_out, int adtype, const void* wr, const void* wsg, int wdtype,
+                            int* topk_idx, float* topk_w, float* gate, float* probs_out, int T, int H, int E, int K,
                             int norm_topk, cudaStream_t stream) {
     if (T <= 0) return kOk;
     if (T > mi_moe_route_small_max_tokens()) {
@@ -834,21 +901,33 @@ int mi_moe_norm_route_small(float* hidden, const float* delta, const void* norm_
                        H, mi_moe_norm_route_small_max_width());
         return kBadShape;
     }
-    const size_t smem = sizeof(float) * (size_t)E + sizeof(int) * ((size_t)E + 1 + (size_t)T * K);
-    if (smem > 160 * 1024 || E + 1 > 65535) {
-        set_last_error("router (decode): %d experts exceed the shared memory of a block", E);
+    const int ncols = E + (wsg ? 1 : 0);
+    const size_t smem = norm_route_small_smem(H, E, ncols, wdtype == 1 ? 2 : 4);
+    if (smem > 200 * 1024) {
+        set_last_error("router with norm: %d experts of width %d exceed the shared memory of a block (%zu bytes); "
+                       "ask mi_moe_norm_route_small_takes first", E, H, smem);
         return kBadShape;
     }
-    const int ncols = E + (wsg ? 1 : 0);
-    const dim3 grid(ncols, T);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(NR_CLUSTER, T);
+    lc.blockDim = dim3(256);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = NR_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
 #define MI_NR_LAUNCH(AT, WT, NT)                                                                                 \
     do {                                                                                                         \
         if (smem > 48 * 1024)                                                                                    \
             cudaFuncSetAttribute(moe_norm_route_small_kernel<AT, WT, NT>,                                        \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
-        moe_norm_route_small_kernel<AT, WT, NT><<<grid, 256, smem, stream>>>(                                    \
-            hidden, delta, (const NT*)norm_w, eps, (AT*)x_out, (const WT*)wr, (const WT*)wsg, z_scratch,         \
-            tickets, topk_idx, topk_w, gate, probs_out, offsets, sorted_token, inv_perm, T, H, E, K, norm_topk); \
+        (void)cudaLaunchKernelEx(&lc, moe_norm_route_small_kernel<AT, WT, NT>, hidden, delta,             \
+                                 (const NT*)norm_w, eps, (AT*)x_out, (const WT*)wr, (const WT*)wsg,              \
+                                 topk_idx, topk_w, gate, probs_out, T, H, E, K, norm_topk);                      \
     } while (0)
     const int combo = adtype * 4 + wdtype * 2 + ndtype;
     if (adtype < 0 || adtype > 1 || wdtype < 0 || wdtype > 1 || ndtype < 0 || ndtype > 1) {

@@ -533,17 +533,21 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
     return idx, w, gate, probs, offsets, sorted_token, inv_perm
 
 
-def norm_route_small_takes(hidden_size: int) -> bool:
-    return hidden_size % 4 == 0 and hidden_size <= int(library().mi_moe_norm_route_small_max_width())
+def norm_route_small_takes(hidden_size: int, num_experts: int = 1, gated: bool = False,
+                           weight_dtype: torch.dtype = torch.bfloat16) -> bool:
+    """Whether :func:`moe_norm_route_small` takes a router of these sizes (its blocks keep their share of the
+    router's rows in shared memory)."""
+    return bool(library().mi_moe_norm_route_small_takes(int(hidden_size), int(num_experts), int(bool(gated)),
+                                                        2 if weight_dtype == torch.bfloat16 else 4))
 
 
 def moe_norm_route_small(hidden: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                          out_dtype: torch.dtype, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor],
-                         top_k: int, norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False,
-                         permute: bool = False):
-    """:func:`add_rmsnorm` and :func:`moe_route_small` of a step of a few tokens in one launch:
+                         top_k: int, norm_topk: bool, ticket: Optional[torch.Tensor] = None, want_probs: bool = False):
+    """:func:`add_rmsnorm` and the routing of a step of a few tokens in one launch (a cluster of blocks per token):
     ``hidden += delta``, the normalised rows ``x`` (of ``out_dtype``) and the routing computed from
-    them.  Returns ``(x, idx, w, gate, probs, offsets, sorted_token, inv_perm)``."""
+    them.  Returns ``(x, idx, w, gate, probs, None, None, None)`` (the places of a permutation, which this
+    form does not build).  ``ticket`` is not used (kept for callers of the form that counted its blocks)."""
     _chk(hidden, "moe_norm_route_small hidden", F32)
     T, H = hidden.shape
     _chk(delta, "moe_norm_route_small delta", F32, (T, H))
@@ -554,28 +558,18 @@ def moe_norm_route_small(hidden: torch.Tensor, delta: Optional[torch.Tensor], no
         _chk(shared_gate_w, "moe_norm_route_small shared gate", router_w.dtype)
         if shared_gate_w.numel() != H:
             raise ValueError("moe_norm_route_small: the shared-expert gate must have hidden_size entries")
-    _chk(ticket, "moe_norm_route_small ticket", I32)
-    if ticket.numel() < 1 + T:
-        raise ValueError(f"moe_norm_route_small: {ticket.numel()} ticket counters for {T} tokens (1 + T wanted)")
     dev = hidden.device
     x = torch.empty(T, H, dtype=out_dtype, device=dev)
     idx = torch.empty(T, top_k, dtype=I32, device=dev)
     w = torch.empty(T, top_k, dtype=F32, device=dev)
     gate = torch.empty(T, dtype=F32, device=dev) if shared_gate_w is not None else None
     probs = torch.empty(T, E, dtype=F32, device=dev) if want_probs else None
-    z = torch.empty(T, E + 1, dtype=F32, device=dev)
-    offsets = sorted_token = inv_perm = None
-    if permute:
-        offsets = torch.empty(E + 1, dtype=I32, device=dev)
-        sorted_token = torch.empty(T * top_k, dtype=I32, device=dev)
-        inv_perm = torch.empty(T * top_k, dtype=I32, device=dev)
     check(library().mi_moe_norm_route_small(
         _ptr(hidden), _ptr(delta), _ptr(norm_weight), _code(norm_weight, "moe_norm_route_small norm weight"),
         float(eps), _ptr(x), _code(x, "moe_norm_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
-        _code(router_w, "moe_norm_route_small weight"), _ptr(z), _ptr(ticket), _ptr(idx), _ptr(w), _ptr(gate),
-        _ptr(probs), _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), int(bool(norm_topk)),
-        _stream()), "moe_norm_route_small")
-    return x, idx, w, gate, probs, offsets, sorted_token, inv_perm
+        _code(router_w, "moe_norm_route_small weight"), _ptr(idx), _ptr(w), _ptr(gate),
+        _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _stream()), "moe_norm_route_small")
+    return x, idx, w, gate, probs, None, None, None
 
 
 def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,

@@ -35,7 +35,7 @@ _SIGNATURES = {
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
     "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],
     "mi_moe_route_small": [P, I, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
-    "mi_moe_norm_route_small": [P, P, P, I, F, P, I, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "mi_moe_norm_route_small": [P, P, P, I, F, P, I, P, P, I, P, P, P, P, I, I, I, I, I, P],
     "mi_grouped_gemm_skinny_pairs": [P, P, P, P, I, I, I, I, I, I, P],
     "mi_qkv_skinny": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "mi_dense_skinny": [P, P, P, P, I, I, I, I, P],
@@ -81,6 +81,8 @@ def library() -> ctypes.CDLL:
     lib.mi_moe_route_small_max_tokens.restype = c_int
     lib.mi_moe_norm_route_small_max_width.argtypes = []
     lib.mi_moe_norm_route_small_max_width.restype = c_int
+    lib.mi_moe_norm_route_small_takes.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mi_moe_norm_route_small_takes.restype = c_int
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.argtypes = []
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.restype = c_int
     lib.mi_attn_prefill_tc_supported.argtypes = [I, I]

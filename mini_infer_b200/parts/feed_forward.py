@@ -180,7 +180,7 @@ class SparseMoE(FeedForward):
             # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
             ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
         if (rms is not None and self._skinny and T <= min(self._pairs_max, TUNING.shared_expert_fork_after_routing_max_tokens)
-                and T * self.K <= TUNING.expert_skinny_rows_per_expert * self.E and F.norm_route_small_takes(self.H)
+                and T * self.K <= TUNING.expert_skinny_rows_per_expert * self.E and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
                 and (delta is None or isinstance(delta, torch.Tensor))):
             x, idx, w, gate, probs, _, _, _ = F.moe_norm_route_small(
                 hidden, delta, rms[0], rms[1], self.rt.act, self.w_router, self.w_shared_gate, self.K,

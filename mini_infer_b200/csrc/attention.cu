@@ -240,6 +240,7 @@ attn_decode_split_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cach
                          float* __restrict__ part_ml, int nh, int nkv, int page_size, int max_pages,
                          int max_splits, int window, float scale) {
     constexpr int E = D / 8;  // elements per thread
+    wait_for_earlier_kernels();
     const int b = blockIdx.z, h = blockIdx.y, sp = blockIdx.x;
     const int kvl = kv_len[b];
     const int pos = kvl - 1;
@@ -353,6 +354,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
                                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
                                          AT* __restrict__ out, int nh, int max_splits, int window) {
     __shared__ float sm_w[MERGE_CAP], sm_l[MERGE_CAP], sm_red[4];
+    wait_for_earlier_kernels();
     const int b = blockIdx.y, h = blockIdx.x;
     const int kvl = kv_len[b];
     const int pos = kvl - 1;
@@ -502,10 +504,10 @@ int mi_attn_decode_split(const void* q, const void* k_cache, const void* v_cache
     const dim3 mgrid(nh, B);
 #define MI_DEC(DD, SS)                                                                                    \
     do {                                                                                                  \
-        attn_decode_split_kernel<AT, DD, SS><<<grid, 128, 0, stream>>>(                                   \
+        launch_dependent(attn_decode_split_kernel<AT, DD, SS>, grid, dim3(128), 0, stream,                \
             (const AT*)q, (const AT*)k_cache, (const AT*)v_cache, block_table, q_start, kv_len, part_o,  \
             part_ml, nh, nkv, page_size, max_pages, max_splits, window, scale);                           \
-        attn_decode_merge_kernel<AT, DD, SS><<<mgrid, DD <= 128 ? DD : 128, 0, stream>>>(                \
+        launch_dependent(attn_decode_merge_kernel<AT, DD, SS>, mgrid, dim3(DD <= 128 ? DD : 128), 0, stream, \
             part_o, part_ml, q_start, kv_len, (AT*)out, nh, max_splits, window);                          \
     } while (0)
 #define MI_DEC_D(SS) do { if (d == 64) MI_DEC(64, SS); else if (d == 128) MI_DEC(128, SS); else MI_DEC(256, SS); } while (0)

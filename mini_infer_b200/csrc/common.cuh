@@ -78,6 +78,37 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return r;
 }
 
+// Programmatic dependent launch: a kernel launched through launch_dependent() may be placed on the SMs
+// while the kernel before it in the stream is still running, so that its launch latency and the part of
+// its prologue that reads nothing an earlier kernel wrote (index arithmetic, barrier set-up) overlap that
+// kernel's tail.  Such a kernel calls wait_for_earlier_kernels() in every thread before its first read
+// or write of memory that another kernel of the step touches, and before any return: the call returns
+// once the kernel before it has completed and its writes are visible (and, since that kernel made the
+// same call, so have all earlier ones).  Without the launch attribute the call returns at once.
+__device__ __forceinline__ void wait_for_earlier_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel's blocks be placed from now on instead of from this block's exit (for kernels of
+// at most one wave of blocks: a waiting block holds its SM's registers and shared memory).
+__device__ __forceinline__ void allow_next_kernel() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Whether launch_dependent() sets the attribute (mi_set_dependent_launch; off by default).
+bool dependent_launch_enabled();
+
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    A... args) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = dependent_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, kernel, static_cast<P>(args)...);
+}
+
 void set_last_error(const char* fmt, ...);
 
 // Checks cudaGetLastError after a launcher queued `n_kernels` kernels and counts them.

@@ -31,6 +31,9 @@ void set_last_error(const char* fmt, ...) {
 }
 
 static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_dependent_launch{0};
+
+bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_relaxed) != 0; }
 
 int finish_launch(const char* what, int n_kernels) {
     cudaError_t e = cudaGetLastError();
@@ -48,6 +51,7 @@ int finish_launch(const char* what, int n_kernels) {
 template <typename WT>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
                                     float* __restrict__ hidden, int H, int V) {
+    wait_for_earlier_kernels();
     const int t = blockIdx.x;
     int id = ids[t];
     // ids are validated on the host; clamp so that a bad id can never read outside the table
@@ -99,6 +103,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ hidden, const float* __restrict__ del
                        const int* __restrict__ rows, const WT* __restrict__ weight,
                        AT* __restrict__ out, int H, float eps) {
     __shared__ float scratch[32];
+    wait_for_earlier_kernels();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float4* h = reinterpret_cast<float4*>(hidden + (int64_t)src * H);
@@ -474,6 +479,7 @@ __global__ void __launch_bounds__(256)
 combine_add_rmsnorm_vec_kernel(float* __restrict__ hidden, CombineArgs ca, const int* __restrict__ rows,
                                const WT* __restrict__ weight, AT* __restrict__ out, int H, float eps) {
     __shared__ float scratch[32];
+    wait_for_earlier_kernels();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float4* h = reinterpret_cast<float4*>(hidden + (int64_t)src * H);
@@ -548,11 +554,15 @@ const char* mi_last_error() { return g_last_error; }
 // Kernels of this library queued since it was loaded (all threads).
 long long mi_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+// Switches programmatic dependent launch on (1) or off (0) for the kernels of decode-sized steps that
+// are written for it (see common.cuh); returns the setting before.
+int mi_set_dependent_launch(int on) { return g_dependent_launch.exchange(on ? 1 : 0, std::memory_order_relaxed); }
+
 int mi_embed_gather(const int* ids, const void* table, int wdtype, float* hidden, int T, int H, int V,
                     cudaStream_t stream) {
     if (T <= 0) return kOk;
     MI_DISPATCH_1(wdtype, WT,
-        embed_gather_kernel<WT><<<T, 256, 0, stream>>>(ids, (const WT*)table, hidden, H, V));
+        launch_dependent(embed_gather_kernel<WT>, dim3(T), dim3(256), 0, stream, ids, (const WT*)table, hidden, H, V));
     return finish_launch("embed_gather");
 }
 
@@ -564,16 +574,16 @@ int mi_add_rmsnorm(float* hidden, const float* delta, const int* rows, const voi
     if (H % 4 == 0 && H >= 1024 && H <= 8192 && aligned) {
         if (H <= 2048) {
             MI_DISPATCH_2(adtype, AT, wdtype, WT,
-                add_rmsnorm_vec_kernel<AT, WT, 2><<<n_rows, 256, 0, stream>>>(
-                    hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+                launch_dependent(add_rmsnorm_vec_kernel<AT, WT, 2>, dim3(n_rows), dim3(256), 0, stream,
+                                 hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
         } else if (H <= 4096) {
             MI_DISPATCH_2(adtype, AT, wdtype, WT,
-                add_rmsnorm_vec_kernel<AT, WT, 4><<<n_rows, 256, 0, stream>>>(
-                    hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+                launch_dependent(add_rmsnorm_vec_kernel<AT, WT, 4>, dim3(n_rows), dim3(256), 0, stream,
+                                 hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
         } else {
             MI_DISPATCH_2(adtype, AT, wdtype, WT,
-                add_rmsnorm_vec_kernel<AT, WT, 8><<<n_rows, 256, 0, stream>>>(
-                    hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
+                launch_dependent(add_rmsnorm_vec_kernel<AT, WT, 8>, dim3(n_rows), dim3(256), 0, stream,
+                                 hidden, delta, rows, (const WT*)weight, (AT*)out, H, eps));
         }
         return finish_launch("add_rmsnorm");
     }
@@ -596,16 +606,16 @@ int mi_combine_add_rmsnorm(float* hidden, const float* y, const int* inv_perm, c
     if (H % 4 == 0 && H >= 1024 && H <= 8192 && aligned) {
         if (H <= 2048) {
             MI_DISPATCH_2(adtype, AT, wdtype, WT,
-                combine_add_rmsnorm_vec_kernel<AT, WT, 2><<<n_rows, 256, 0, stream>>>(
-                    hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+                launch_dependent(combine_add_rmsnorm_vec_kernel<AT, WT, 2>, dim3(n_rows), dim3(256), 0, stream,
+                                 hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
         } else if (H <= 4096) {
             MI_DISPATCH_2(adtype, AT, wdtype, WT,
-                combine_add_rmsnorm_vec_kernel<AT, WT, 4><<<n_rows, 256, 0, stream>>>(
-                    hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+                launch_dependent(combine_add_rmsnorm_vec_kernel<AT, WT, 4>, dim3(n_rows), dim3(256), 0, stream,
+                                 hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
         } else {
             MI_DISPATCH_2(adtype, AT, wdtype, WT,
-                combine_add_rmsnorm_vec_kernel<AT, WT, 8><<<n_rows, 256, 0, stream>>>(
-                    hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
+                launch_dependent(combine_add_rmsnorm_vec_kernel<AT, WT, 8>, dim3(n_rows), dim3(256), 0, stream,
+                                 hidden, ca, rows, (const WT*)weight, (AT*)out, H, eps));
         }
         return finish_launch("combine_add_rmsnorm");
     }

@@ -553,6 +553,7 @@ moe_norm_route_small_kernel(float* __restrict__ hidden, const float* __restrict_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nv = H >> 2;
     const int r0 = min(ncols, rank * rows), r1 = min(ncols, r0 + rows);
+    wait_for_earlier_kernels();
     // first half of a barrier that is completed before the first write into another block's shared memory:
     // that block has to have started by then
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
@@ -913,13 +914,15 @@ int mi_moe_norm_route_small(float* hidden, const float* delta, const void* norm_
     lc.blockDim = dim3(256);
     lc.dynamicSmemBytes = smem;
     lc.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = NR_CLUSTER;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
-    lc.numAttrs = 1;
+    lc.numAttrs = dependent_launch_enabled() ? 2 : 1;
 #define MI_NR_LAUNCH(AT, WT, NT)                                                                                 \
     do {                                                                                                         \
         if (smem > 48 * 1024)                                                                                    \

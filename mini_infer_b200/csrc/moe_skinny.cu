@@ -260,6 +260,7 @@ template <int MODE, int NT>
 __global__ void __launch_bounds__(256)
 dense_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                     const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
+    wait_for_earlier_kernels();
     splitk_tile<MODE, NT>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
 }
 
@@ -270,6 +271,7 @@ template <int MODE, int NT>
 __global__ void __launch_bounds__(1024)
 dense_skinny_wide_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                          const float* __restrict__ bias, void* __restrict__ C, int rows, int Nout, int Kd) {
+    wait_for_earlier_kernels();
     splitk_tile<MODE, NT, 32>(A, nullptr, nullptr, W, bias, C, rows, blockIdx.x * 16, Nout, Kd);
 }
 
@@ -288,6 +290,7 @@ grouped_gemm_skinny_pairs_splitk_kernel(const __nv_bfloat16* __restrict__ A, con
                                         int K, int src_is_token, int Nout, int Kd) {
     __shared__ int pair_sh[8], from_sh[8];
     __shared__ int cnt_sh, e_sh;
+    wait_for_earlier_kernels();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp == 0) {
         // the blockIdx.y-th distinct expert
@@ -345,6 +348,7 @@ qkv_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __re
                   __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
                   __nv_bfloat16* __restrict__ v_cache, int rows, int Kd, int nh, int nkv, int d, int page_size) {
     __shared__ float red[8][NT * 4][32];
+    wait_for_earlier_kernels();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int head = blockIdx.y, half = d >> 1;
     const int p0 = blockIdx.x * 8;
@@ -474,7 +478,7 @@ int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void*
         const bool compact = 4 * T * K <= E;
         const dim3 sgrid((Nout + 15) / 16, compact ? T * K : E);
 #define MI_PAIRS_SPLITK(MODE, COMPACT)                                                                   \
-    grouped_gemm_skinny_pairs_splitk_kernel<MODE, COMPACT><<<sgrid, 256, 0, stream>>>(                   \
+    launch_dependent(grouped_gemm_skinny_pairs_splitk_kernel<MODE, COMPACT>, sgrid, dim3(256), 0, stream, \
         (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, MODE, Nout, Kd)
         if (mode == 1) { if (compact) MI_PAIRS_SPLITK(1, true); else MI_PAIRS_SPLITK(1, false); }
         else { if (compact) MI_PAIRS_SPLITK(0, true); else MI_PAIRS_SPLITK(0, false); }
@@ -523,14 +527,14 @@ int mi_dense_skinny(const void* A, const void* W, const float* bias, void* C, in
     // go in two launches: the partial sums of 32 rows x 32 warps would not fit the static shared memory)
     if (mode == 0 && (int)grid.x <= num_sms && Kd >= 1024) {
         float* c = (float*)C;
-        if (rows <= 8) dense_skinny_wide_kernel<0, 1><<<grid, 1024, 0, stream>>>(a, w, bias, c, rows, Nout, Kd);
-        else dense_skinny_wide_kernel<0, 2><<<grid, 1024, 0, stream>>>(a, w, bias, c, rows < 16 ? rows : 16, Nout, Kd);
+        if (rows <= 8) launch_dependent(dense_skinny_wide_kernel<0, 1>, grid, dim3(1024), 0, stream, a, w, bias, c, rows, Nout, Kd);
+        else launch_dependent(dense_skinny_wide_kernel<0, 2>, grid, dim3(1024), 0, stream, a, w, bias, c, rows < 16 ? rows : 16, Nout, Kd);
         if (rows > 16)
-            dense_skinny_wide_kernel<0, 2><<<grid, 1024, 0, stream>>>(a + (int64_t)16 * Kd, w, bias,
-                                                                      c + (int64_t)16 * Nout, rows - 16, Nout, Kd);
+            launch_dependent(dense_skinny_wide_kernel<0, 2>, grid, dim3(1024), 0, stream, a + (int64_t)16 * Kd, w, bias,
+                             c + (int64_t)16 * Nout, rows - 16, Nout, Kd);
         return finish_launch("dense_skinny", rows > 16 ? 2 : 1);
     }
-#define MI_DENSE_SKINNY(MODE, NT) dense_skinny_kernel<MODE, NT><<<grid, block, 0, stream>>>(a, w, bias, C, rows, Nout, Kd)
+#define MI_DENSE_SKINNY(MODE, NT) launch_dependent(dense_skinny_kernel<MODE, NT>, grid, block, 0, stream, a, w, bias, C, rows, Nout, Kd)
     if (mode == 1) {
         if (rows <= 8) MI_DENSE_SKINNY(1, 1);
         else if (rows <= 16) MI_DENSE_SKINNY(1, 2);
@@ -571,7 +575,7 @@ int mi_qkv_skinny(const void* A, const void* W, const float* bias, const int* po
     }
     const dim3 grid(d / 16, nh + 2 * nkv), block(256);
 #define MI_QKV_SKINNY(NT)                                                                                  \
-    qkv_skinny_kernel<NT><<<grid, block, 0, stream>>>(                                                     \
+    launch_dependent(qkv_skinny_kernel<NT>, grid, block, 0, stream,                                        \
         (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, positions, inv_freq, slot_mapping,         \
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, rows, Kd, nh, nkv, d, page_size)
     if (rows <= 8) MI_QKV_SKINNY(1);

@@ -56,6 +56,7 @@ sample_rows_kernel(const float* __restrict__ logits, const float* __restrict__ t
     __shared__ ArgBest ascratch[32];
     __shared__ float chunk_sum[SAMP_THREADS];
     __shared__ int chosen;
+    wait_for_earlier_kernels();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (int64_t)r * V;
     const float T = temperature ? temperature[r] : 0.f;
@@ -161,7 +162,7 @@ int mi_sample_rows(const float* logits, const float* temperature, const float* t
         set_last_error("sample_rows: temperature sampling needs the uniforms and a scratch row per request");
         return kBadShape;
     }
-    sample_rows_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, temperature, top_p, u, probs, out, V);
+    launch_dependent(sample_rows_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, temperature, top_p, u, probs, out, V);
     return finish_launch("sample_rows");
 }
 

@@ -15,6 +15,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..cache.manager import plan_groups
+from ..ops import functional as F
 from ..config.registry import part_class
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
 from ..parts.base import (BuiltLayer, CacheBinding, PagedCacheNeed, Part, Runtime, StateNeed, StepContext,
@@ -154,6 +155,12 @@ class Model:
     def forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run all tokens of ``ctx``; return float32 logits ``[R, V]`` for ``logit_rows`` (int32
         token indices), or None when no logits are wanted (the cache is still written)."""
+        if ctx.dependent_launch:
+            with F.dependent_launch(True):
+                return self._forward(ctx, logit_rows)
+        return self._forward(ctx, logit_rows)
+
+    def _forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         hidden = self.embedding.forward(ctx.token_ids)
         pending = None
         schedule = self.spec.schedule

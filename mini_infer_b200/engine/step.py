@@ -326,6 +326,7 @@ class ModelRunner:
         from ..parts.tuning import TUNING
         if self.rt.act == torch.bfloat16 and T <= TUNING.l2_prefetch_max_tokens:
             ctx.prefetch = self._prefetcher
+        ctx.dependent_launch = self.rt.act == torch.bfloat16 and T <= TUNING.dependent_launch_max_tokens
         logit_rows = d("logit_rows", R) if R else None
         return ctx, logit_rows, index
 

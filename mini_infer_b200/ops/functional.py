@@ -610,6 +610,23 @@ def l2_prefetch(t: torch.Tensor, max_bytes: Optional[int] = None) -> None:
     check(library().mi_l2_prefetch(_ptr(t), n, _stream()), "l2_prefetch")
 
 
+class dependent_launch:
+    """``with dependent_launch(True):`` the kernels of decode-sized steps that are written for it (they wait
+    for the kernels before them at their first line) are launched so that the device may place their blocks
+    while the kernel before them in the stream is still running; a pass captured under it replays so."""
+
+    def __init__(self, on: bool):
+        self.on = bool(on)
+
+    def __enter__(self):
+        self.before = library().mi_set_dependent_launch(int(self.on))
+        return self
+
+    def __exit__(self, *exc):
+        library().mi_set_dependent_launch(self.before)
+        return False
+
+
 def dense_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` in true float32 (``x [T, K]``, ``w [N, K]``): every output element is one chain of
     fused multiply-adds over ``k`` in ascending order, so a row's result does not depend on how many rows

@@ -81,6 +81,8 @@ def library() -> ctypes.CDLL:
     lib.mi_moe_route_small_max_tokens.restype = c_int
     lib.mi_moe_norm_route_small_max_width.argtypes = []
     lib.mi_moe_norm_route_small_max_width.restype = c_int
+    lib.mi_set_dependent_launch.argtypes = [c_int]
+    lib.mi_set_dependent_launch.restype = c_int
     lib.mi_moe_norm_route_small_takes.argtypes = [c_int, c_int, c_int, c_int]
     lib.mi_moe_norm_route_small_takes.restype = c_int
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.argtypes = []

@@ -180,6 +180,8 @@ class StepContext:
     # that a layer's last part can call ``ctx.prefetch(ctx.prefetch_upcoming)`` while its own tail runs.
     prefetch: Optional[Any] = None
     prefetch_upcoming: Optional[Any] = None
+    # launch this step's decode-sized kernels as programmatic dependents of the kernels before them
+    dependent_launch: bool = False
     # host copies, for parts written in plain PyTorch (tests' toy parts)
     host_q_start: Sequence[int] = ()
     host_kv_len: Sequence[int] = ()

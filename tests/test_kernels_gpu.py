@@ -918,3 +918,46 @@ def test_debug_bounds_mode_names_the_bad_index(monkeypatch):
     with pytest.raises(KernelError, match="1 splits of 512 keys cannot hold"):
         f.decode_attention(dec["q"], dec["kc"], dec["vc"], dec["table"], dec["q_start"], dec["kv_len"], po, pml, 1)
     assert f.debug_checks_run > 0
+
+
+def test_dependent_launch_gives_the_same_bits():
+    """A chain of decode-sized kernels launched as programmatic dependents of one another (each waits for
+    the kernels before it at its first line), eagerly and replayed from a CUDA graph, against the same
+    chain launched plainly."""
+    T, H, N = 5, 1024, 640
+    hidden0 = rnd(T, H, seed=1)
+    delta = rnd(T, H, seed=2)
+    nw = (1.0 + 0.1 * rnd(H, seed=3)).to(torch.bfloat16)
+    w1 = rnd(N, H, dtype=torch.bfloat16, scale=0.05, seed=4)
+    w2 = rnd(H, N, dtype=torch.bfloat16, scale=0.05, seed=5)
+
+    def chain(hidden):
+        x = F().add_rmsnorm(hidden, delta, nw, 1e-6, torch.bfloat16)
+        y = F().dense_skinny(x, w1, None, False)
+        z = F().dense_skinny(y.to(torch.bfloat16), w2, None, False)
+        x2 = F().add_rmsnorm(hidden, z, nw, 1e-6, torch.bfloat16)
+        return x2, F().sample_rows(F().dense_skinny(x2, w1, None, False))
+
+    h = hidden0.clone()
+    want_x, want_tok = chain(h)
+    want_h = h.clone()
+    with F().dependent_launch(True):
+        h = hidden0.clone()
+        got_x, got_tok = chain(h)
+        torch.cuda.synchronize()
+        assert torch.equal(got_x, want_x) and torch.equal(got_tok, want_tok) and torch.equal(h, want_h)
+        static_h = hidden0.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain(static_h)                                     # warm-up outside the capture
+            static_h.copy_(hidden0)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                gx, gt = chain(static_h)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            static_h.copy_(hidden0)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(gx, want_x) and torch.equal(gt, want_tok) and torch.equal(static_h, want_h)

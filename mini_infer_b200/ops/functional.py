@@ -543,11 +543,10 @@ def norm_route_small_takes(hidden_size: int, num_experts: int = 1, gated: bool =
 
 def moe_norm_route_small(hidden: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                          out_dtype: torch.dtype, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor],
-                         top_k: int, norm_topk: bool, ticket: Optional[torch.Tensor] = None, want_probs: bool = False):
+                         top_k: int, norm_topk: bool, want_probs: bool = False):
     """:func:`add_rmsnorm` and the routing of a step of a few tokens in one launch (a cluster of blocks per token):
     ``hidden += delta``, the normalised rows ``x`` (of ``out_dtype``) and the routing computed from
-    them.  Returns ``(x, idx, w, gate, probs, None, None, None)`` (the places of a permutation, which this
-    form does not build).  ``ticket`` is not used (kept for callers of the form that counted its blocks)."""
+    them.  Returns ``(x, idx, w, gate, probs)``."""
     _chk(hidden, "moe_norm_route_small hidden", F32)
     T, H = hidden.shape
     _chk(delta, "moe_norm_route_small delta", F32, (T, H))
@@ -569,7 +568,7 @@ def moe_norm_route_small(hidden: torch.Tensor, delta: Optional[torch.Tensor], no
         float(eps), _ptr(x), _code(x, "moe_norm_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
         _code(router_w, "moe_norm_route_small weight"), _ptr(idx), _ptr(w), _ptr(gate),
         _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _stream()), "moe_norm_route_small")
-    return x, idx, w, gate, probs, None, None, None
+    return x, idx, w, gate, probs
 
 
 def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,

@@ -182,9 +182,9 @@ class SparseMoE(FeedForward):
         if (rms is not None and self._skinny and T <= min(self._pairs_max, TUNING.shared_expert_fork_after_routing_max_tokens)
                 and T * self.K <= TUNING.expert_skinny_rows_per_expert * self.E and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
                 and (delta is None or isinstance(delta, torch.Tensor))):
-            x, idx, w, gate, probs, _, _, _ = F.moe_norm_route_small(
+            x, idx, w, gate, probs = F.moe_norm_route_small(
                 hidden, delta, rms[0], rms[1], self.rt.act, self.w_router, self.w_shared_gate, self.K,
-                self.norm_topk, self._route_ticket, want_probs=self.keep_routing)
+                self.norm_topk, want_probs=self.keep_routing)
             return self._run(x, ctx, (idx, w, gate, probs))
         return super().forward_from_residual(hidden, delta, norm, ctx)
 

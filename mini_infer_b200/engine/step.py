@@ -120,7 +120,8 @@ class ModelRunner:
         for g, n in zip(groups, pages):
             self.kv_tensors.append({name: torch.zeros((g.num_layers, n) + tuple(shape), dtype=dtype or act, device=dev)
                                     for name, shape, dtype in g.need.tensors(page_size)})
-        self.state_tensors = [torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype or torch.float32,
+        # (one slot more than requests: the rows that only fill a captured batch up write their state there)
+        self.state_tensors = [torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype or torch.float32,
                                           device=dev) for _, need in model.state_needs]
         self.scratch = {k: torch.empty(n, dtype=torch.float32, device=dev)
                         for k, n in model.scratch_need(max_requests, max_context).items()}
@@ -238,8 +239,11 @@ class ModelRunner:
         return arrays
 
     def prepare(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
-                ahead: bool = False) -> Tuple[StepContext, Optional[torch.Tensor], List]:
+                ahead: bool = False, pad_to: int = 0) -> Tuple[StepContext, Optional[torch.Tensor], List]:
         """Validate, reserve pages (all entries or none), stage and upload the metadata.
+
+        ``pad_to`` (decode steps that are replayed from a captured pass): the batch is filled up to this many
+        rows with rows of no request (see :meth:`_stage`).
 
         With ``device_tokens`` (int32, one per row, on the device) the token ids of ``entries`` are
         placeholders and the step reads the given ones; ``ahead`` reserves through
@@ -254,7 +258,7 @@ class ModelRunner:
                 starts.append(self.cache.reserve_ahead(e.rid, len(e.tokens)) if ahead
                               else self.cache.reserve(e.rid, len(e.tokens)))
                 done.append(e.rid)
-            staged = self._stage(entries, arrays, starts, device_tokens)
+            staged = self._stage(entries, arrays, starts, device_tokens, pad_to)
         except BaseException:
             for rid in done:
                 self.cache.cancel(rid)
@@ -262,12 +266,25 @@ class ModelRunner:
         self.host_prepare_seconds += time.perf_counter() - t_begin
         return staged
 
-    def _stage(self, entries, arrays, starts, device_tokens):
+    def _stage(self, entries, arrays, starts, device_tokens, pad_to=0):
         """Fill the pinned staging buffer (whole arrays at a time, no per-token work on the host) and
-        queue its one copy to the device."""
-        B = len(entries)
-        counts = np.fromiter((a.shape[0] for a in arrays), dtype=np.int64, count=B)
+        queue its one copy to the device.
+
+        With ``pad_to`` above the number of entries, rows of no request follow the entries' rows, one
+        token each: token 0 at position 0, written nowhere (slot -1), attending to the one key at the start
+        of page 0 (finite data whatever it is), state in the spare slot, logits wanted so that the shapes
+        are those of a full batch.  Every kernel works row by row, so the entries' results are what they
+        would be without them; the caller drops the extra rows of logits."""
+        B_real = len(entries)
+        extra = max(0, int(pad_to) - B_real)
+        B = B_real + extra
+        counts = np.fromiter((a.shape[0] for a in arrays), dtype=np.int64, count=B_real)
         starts_np = np.asarray(starts, dtype=np.int64)
+        T_real = int(counts.sum())
+        if extra:
+            counts = np.concatenate([counts, np.ones(extra, dtype=np.int64)])
+            starts_np = np.concatenate([starts_np, np.zeros(extra, dtype=np.int64)])
+            arrays = list(arrays) + [np.zeros(extra, dtype=np.int64)]
         T = int(counts.sum())
         self._copied.synchronize()      # the previous step's upload has left the pinned buffer
         h = self._hview_np
@@ -276,7 +293,9 @@ class ModelRunner:
         req_of_token = np.repeat(np.arange(B, dtype=np.int64), counts)
         positions = np.arange(T, dtype=np.int64) - first[req_of_token] + starts_np[req_of_token]
         kv_len = starts_np + counts
-        slots = np.fromiter((self.cache.slot_of(e.rid) for e in entries), dtype=np.int64, count=B)
+        slots = np.fromiter((self.cache.slot_of(e.rid) for e in entries), dtype=np.int64, count=B_real)
+        if extra:
+            slots = np.concatenate([slots, np.full(extra, self.max_requests, dtype=np.int64)])
         h("token_ids", T)[:] = np.concatenate(arrays)
         h("positions", T)[:] = positions
         h("req_of_token", T)[:] = req_of_token
@@ -290,6 +309,7 @@ class ModelRunner:
             for w in e.want:
                 row_l.append(int(first[b]) + int(w))
                 index.append((e.rid, int(w)))
+        row_l.extend(range(T_real, T))
         R = len(row_l)
         if R:
             h("logit_rows", R)[:] = row_l
@@ -300,17 +320,19 @@ class ModelRunner:
             for b, e in enumerate(entries):
                 table = self.cache.block_table(g, e.rid)
                 bt[b, :len(table)] = table
+            bt[B_real:, 0] = 0
             pages = bt[req_of_token, positions // ps]
-            if pages.size and int(pages.min()) < 0:
-                t = int(np.argmin(pages))
+            if pages.size and int(pages[:T_real].min()) < 0:
+                t = int(np.argmin(pages[:T_real]))
                 raise RuntimeError(f"step: position {int(positions[t])} of request {entries[int(req_of_token[t])].rid!r} "
                                    f"lies in a released page of cache group {g}")
             h(f"slot_mapping{g}", T)[:] = pages.astype(np.int64) * ps + positions % ps
+            h(f"slot_mapping{g}", T)[T_real:] = -1
         self._dev.copy_(self._host, non_blocking=True)
         self._copied.record()
         d = self._dview
         if device_tokens is not None:
-            d("token_ids", T).copy_(device_tokens[:T], non_blocking=True)
+            d("token_ids", T_real).copy_(device_tokens[:T_real], non_blocking=True)
         views = []
         for g in range(len(self.model.kv_groups)):
             views.append(KVGroupView(
@@ -323,6 +345,7 @@ class ModelRunner:
             kv_len=d("kv_len", B), req_of_token=d("req_of_token", T), state_slot=d("state_slot", B),
             fresh=d("fresh", B), kv_groups=views, states=self.state_tensors, scratch=self.scratch,
             host_q_start=first.tolist(), host_kv_len=kv_len.tolist(), host_state_slot=slots.tolist())
+        ctx.rows_of_no_request = extra
         from ..parts.tuning import TUNING
         if self.rt.act == torch.bfloat16 and T <= TUNING.l2_prefetch_max_tokens:
             ctx.prefetch = self._prefetcher
@@ -350,6 +373,13 @@ class ModelRunner:
         e = entries[0]
         n = len(e.tokens)
         return n == self.graph_chunk_tokens and list(e.want) in ([], [n - 1])
+
+    def _graph_batch(self, num_requests: int) -> int:
+        """The batch size whose captured pass a decode step of ``num_requests`` requests is replayed from:
+        the next size of the tuning's ladder, so that a batch that grows and shrinks by single requests does
+        not capture a pass per size."""
+        from ..parts.tuning import TUNING
+        return min(TUNING.decode_graph_batch(num_requests), self.max_requests, self.max_tokens)
 
     def _decode_with_graph(self, ctx: StepContext, logit_rows: Optional[torch.Tensor],
                            chunk: bool = False) -> Optional[torch.Tensor]:
@@ -399,11 +429,14 @@ class ModelRunner:
                 p.adopt_side_outputs(outputs)
         self.graph_replays += 1
         self.graph_kernel_launches += kernels
+        if out is not None and ctx.rows_of_no_request:
+            out = out[:out.shape[0] - ctx.rows_of_no_request]
         return out
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> StepResult:
-        ctx, logit_rows, index = self.prepare(entries)
+        decode_graph = self._graph_eligible(entries)
+        ctx, logit_rows, index = self.prepare(entries, pad_to=self._graph_batch(len(entries)) if decode_graph else 0)
         # What a failed step wrote into the paged caches lies beyond every request's committed tokens and
         # is written again; a per-request state is updated in place, so the entries' slots are kept aside
         # and put back if the forward pass fails.
@@ -412,7 +445,7 @@ class ModelRunner:
             slots = torch.as_tensor(ctx.host_state_slot, dtype=torch.long, device=self.rt.device)
             saved = (slots, [st.index_select(0, slots) for st in self.state_tensors])
         try:
-            if self._graph_eligible(entries):
+            if decode_graph:
                 logits = self._decode_with_graph(ctx, logit_rows)
             elif self._chunk_graph_eligible(entries):
                 logits = self._decode_with_graph(ctx, logit_rows, chunk=True)
@@ -431,7 +464,7 @@ class ModelRunner:
             raise
         for e in entries:
             self.cache.commit(e.rid)
-        return StepResult(logits, index, ctx.num_tokens)
+        return StepResult(logits, index, ctx.num_tokens - ctx.rows_of_no_request)
 
     # ------------------------------------------------------------------ #
     # a decode step launched ahead of the scheduler's decision
@@ -452,7 +485,8 @@ class ModelRunner:
         :meth:`adopt_ahead` or :meth:`drop_ahead`.  Raises :class:`OutOfPages` and changes nothing
         if a request cannot grow."""
         entries = [StepEntry(r, [0], [0]) for r in rids]
-        ctx, logit_rows, _ = self.prepare(entries, device_tokens=device_tokens, ahead=True)
+        ctx, logit_rows, _ = self.prepare(entries, device_tokens=device_tokens, ahead=True,
+                                          pad_to=self._graph_batch(len(entries)))
         try:
             return self._decode_with_graph(ctx, logit_rows)
         except Exception:

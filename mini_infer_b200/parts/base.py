@@ -182,6 +182,9 @@ class StepContext:
     prefetch_upcoming: Optional[Any] = None
     # launch this step's decode-sized kernels as programmatic dependents of the kernels before them
     dependent_launch: bool = False
+    # the last rows of the step (one token each) belong to no request: they fill a captured batch up to its
+    # size, are written nowhere and their logits are dropped
+    rows_of_no_request: int = 0
     # host copies, for parts written in plain PyTorch (tests' toy parts)
     host_q_start: Sequence[int] = ()
     host_kv_len: Sequence[int] = ()

@@ -74,3 +74,32 @@ def test_window_group_gives_pages_back_while_decoding(tmp_path):
     full = 1 - win
     assert runner.cache.pools[win].high_water <= (24 + 13) // 4 + 2          # window 24, portion 13, pages of 4
     assert runner.cache.pools[full].high_water == -(-150 // 4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_batches_filled_up_to_a_captured_size(tmp_path, dtype):
+    """Decode steps of 11, 9 and 5 requests: above 8 requests the step is filled up with rows of no request
+    to the next captured batch size (12 here), so 11 and 9 requests replay the same pass.  The rows of the
+    requests must be the plain model's, the filling rows must write nothing (pages, other requests' keys),
+    and in float32 the logits are bit for bit those of the same trace launched eagerly without any filling."""
+    cfg = tiny.CONFIGS["D"]
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=47, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    g = torch.Generator().manual_seed(9)
+    lens = [40, 33, 21, 30, 26, 35, 24, 22, 38, 20, 28]
+    tail = {f"r{i}": t for i, t in enumerate([12, 12, 6, 12, 6, 12, 3, 3, 12, 6, 6])}
+    reqs = {f"r{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate(lens)}
+    steps = traces.decoded_together(reqs, tail)
+    sizes = [len(st["entries"]) for st in steps[len(reqs):]]
+    assert sizes[0] == 11 and 9 in sizes and sizes[-1] == 5
+    kw = dict(page_size=16, num_pages=48, max_requests=12, max_tokens=64, max_context=128)
+    runner = make_runner(folder, dtype, **kw)
+    _, got = run_and_compare(runner, steps, cfg, w, reqs, dtype, 2e-5 if dtype == "float32" else 3e-2)
+    assert runner.graph_replays == len(sizes)
+    assert sorted({key[0] for key in runner._graphs}) == [5, 12]
+    assert runner.cache.used_pages() == [0]
+    if dtype == "float32":
+        eager = run_trace(make_runner(folder, dtype, cuda_graphs=False, **kw), steps)
+        assert set(eager) == set(got)
+        for key in got:
+            assert torch.equal(got[key], eager[key]), key

@@ -296,3 +296,27 @@ def test_state_mixer_inside_graph_replays_and_a_failed_step_leaves_no_trace(dtyp
         assert float((res.logits.float().cpu() - ref[3:5]).abs().max()) <= 3e-5 * float(ref.abs().max())
     runner.release("f")
     runner.cache.check_invariants()
+
+
+def test_rows_that_fill_a_captured_batch_keep_their_state_to_themselves():
+    """Ten requests decode together through the mixer with a state of its own: the step is filled up to the
+    captured size of 12 with rows of no request, whose state goes to the spare slot and nowhere else."""
+    from mini_infer_b200.config import PartSpec, build_model_spec
+    _register()
+    cfg = tiny.CONFIG_A
+    base = build_model_spec(cfg)
+    toy = base.layers[1].with_part("mixer", PartSpec(
+        "toy_graph_safe_state", {"hidden_size": cfg["hidden_size"], "state_size": 20, "decay": 0.8}))
+    spec = dataclasses.replace(base, layers=(base.layers[0], toy))
+    runner, weights = build(spec, "float32", max_requests=12, num_pages=80)
+    g = torch.Generator().manual_seed(3)
+    reqs = {f"s{i}": torch.randint(0, cfg["vocab_size"], (9 + i,), generator=g).tolist() for i in range(10)}
+    steps = traces.decoded_together(reqs, tail=5)
+    routing = {}
+    got = run_trace(runner, steps, routing)
+    assert runner.graph_replays == 5 and {key[0] for key in runner._graphs} == {12}
+    for rid, toks in reqs.items():
+        ref = plain(spec, weights, toks, cfg, routing.get(rid))
+        for pos in range(len(toks) - 6, len(toks)):
+            assert float((got[(rid, pos)] - ref[pos]).abs().max()) <= 3e-5 * float(ref.abs().max()), (rid, pos)
+    assert not bool(runner.state_tensors[0][12].eq(0).all())      # the spare slot took the filling rows' state

@@ -134,7 +134,8 @@ def test_toy_mixer_with_state_of_its_own(dtype):
         "toy_decaying_sum", {"hidden_size": cfg["hidden_size"], "state_size": 24, "decay": 0.9}))
     spec = dataclasses.replace(base, layers=(base.layers[0], toy_layer))
     runner, weights = build(spec, dtype)
-    assert len(runner.state_tensors) == 1 and runner.state_tensors[0].shape == (4, 24)
+    # (a slot per request and a spare one for the rows that fill a captured batch up)
+    assert len(runner.state_tensors) == 1 and runner.state_tensors[0].shape == (4 + 1, 24)
     assert [b["mixer"].kind for b in runner.model.bindings] == ["kv", "state"]
     g = torch.Generator().manual_seed(0)
     reqs = {f"t{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()

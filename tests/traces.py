@@ -29,6 +29,26 @@ def tail_decoded(requests: Dict[str, List[int]], tail: int = 32) -> List[dict]:
     return steps
 
 
+def decoded_together(requests: Dict[str, List[int]], tail) -> List[dict]:
+    """Every prompt whole in a step of its own (logits at its last place), then decode steps of all live
+    requests together, one token each; ``tail`` (a number, or one per request) is how many tokens of a
+    request are decoded, so requests with short tails leave on the way and the batch shrinks."""
+    tails = {rid: (tail[rid] if isinstance(tail, dict) else tail) for rid in requests}
+    steps = []
+    fed = {}
+    for rid, toks in requests.items():
+        n = max(1, len(toks) - tails[rid])
+        steps.append({"entries": [(rid, toks[:n], [n - 1])], "end": []})
+        fed[rid] = n
+    while any(fed[rid] < len(requests[rid]) for rid in requests):
+        live = [rid for rid in requests if fed[rid] < len(requests[rid])]
+        entries = [(rid, [requests[rid][fed[rid]]], [0]) for rid in live]
+        for rid in live:
+            fed[rid] += 1
+        steps.append({"entries": entries, "end": [rid for rid in live if fed[rid] == len(requests[rid])]})
+    return steps
+
+
 def portions(requests: Dict[str, List[int]], sizes: Sequence[int] = (7, 2, 13, 3, 2, 5, 17, 2, 31, 4)) -> List[dict]:
     """Each request alone, in portions of changing size, down to two tokens."""
     steps = []

@@ -149,6 +149,31 @@ def test_generation_as_the_product_runs_it_against_the_plain_model(tmp_path, nam
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_of_eleven_requests_on_batches_filled_up_to_a_captured_size(tmp_path, dtype):
+    """Eleven requests with different numbers of new tokens: the decode steps of 11, 10 and 9 requests are
+    replays of the pass captured for 12 (filled up with rows of no request), launched ahead of the host's
+    tokens as in serving; every row of logits a token was sampled from against the plain model."""
+    from engine_harness import GenerationObserver, compare_generation
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    cfg = tiny.CONFIGS["D"]
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=59, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    prompts = [tiny.pick_tokens(cfg, w, n, 5 * n) for n in (12, 31, 7, 22, 40, 9, 17, 28, 5, 35, 14)]
+    news = [10, 14, 10, 12, 14, 10, 14, 12, 14, 14, 14]
+    llm = LLM(folder, dtype=dtype, max_seq_len=128, max_running=12, max_tokens_per_step=256)
+    obs = GenerationObserver(llm.runner, [len(p) for p in prompts])
+    llm.executor.observer = obs
+    outs = llm.generate(prompts, [SamplingParams(greedy=True, max_new_tokens=n) for n in news])
+    assert [len(o.token_ids) for o in outs] == news
+    assert llm.executor.steps_adopted > 0 and 12 in {key[0] for key in llm.runner._graphs}
+    assert not {9, 10, 11} & {key[0] for key in llm.runner._graphs}
+    compare_generation(obs, llm._calls, prompts, outs, cfg, w, dtype, 2e-5 if dtype == "float32" else 2e-2)
+    assert llm.runner.cache.used_pages() == [0]
+    llm.runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_full_prompt_portions_are_graph_replays_too(tmp_path, dtype, monkeypatch):
     """With chunked prefill every full portion of a long prompt has the same shape; its pass is captured once
     and replayed with whatever context lies before it.  A prompt of 5 full portions and a rest, then decoding:

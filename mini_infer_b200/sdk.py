@@ -15,11 +15,12 @@ and the ``[mini-infer] N tokens in Xs`` line, and ``stream`` yields the program'
 output as it arrives.  ``stream`` of the in-process backend yields each token's
 text as soon as the scheduler's step that sampled it has ended.
 
-Not part of this engine: ``endpoint=`` (the HTTP backend), ``draft_path=``
-(speculative decoding), and the ``chat`` and ``batch`` helpers, which in the
-reference are conveniences over the same two backends
-(sdk/mini_infer_sdk/engine.py:100-112, chat.py, batch.py): they belong to the
-serving layer that this engine leaves out.
+``chat(system_prompt)`` gives a conversation that keeps its history and sends the whole of it as one raw
+prompt each turn, and ``batch()`` a helper that runs many prompts and reports totals
+(sdk/mini_infer_sdk/engine.py:100-112, chat.py, batch.py).  Here the batch is ONE continuous batch of the
+scheduler, not a loop of single calls, and its ``stream`` yields every result when its request ends.
+
+Not part of this engine: ``endpoint=`` (the HTTP backend) and ``draft_path=`` (speculative decoding).
 
 Token ids work everywhere a prompt does (``generate([1, 2, 3])``), because
 random-weight models have no tokenizer; ``generate_ids`` runs many prompts as
@@ -102,6 +103,126 @@ class GenerationResult:
 Prompt = Union[str, Sequence[int]]
 
 
+@dataclass
+class ChatMessage:
+    role: str
+    content: str
+
+
+class ChatSession:
+    """A conversation with its history (sdk/mini_infer_sdk/chat.py:17-72): ``send`` returns the assistant's
+    message, ``stream`` yields its text as it is produced; both append the turn to ``history``.  Every turn
+    sends the whole history as one raw prompt (``tokenizer.chat_prompt``), so it needs a tokenizer."""
+
+    def __init__(self, engine: "MiniInfer", system_prompt: Optional[str] = None,
+                 config: Optional[InferenceConfig] = None):
+        self._engine = engine
+        self._config = config or engine.config
+        self.history: List[ChatMessage] = []
+        if system_prompt:
+            self.history.append(ChatMessage("system", system_prompt))
+
+    def _prompt_ids(self):
+        return self._engine._encode_conversation([{"role": m.role, "content": m.content} for m in self.history])
+
+    def send(self, message: str) -> ChatMessage:
+        self.history.append(ChatMessage("user", message))
+        try:
+            ids, stop = self._prompt_ids()
+            result = self._engine._generate_encoded([(ids, stop)], self._config)[0]
+        except BaseException:
+            self.history.pop()
+            raise
+        self.last_result = result
+        self.history.append(ChatMessage("assistant", result.text))
+        return self.history[-1]
+
+    def stream(self, message: str) -> Iterator[str]:
+        self.history.append(ChatMessage("user", message))
+        pieces: List[str] = []
+        try:
+            ids, stop = self._prompt_ids()
+            for piece in self._engine._stream_encoded(ids, stop, self._config):
+                pieces.append(piece)
+                yield piece
+        finally:
+            # a consumer that walks away keeps what it has seen as the assistant's turn
+            self.history.append(ChatMessage("assistant", "".join(pieces)))
+
+    def clear(self) -> None:
+        self.history.clear()
+
+    def last_message(self) -> Optional[ChatMessage]:
+        return self.history[-1] if self.history else None
+
+    def __repr__(self):
+        return f"ChatSession(turns={sum(1 for m in self.history if m.role == 'user')})"
+
+
+@dataclass
+class BatchResult:
+    prompt: Prompt
+    result: GenerationResult
+    index: int
+
+
+@dataclass
+class BatchStats:
+    total_prompts: int
+    total_generated_tokens: int
+    total_elapsed: float
+    tokens_per_sec: float
+    results: List[BatchResult] = field(default_factory=list)
+
+
+class BatchInfer:
+    """Many prompts at once (sdk/mini_infer_sdk/batch.py:33-136 loops over single calls, in threads if asked).
+    With the engine in this process the prompts are one continuous batch of the scheduler, so ``workers`` has
+    nothing to add there; with the subprocess backend it is the number of programs run side by side."""
+
+    def __init__(self, engine: "MiniInfer", config: Optional[InferenceConfig] = None):
+        self._engine = engine
+        self._config = config or engine.config
+
+    def process(self, prompts: Sequence[Prompt], workers: int = 1) -> BatchStats:
+        t0 = time.perf_counter()
+        eng = self._engine
+        if eng.llm is None and workers > 1:
+            from concurrent.futures import ThreadPoolExecutor
+            with ThreadPoolExecutor(max_workers=workers) as pool:
+                results = list(pool.map(lambda p: eng.generate(p, self._config), prompts))
+        else:
+            results = eng.generate_ids(list(prompts), self._config)
+        elapsed = time.perf_counter() - t0
+        total = sum(r.generated_tokens for r in results)
+        return BatchStats(len(results), total, elapsed, total / elapsed if elapsed > 0 else 0.0,
+                          [BatchResult(p, r, i) for i, (p, r) in enumerate(zip(prompts, results))])
+
+    def stream(self, prompts: Sequence[Prompt]) -> Iterator[BatchResult]:
+        """Yield every prompt's result as soon as its request has ended (in that order, not the prompts')."""
+        eng, cfg = self._engine, self._config
+        if eng.llm is None:
+            for i, p in enumerate(prompts):
+                yield BatchResult(p, eng.generate(p, cfg), i)
+            return
+        enc = [eng._encode(p) for p in prompts]
+        t0 = time.perf_counter()
+        tokens = eng.llm.generate_iter([e[0] for e in enc], [eng._params(cfg, e[1]) for e in enc])
+        gen: List[List[int]] = [[] for _ in enc]
+        try:
+            for i, token in tokens:
+                gen[i].append(token)
+                stopped = token in enc[i][1]
+                if stopped or len(gen[i]) >= cfg.max_new_tokens:
+                    ids = enc[i][0]
+                    yield BatchResult(prompts[i], GenerationResult(
+                        text=eng.detokenize(gen[i]), tokens=list(ids) + gen[i], prompt_tokens=len(ids),
+                        generated_tokens=len(gen[i]), elapsed_sec=time.perf_counter() - t0,
+                        finish_reason="stop" if stopped else "length"), i)
+        finally:
+            tokens.close()
+
+
 class MiniInfer:
     def __init__(self, model_path: Optional[str] = None, draft_path: Optional[str] = None,
                  binary: Optional[str] = None, python_path: Optional[str] = None,
@@ -172,16 +293,35 @@ class MiniInfer:
             stop = [self.tokenizer.eos_token_id]
         return [int(t) for t in prompt], stop
 
+    def _encode_conversation(self, messages):
+        """The ids of a whole conversation up to the assistant's next turn, and the ids that end that turn."""
+        from .tokenizer import chat_prompt
+        tok = self.tokenizer
+        if tok is None:
+            raise RuntimeError("MiniInfer: a chat needs text, and this model folder has no tokenizer.json")
+        ids = tok.encode(chat_prompt(messages, tok.has_chat_tokens))
+        stop = [tok.im_end_id] if tok.has_chat_tokens else []
+        if tok.eos_token_id >= 0:
+            stop.append(tok.eos_token_id)
+        return ids, stop
+
     # -- core API ------------------------------------------------------------ #
     def generate(self, prompt: Prompt, config: Optional[InferenceConfig] = None) -> GenerationResult:
         return self.generate_ids([prompt], config)[0]
+
+    def chat(self, system_prompt: Optional[str] = None, config: Optional[InferenceConfig] = None) -> ChatSession:
+        return ChatSession(self, system_prompt=system_prompt, config=config)
+
+    def batch(self, config: Optional[InferenceConfig] = None) -> BatchInfer:
+        return BatchInfer(self, config=config or self.config)
 
     def generate_ids(self, prompts: Sequence[Prompt], config: Optional[InferenceConfig] = None
                      ) -> List[GenerationResult]:
         """Many prompts as one continuous batch (request ``i`` uses random stream ``i``); with the
         subprocess backend one program run per prompt."""
-        cfg = config or self.config
-        enc = [self._encode(p) for p in prompts]
+        return self._generate_encoded([self._encode(p) for p in prompts], config or self.config)
+
+    def _generate_encoded(self, enc, cfg: InferenceConfig) -> List[GenerationResult]:
         if self.llm is None:
             return [self._run_binary(ids, stop, cfg) for ids, stop in enc]
         t0 = time.perf_counter()
@@ -197,8 +337,10 @@ class MiniInfer:
     def stream(self, prompt: Prompt, config: Optional[InferenceConfig] = None) -> Iterator[str]:
         """Yield the text of the generated tokens as they are produced: from the in-process engine after
         every scheduler step, from the subprocess backend as the program prints it."""
-        cfg = config or self.config
         ids, stop = self._encode(prompt)
+        yield from self._stream_encoded(ids, stop, config or self.config)
+
+    def _stream_encoded(self, ids, stop, cfg: InferenceConfig) -> Iterator[str]:
         if self.llm is None:
             yield from self._stream_binary(ids, cfg)
             return

@@ -49,3 +49,15 @@ def load_tokenizer(model_dir: str) -> Optional[Tokenizer]:
 def chatml(prompt: str) -> str:
     """The single-turn wrap of src/core/main.cc:133-135."""
     return "<|im_start|>user\n" + prompt + "<|im_end|>\n<|im_start|>assistant\n"
+
+
+def chat_prompt(messages, chat_tokens: bool) -> str:
+    """A conversation (``[{"role": ..., "content": ...}]``) as one raw prompt that ends where the assistant's
+    next turn begins: ChatML turns when the vocabulary has the turn markers, plain ``Role: text`` lines
+    otherwise (the two forms of sdk/mini_infer_sdk/backends/local.py:50-69)."""
+    if chat_tokens:
+        turns = [f"<|im_start|>{m['role']}\n{m['content']}<|im_end|>" for m in messages]
+        return "\n".join(turns + ["<|im_start|>assistant\n"])
+    names = {"system": "System", "assistant": "Assistant"}
+    lines = [f"{names.get(m['role'], 'User')}: {m['content']}" for m in messages]
+    return "\n".join(lines + ["Assistant: "])

@@ -256,6 +256,85 @@ def test_sdk_streams_tokens_as_the_scheduler_produces_them(folders):
     assert eng.generate(toks).generated_ids == gen                        # and the engine is as before
 
 
+def _folder_with_tokenizer(tmp_path, cfg):
+    """A random-weight folder with a word-level ``tokenizer.json`` made for the test: one word per id
+    (``t0``, ``t1`` ...), the two ChatML markers as special tokens, whitespace splitting."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=61, dtype=torch.float32)
+    V = cfg["vocab_size"]
+    vocab = {"<unk>": 0, "<|im_start|>": 1, "<|im_end|>": 2, "user": 3, "assistant": 4, "system": 5}
+    for i in range(len(vocab), V):
+        vocab[f"t{i}"] = i
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.add_special_tokens(["<|im_start|>", "<|im_end|>"])
+    tok.save(os.path.join(folder, "tokenizer.json"))
+    return folder, tiny.read_weights(folder)
+
+
+def test_sdk_text_prompts_chat_and_batch(tmp_path):
+    """Text goes through the folder's tokenizer: a single prompt is wrapped as one ChatML turn, a chat sends
+    its whole history as one raw prompt each turn and stops at the end-of-turn marker, and a batch is one
+    continuous batch whose results equal the single calls'.  Every token against the plain model."""
+    from mini_infer_sdk import InferenceConfig, MiniInfer
+    from mini_infer_b200.tokenizer import chat_prompt, chatml
+    cfg = tiny.CONFIGS["A"]
+    folder, w = _folder_with_tokenizer(tmp_path, cfg)
+    eng = MiniInfer(model_path=folder, config=InferenceConfig(max_new_tokens=5, max_seq_len=256, dtype="float32",
+                                                              max_running=4))
+    tok = eng.tokenizer
+    assert tok.has_chat_tokens and tok.im_start_id == 1 and tok.im_end_id == 2
+    stop = [tok.im_end_id]
+
+    def expect(ids):
+        return pm.generate(cfg, w, ids, 5, stop_ids=stop)
+
+    # one text prompt: a single ChatML turn
+    ids = tok.encode(chatml("t9 t17 t40"))
+    assert ids == [1, 3, 9, 17, 40, 2, 1, 4]
+    r = eng.generate("t9 t17 t40")
+    assert r.tokens[:r.prompt_tokens] == ids and r.generated_ids == expect(ids)
+    assert r.text == tok.decode(r.generated_ids)
+    # a conversation: the history grows and every turn sends all of it
+    chat = eng.chat(system_prompt="t7 t8")
+    first = chat.send("t20 t21 t22")
+    msgs = [{"role": "system", "content": "t7 t8"}, {"role": "user", "content": "t20 t21 t22"}]
+    ids1 = tok.encode(chat_prompt(msgs, True))
+    assert ids1 == [1, 5, 7, 8, 2, 1, 3, 20, 21, 22, 2, 1, 4]
+    assert chat.last_result.generated_ids == expect(ids1) and first.role == "assistant"
+    assert first.content == tok.decode(expect(ids1))
+    pieces = list(chat.stream("t30"))
+    msgs += [{"role": "assistant", "content": first.content}, {"role": "user", "content": "t30"}]
+    ids2 = tok.encode(chat_prompt(msgs, True))
+    assert "".join(pieces) == tok.decode(expect(ids2)) == chat.last_message().content
+    assert [m.role for m in chat.history] == ["system", "user", "assistant", "user", "assistant"]
+    assert repr(chat) == "ChatSession(turns=2)"
+    chat.clear()
+    assert chat.history == [] and chat.last_message() is None
+    # without the markers the conversation is plain lines
+    assert chat_prompt(msgs[:2], False) == "System: t7 t8\nUser: t20 t21 t22\nAssistant: "
+    # a batch: one continuous batch, results in the prompts' order; its stream yields as requests end
+    prompts = ["t9 t17 t40", [11, 12, 13, 14, 15, 16, 17], "t50 t51"]
+    stats = eng.batch().process(prompts)
+    singles = [eng.generate(p) for p in prompts]
+    assert [b.result.generated_ids for b in stats.results] == [r.generated_ids for r in singles]
+    assert [b.index for b in stats.results] == [0, 1, 2] and stats.total_prompts == 3
+    assert stats.total_generated_tokens == sum(r.generated_tokens for r in singles) and stats.tokens_per_sec > 0
+    streamed = list(eng.batch().stream(prompts))
+    assert sorted(b.index for b in streamed) == [0, 1, 2]
+    for b in streamed:
+        assert b.result.generated_ids == singles[b.index].generated_ids
+        assert b.result.finish_reason == singles[b.index].finish_reason
+    assert eng.llm.runner.cache.used_pages() == [0]
+    # a folder without a tokenizer cannot chat
+    plain_folder = tiny.make_folder(str(tmp_path / "no_tok"), cfg, seed=61, dtype=torch.float32)
+    bare = MiniInfer(model_path=plain_folder, config=InferenceConfig(max_new_tokens=2, max_seq_len=64, dtype="float32",
+                                                                     max_running=1))
+    with pytest.raises(RuntimeError, match="tokenizer"):
+        bare.chat().send("hello")
+    assert bare.chat().history == []
+
+
 def test_sdk_subprocess_backend(folders):
     """``binary=``: every call runs the command-line program and reads its printed contract, as the
     reference's local backend does."""
@@ -287,3 +366,27 @@ def test_command_line_contract(folders):
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mini_infer"), "serve", "--model", folder],
                          capture_output=True, text=True)
     assert bad.returncode == 2 and "not part of this engine" in bad.stderr
+
+
+def test_command_line_with_text_and_the_chat_command(tmp_path):
+    """``--prompt TEXT`` wraps the text as one ChatML turn unless ``--raw``, and stops at the end-of-turn
+    marker; ``python -m mini_infer_sdk chat`` reads a line and answers it."""
+    cfg = tiny.CONFIGS["A"]
+    folder, w = _folder_with_tokenizer(tmp_path, cfg)
+    base = [sys.executable, os.path.join(ROOT, "bin", "mini_infer"), "generate", "--model", folder, "--prompt",
+            "t9 t17 t40", "--max-new-tokens", "5", "--greedy", "--dtype", "float32", "--max-seq-len", "64", "--json"]
+    wrapped = [1, 3, 9, 17, 40, 2, 1, 4]
+    for extra, ids in (([], wrapped), (["--raw"], [9, 17, 40])):
+        p = subprocess.run(base + extra, capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        lines = p.stdout.splitlines()
+        got = json.loads(lines[lines.index("--- end ---") + 2])["token_ids"]
+        assert got == pm.generate(cfg, w, ids, 5, stop_ids=[2]), extra
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    chat = subprocess.run([sys.executable, "-m", "mini_infer_sdk", "chat", "--model", folder, "--greedy",
+                           "--max-tokens", "4", "--dtype", "float32", "--system", "t7"],
+                          input="t20 t21\nexit\n", capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert chat.returncode == 0, chat.stderr[-2000:]
+    ids = [1, 5, 7, 2, 1, 3, 20, 21, 2, 1, 4]
+    words = " ".join(f"t{t}" for t in pm.generate(cfg, w, ids, 4, stop_ids=[2]) if t > 5)
+    assert f"assistant> {words}" in chat.stdout

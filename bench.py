@@ -210,6 +210,53 @@ def run_timeline(args):
     return 0
 
 
+def run_serving(args):
+    """A continuous-batching workload through ``LLM.generate``, in the manner of the reference's
+    ``benchmarks/bench_continuous.cpp`` (requests of mixed prompt lengths submitted at once, a fixed number of
+    new tokens each) with seeded synthetic token ids: throughput and time to first token, cold (the first
+    call captures its CUDA graphs) and warm."""
+    import torch
+    from mini_infer_b200.engine.defaults import DEFAULT_PAGE_SIZE
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.engine.loading import random_model
+    from mini_infer_b200.sampling import SamplingParams
+    model_name, named = SIZES[args.sizes]
+    cfg = dict(named)
+    full_layers = named["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers if args.layers > 0 else full_layers
+    model, rt = random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0")
+    g = torch.Generator().manual_seed(args.seed + 3)
+    n, new = args.serving, args.serving_new_tokens
+    lo, hi = args.serving_prompt_min, args.serving_prompt_max
+    lens = torch.randint(lo, hi + 1, (n,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (k,), generator=g).tolist() for k in lens]
+    ctx = hi + new + 16
+    llm = LLM(model, runtime=rt, max_seq_len=ctx, max_running=args.serving_max_running, max_tokens_per_step=2048,
+              prefill_chunk=2048, num_pages=args.serving_max_running * (ctx // DEFAULT_PAGE_SIZE + 1))
+    sp = SamplingParams(greedy=True, max_new_tokens=new)
+    llm.generate(prompts[:2], SamplingParams(greedy=True, max_new_tokens=4))       # library warm-up only
+    runs = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        t0 = time.time()
+        outs = llm.generate(prompts, sp)
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+        ttft = sorted(o.ttft for o in outs if o.ttft is not None)
+        h = llm.last_history
+        runs.append({"seconds": round(dt, 3), "out_tok_s": round(n * new / dt, 1),
+                     "total_tok_s": round((sum(lens) + n * new) / dt, 1),
+                     "ttft_ms_p50": round(1e3 * ttft[len(ttft) // 2], 1), "ttft_ms_max": round(1e3 * ttft[-1], 1),
+                     "steps": len(h), "steps_with_prompt_and_decode": sum(1 for s in h if s.prefill_tokens and s.decode_tokens),
+                     "graphs": len(llm.runner._graphs)})
+    print(json.dumps({"impl": "ours", "workload": "continuous batching, all requests submitted at once",
+                      "model": f"{model_name} layer sizes", "layers": cfg["num_hidden_layers"], "requests": n,
+                      "prompt_tokens": sum(lens), "prompt_len_range": [lo, hi], "new_tokens_each": new,
+                      "max_running": args.serving_max_running, "cold": runs[0], "warm": runs[-1],
+                      "data": "synthetic: random-init weights, seeded uniform-random token ids"}))
+    return 0
+
+
 def run_ours(args):
     import torch
     from mini_infer_b200.engine.llm import LLM, GPUExecutor
@@ -519,6 +566,13 @@ def main():
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one step as they run inside the engine (with --only decode or "
                          "--only prefill; --layers defaults to 4) instead of benchmarking")
+    ap.add_argument("--serving", type=int, default=0,
+                    help="instead of the benchmark line: this many requests of mixed prompt lengths through "
+                         "LLM.generate as one continuous batch (throughput and time to first token)")
+    ap.add_argument("--serving-new-tokens", type=int, default=128)
+    ap.add_argument("--serving-prompt-min", type=int, default=100)
+    ap.add_argument("--serving-prompt-max", type=int, default=2000)
+    ap.add_argument("--serving-max-running", type=int, default=64)
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     ap.add_argument("--reference-prefill-batch", type=int, default=1,
                     help="prompts the reference's scheduler prefills per iteration (its cuBLAS handles, one per "
@@ -534,6 +588,8 @@ def main():
         args.warmup = 3
     if args.timeline:
         return run_timeline(args)
+    if args.serving > 0:
+        return run_serving(args)
     return run_ours(args)
 
 

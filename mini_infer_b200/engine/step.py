@@ -346,6 +346,10 @@ class ModelRunner:
             fresh=d("fresh", B), kv_groups=views, states=self.state_tensors, scratch=self.scratch,
             host_q_start=first.tolist(), host_kv_len=kv_len.tolist(), host_state_slot=slots.tolist())
         ctx.rows_of_no_request = extra
+        single = counts == 1
+        lead = B if bool(single.all()) else int(np.argmin(single))
+        ctx.num_leading_decodes = lead
+        ctx.leading_decodes_max_kv_len = int(kv_len[:lead].max()) if lead else 0
         from ..parts.tuning import TUNING
         if self.rt.act == torch.bfloat16 and T <= TUNING.l2_prefetch_max_tokens:
             ctx.prefetch = self._prefetcher

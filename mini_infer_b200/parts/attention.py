@@ -130,11 +130,25 @@ class GQAttention(Mixer):
             a = F.decode_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len,
                                    ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"], splits, self.window,
                                    split=split)
-        elif self._tensor_core_prefill and F.prefill_attention_tc_supported(self.d, view.page_size):
-            a = F.prefill_attention_tc(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                       self.window)
         elif self._tensor_core_prefill:
-            a = F.prefill_attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
+            prefill = (F.prefill_attention_tc if F.prefill_attention_tc_supported(self.d, view.page_size)
+                       else F.prefill_attention)
+            n = ctx.num_leading_decodes
+            if (TUNING.mixed_step_decode_kernel_min_requests <= n < ctx.num_requests
+                    and "attn_part_o" in ctx.scratch and F.decode_attention_supported(self.d)):
+                # A prompt portion beside decoding requests: the requests that bring one token stand first.
+                # Their attention is a stream over their whole caches, which the split-KV kernel reads at
+                # the memory's speed; a prefill kernel would spend a 128-query tile on each of them.  Both
+                # kernels index the step's rows through q_start, so each takes its requests and all rows.
+                a = torch.empty_like(q)
+                split = F.decode_split_size()
+                F.decode_attention(q[:n], kc, vc, view.block_table[:n], ctx.q_start[:n + 1], ctx.kv_len[:n],
+                                   ctx.scratch["attn_part_o"], ctx.scratch["attn_part_ml"],
+                                   -(-ctx.leading_decodes_max_kv_len // split), self.window, out=a[:n], split=split)
+                prefill(q, kc, vc, view.block_table[n:], ctx.q_start[n:], ctx.kv_len[n:], ctx.max_q_len, self.window,
+                        out=a)
+            else:
+                a = prefill(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
         else:
             a = F.attention(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len, self.window)
         return linear(a.view(ctx.num_tokens, self.nh * self.d), self.w_o, torch.float32)

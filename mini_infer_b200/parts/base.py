@@ -182,6 +182,11 @@ class StepContext:
     prefetch_upcoming: Optional[Any] = None
     # launch this step's decode-sized kernels as programmatic dependents of the kernels before them
     dependent_launch: bool = False
+    # how many requests at the front of the step bring exactly one token (the scheduler puts decoding
+    # requests first), and the longest context among them: a mixer may serve them with its decode kernel
+    # and the prompt portions behind them with its prefill kernel
+    num_leading_decodes: int = 0
+    leading_decodes_max_kv_len: int = 0
     # the last rows of the step (one token each) belong to no request: they fill a captured batch up to its
     # size, are written nowhere and their logits are dropped
     rows_of_no_request: int = 0

@@ -64,6 +64,11 @@ class Tuning:
     # line instead of at its blocks' exit lost 5 to 8 % at batch 1 and 2: waiting blocks crowd the running ones.)
     dependent_launch_max_tokens: int = 8
 
+    # A step with a prompt portion beside decoding requests serves the decoding requests (they stand first)
+    # with the split-KV decode attention and the portion with the prefill attention, from this many decoding
+    # requests on (below, two more launches per layer cost more than the prefill kernel's wasted tiles).
+    mixed_step_decode_kernel_min_requests: int = 4
+
     # Decode steps are replayed from a pass captured per batch size.  Up to this size every batch size has its
     # own pass (the kernels of the smallest steps change with the size); above it sizes are rounded up to a
     # multiple of 4 (to 32) or 8 and the step is filled up with rows of no request, so that a batch that grows

@@ -103,3 +103,60 @@ def test_decode_batches_filled_up_to_a_captured_size(tmp_path, dtype):
         assert set(eager) == set(got)
         for key in got:
             assert torch.equal(got[key], eager[key]), key
+
+
+@pytest.mark.parametrize("name,page_size", [("D", 16), ("E", 16), ("E", 32), ("D", 4)])
+def test_prompt_portions_behind_decoding_requests_take_two_attention_kernels(tmp_path, name, page_size, monkeypatch):
+    """Six requests decode while a seventh and an eighth arrive in portions: in such a step the decoding
+    requests stand first and are served by the split-KV decode attention, the portions by a prefill kernel
+    (tcgen05, or mma.sync where the page size is not one the tcgen05 kernel takes), both over the same
+    rows.  Every row against the plain model; in the steps with fewer than four decoding requests the
+    prefill kernel serves all."""
+    from mini_infer_b200.ops import functional as F
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=67, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    g = torch.Generator().manual_seed(11)
+    lens = {"a": 150, "b": 41, "c": 97, "d": 64, "e": 33, "f": 120, "late": 170, "later": 75}
+    reqs = {rid: torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for rid, n in lens.items()}
+    steps, fed = [], {}
+    for rid in "abcdef":
+        n = lens[rid] - 14
+        steps.append({"entries": [(rid, reqs[rid][:n], [n - 1])], "end": []})
+        fed[rid] = n
+    portions = {"late": [60, 2, 70, 38], "later": [40, 35]}
+    fed.update(late=0, later=0)
+    for i in range(14):
+        entries = [(rid, [reqs[rid][fed[rid]]], [0]) for rid in "abcdef" if not (rid in "ab" and i >= 11)]
+        for rid in ("late", "later"):
+            if portions[rid] and (rid == "late" or i >= 5):
+                k = portions[rid].pop(0)
+                entries.append((rid, reqs[rid][fed[rid]:fed[rid] + k], [0, k - 1]))
+        for rid, toks, _ in entries:
+            fed[rid] += len(toks)
+        steps.append({"entries": entries, "end": [rid for rid, _, _ in entries if fed[rid] == lens[rid]]})
+    # the two requests that paused: their last three tokens, two requests to a step
+    for i in range(3):
+        steps.append({"entries": [(rid, [reqs[rid][fed[rid]]], [0]) for rid in "ab"], "end": []})
+        for rid in "ab":
+            fed[rid] += 1
+    steps[-1]["end"] = ["a", "b"]
+    assert all(fed[rid] == lens[rid] for rid in lens), fed
+    calls = {"decode": 0, "prefill": 0}
+    for face, key in (("decode_attention", "decode"), ("prefill_attention_tc", "prefill"), ("prefill_attention", "prefill")):
+        def counted(*a, _fn=getattr(F, face), _key=key, **k):
+            calls[_key] += 1
+            return _fn(*a, **k)
+        monkeypatch.setattr(F, face, counted)
+    runner = make_runner(folder, "bfloat16", page_size=page_size, num_pages=1100 // page_size, max_requests=8,
+                         max_tokens=256, max_context=256, cuda_graphs=False)
+    run_and_compare(runner, steps, cfg, w, reqs, "bfloat16", 3e-2)
+    layers = cfg["num_hidden_layers"]
+    mixed = sum(1 for st in steps if any(len(t) > 1 for _, t, _ in st["entries"]) and
+                sum(1 for _, t, _ in st["entries"] if len(t) == 1) >= 4)
+    assert mixed == 6
+    if F.decode_attention_supported(cfg["hidden_size"] // cfg["num_attention_heads"]):
+        decode_only = sum(1 for st in steps if all(len(t) == 1 for _, t, _ in st["entries"]))
+        assert calls["decode"] == (mixed + decode_only) * layers
+        assert calls["prefill"] == (len(steps) - decode_only) * layers
+    assert not any(runner.cache.used_pages())

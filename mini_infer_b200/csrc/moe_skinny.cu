@@ -456,6 +456,8 @@ int mi_grouped_gemm_skinny(const void* A, const int* gather, const void* W, cons
 
 // Largest step (in tokens) of the pair-indexed grouped product.
 int mi_grouped_gemm_skinny_pairs_max_tokens() { return PAIR_MAX_TOKENS; }
+// Steps of up to this many tokens take the form whose blocks split the inner dimension over their warps.
+int mi_grouped_gemm_skinny_pairs_split_inner_max_tokens() { return PAIR_SPLITK_MAX_TOKENS; }
 
 // The decode-sized grouped product without a permutation.  topk_idx [T*K]: expert of pair t*K+k (each
 // token names an expert at most once).  mode 1: A [T, Kd], C bfloat16 [T*K, Nout] = SwiGLU pair of

@@ -739,6 +739,12 @@ def skinny_pairs_max_tokens() -> int:
     return int(library().mi_grouped_gemm_skinny_pairs_max_tokens())
 
 
+def skinny_pairs_split_inner_max_tokens() -> int:
+    """Steps of up to this many tokens take the form of :func:`grouped_gemm_skinny_pairs` whose blocks own
+    16 features and split the inner dimension over their warps."""
+    return int(library().mi_grouped_gemm_skinny_pairs_split_inner_max_tokens())
+
+
 def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.Tensor,
                               swiglu_pair: bool) -> torch.Tensor:
     """The decode-sized grouped product without a permutation: row ``t*K + k`` of the result

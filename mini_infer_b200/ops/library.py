@@ -85,6 +85,8 @@ def library() -> ctypes.CDLL:
     lib.mi_set_dependent_launch.restype = c_int
     lib.mi_moe_norm_route_small_takes.argtypes = [c_int, c_int, c_int, c_int]
     lib.mi_moe_norm_route_small_takes.restype = c_int
+    lib.mi_grouped_gemm_skinny_pairs_split_inner_max_tokens.argtypes = []
+    lib.mi_grouped_gemm_skinny_pairs_split_inner_max_tokens.restype = c_int
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.argtypes = []
     lib.mi_grouped_gemm_skinny_pairs_max_tokens.restype = c_int
     lib.mi_attn_prefill_tc_supported.argtypes = [I, I]

@@ -179,8 +179,8 @@ class SparseMoE(FeedForward):
         if ctx.prefetch is not None and self.sI > 0:
             # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
             ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
-        if (rms is not None and self._skinny and T <= min(self._pairs_max, TUNING.shared_expert_fork_after_routing_max_tokens)
-                and T * self.K <= TUNING.expert_skinny_rows_per_expert * self.E and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
+        if (rms is not None and T <= TUNING.shared_expert_fork_after_routing_max_tokens and self._by_pair(T)
+                and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
                 and (delta is None or isinstance(delta, torch.Tensor))):
             x, idx, w, gate, probs = F.moe_norm_route_small(
                 hidden, delta, rms[0], rms[1], self.rt.act, self.w_router, self.w_shared_gate, self.K,
@@ -188,12 +188,30 @@ class SparseMoE(FeedForward):
             return self._run(x, ctx, (idx, w, gate, probs))
         return super().forward_from_residual(hidden, delta, norm, ctx)
 
+    def _few_rows_per_expert(self, T: int) -> bool:
+        """Whether a step of T tokens takes the decode-sized expert products (every used expert's weights
+        read once into mma.sync fragments) rather than the tcgen05 product: the smallest steps always
+        (their form splits the inner dimension over a block's warps and streams at the memory's speed),
+        larger ones up to the tuned number of rows per expert; without the tcgen05 product (inner sizes it
+        does not take) up to 8 rows per expert, beyond which re-reading weights per 16 rows costs more than
+        the plain kernel."""
+        if not self._skinny:
+            return False
+        if T <= F.skinny_pairs_split_inner_max_tokens() and T <= self._pairs_max:
+            return True
+        rows = TUNING.expert_skinny_rows_per_expert if self._tc else 8
+        return T * self.K <= rows * self.E
+
+    def _by_pair(self, T: int) -> bool:
+        """... and without a permutation (result rows indexed by (token, slot) pair)."""
+        return T <= self._pairs_max and self._few_rows_per_expert(T)
+
     def _run(self, x: torch.Tensor, ctx: StepContext, routed) -> WeightedRowSum:
         T = x.shape[0]
         shared = side = inv_perm = None
         overlap = self.sI > 0 and TUNING.shared_expert_overlap
         n = T * self.K
-        if self._skinny and T <= self._pairs_max and n <= TUNING.expert_skinny_rows_per_expert * self.E:
+        if self._by_pair(T):
             # decode-sized step: routing in one launch, no permutation; every used expert's weights
             # are read once and result rows are indexed by (token, slot) pair
             fork_first = T > TUNING.shared_expert_fork_after_routing_max_tokens
@@ -224,7 +242,7 @@ class SparseMoE(FeedForward):
                 idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
                                                    want_probs=self.keep_routing)
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
-            if self._skinny and n <= TUNING.expert_skinny_rows_per_expert * self.E:
+            if self._few_rows_per_expert(T):
                 # a few rows per expert: bound by reading each used expert once
                 act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
                 y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)

@@ -22,11 +22,13 @@ class Tuning:
     # rises steadily across the threshold (no cliff between 8 and 16 tokens).
     dense_skinny_max_tokens: int = 8
 
-    # Grouped expert products: up to this many rows per expert on average (tokens * top_k / experts) the
-    # decode-sized mma.sync kernel reads every used expert once; above it the tcgen05 kernel's row tiles
-    # pay.  Checked at 60 experts with top-4 routing by decoding at batch 16, 32, 64 and 128 (1 to 8.5 rows
-    # per expert): throughput rises steadily, no cliff where the kernels change.
-    expert_skinny_rows_per_expert: int = 8
+    # Grouped expert products of steps above 8 tokens: up to this many rows per expert on average (tokens *
+    # top_k / experts) the decode-sized mma.sync kernel reads every used expert once into fragments; above it
+    # the persistent tcgen05 kernel, whose TMA ring keeps four times as many bytes in flight, streams the same
+    # weights faster even though its tiles are nearly empty.  At 60 experts with top-4 routing, 8 against 1:
+    # batch 16 +2.3 %, 24 +5 %, 32 +6.4 %, 64 +3.5 %, 100 +9.7 %; at 9, 12 and 15 tokens (where 1 keeps the
+    # mma.sync kernel) within 2 % either way.
+    expert_skinny_rows_per_expert: int = 1
 
     # The shared expert runs on a second stream beside the routed experts: in decode-sized steps every
     # kernel is short, and in prefill its library products are bound by the tensor cores while the grouped
@@ -70,17 +72,17 @@ class Tuning:
     mixed_step_decode_kernel_min_requests: int = 4
 
     # Decode steps are replayed from a pass captured per batch size.  Up to this size every batch size has its
-    # own pass (the kernels of the smallest steps change with the size); above it sizes are rounded up to a
-    # multiple of 4 (to 32) or 8 and the step is filled up with rows of no request, so that a batch that grows
-    # and shrinks request by request captures a handful of passes, not one per size (48 requests of 100-2,000
-    # prompt tokens and 128 new ones through LLM.generate, cold: 2.59 s with a pass per size, of which 1.2 s
-    # were 29 captures).
-    decode_graph_exact_batch_max: int = 8
+    # own pass (the kernels of the smallest steps change with the size, and a request more means up to top_k
+    # experts more to read: 9 requests run as 12 would take 5.1 instead of 4.2 ms); above it sizes are rounded
+    # up to a multiple of 2 (to 32), 4 (to 64) or 8 and the step is filled up with rows of no request, which
+    # costs a few per cent of a step at most and saves a capture (30-50 ms) per size that a batch passes
+    # through while it grows and shrinks request by request.
+    decode_graph_exact_batch_max: int = 16
 
     def decode_graph_batch(self, num_requests: int) -> int:
         if num_requests <= self.decode_graph_exact_batch_max:
             return num_requests
-        step = 4 if num_requests <= 32 else 8
+        step = 2 if num_requests <= 32 else (4 if num_requests <= 64 else 8)
         return -(-num_requests // step) * step
 
     def decode_split(self, num_requests: int, default: int) -> int:

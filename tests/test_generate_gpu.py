@@ -149,13 +149,16 @@ def test_generation_as_the_product_runs_it_against_the_plain_model(tmp_path, nam
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_generation_of_eleven_requests_on_batches_filled_up_to_a_captured_size(tmp_path, dtype):
+def test_generation_of_eleven_requests_on_batches_filled_up_to_a_captured_size(tmp_path, dtype, monkeypatch):
     """Eleven requests with different numbers of new tokens: the decode steps of 11, 10 and 9 requests are
     replays of the pass captured for 12 (filled up with rows of no request), launched ahead of the host's
     tokens as in serving; every row of logits a token was sampled from against the plain model."""
     from engine_harness import GenerationObserver, compare_generation
     from mini_infer_b200.engine.llm import LLM
     from mini_infer_b200.sampling import SamplingParams
+    # a coarse ladder of captured sizes for the test: every size to 8, multiples of 4 above
+    from mini_infer_b200.parts.tuning import Tuning
+    monkeypatch.setattr(Tuning, "decode_graph_batch", lambda self, n: n if n <= 8 else -(-n // 4) * 4)
     cfg = tiny.CONFIGS["D"]
     folder = tiny.make_folder(str(tmp_path), cfg, seed=59, dtype=torch.bfloat16)
     w = tiny.read_weights(folder)

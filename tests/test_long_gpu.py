@@ -77,11 +77,14 @@ def test_window_group_gives_pages_back_while_decoding(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_decode_batches_filled_up_to_a_captured_size(tmp_path, dtype):
+def test_decode_batches_filled_up_to_a_captured_size(tmp_path, dtype, monkeypatch):
     """Decode steps of 11, 9 and 5 requests: above 8 requests the step is filled up with rows of no request
     to the next captured batch size (12 here), so 11 and 9 requests replay the same pass.  The rows of the
     requests must be the plain model's, the filling rows must write nothing (pages, other requests' keys),
     and in float32 the logits are bit for bit those of the same trace launched eagerly without any filling."""
+    # a coarse ladder of captured sizes for the test: every size to 8, multiples of 4 above
+    from mini_infer_b200.parts.tuning import Tuning
+    monkeypatch.setattr(Tuning, "decode_graph_batch", lambda self, n: n if n <= 8 else -(-n // 4) * 4)
     cfg = tiny.CONFIGS["D"]
     folder = tiny.make_folder(str(tmp_path), cfg, seed=47, dtype=torch.bfloat16)
     w = tiny.read_weights(folder)

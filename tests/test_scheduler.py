@@ -252,3 +252,15 @@ def test_look_ahead_with_a_pool_that_runs_out_still_finishes_right():
         assert done[i].generated == expected_tokens(range(1, 6 + i), 7)
     assert s.num_preemptions >= 1
     assert ex.cache.free_pages() == [6]
+
+
+def test_captured_batch_sizes_form_a_ladder():
+    """Every size to 16 has a captured pass of its own; above, sizes are rounded up in steps of 2, 4 and 8,
+    never down, never by more than a step."""
+    from mini_infer_b200.parts.tuning import Tuning
+    t = Tuning()
+    sizes = [t.decode_graph_batch(n) for n in range(1, 200)]
+    assert sizes[:16] == list(range(1, 17))
+    assert all(n <= s < n + 8 for n, s in zip(range(1, 200), sizes)) and sizes == sorted(sizes)
+    assert t.decode_graph_batch(17) == 18 and t.decode_graph_batch(33) == 36 and t.decode_graph_batch(65) == 72
+    assert len(set(sizes[:128])) == 16 + 8 + 8 + 8

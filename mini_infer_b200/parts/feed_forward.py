@@ -231,7 +231,8 @@ class SparseMoE(FeedForward):
                 # while the experts' rows are summed and normalised, the next layer's first weights arrive
                 ctx.prefetch(ctx.prefetch_upcoming)
         else:
-            if overlap:
+            fork_first = T > TUNING.shared_expert_fork_after_permutation_max_tokens
+            if overlap and fork_first:
                 side, shared = self._fork_shared_expert(x)
             # (the float32 path routes every step with the same kernel: same bits however the work is cut)
             if T <= self._route_small_max and self.rt.act == torch.bfloat16:
@@ -242,6 +243,8 @@ class SparseMoE(FeedForward):
                 idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
                                                    want_probs=self.keep_routing)
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
+            if overlap and not fork_first:
+                side, shared = self._fork_shared_expert(x)
             if self._few_rows_per_expert(T):
                 # a few rows per expert: bound by reading each used expert once
                 act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)

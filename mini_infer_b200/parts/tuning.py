@@ -41,6 +41,12 @@ class Tuning:
     # In the smallest steps the routing is a chain of short dependent loads that a concurrent weight
     # stream slows down, so there the shared expert is forked after the routing, not before it.
     shared_expert_fork_after_routing_max_tokens: int = 8
+    # The same for larger decode steps, whose expert rows are sorted (routing and permutation in one launch):
+    # up to this many tokens the shared expert's library products start after that launch, which they would
+    # slow down, and run beside the routed products.  128 against 0 (always before): batch 16 +0.3 %,
+    # 24 +1.5 %, 32 +1.1 %, 64 +2.5 %, 128 +0.4 %.  A prompt portion keeps the order "shared expert first":
+    # its first library product is as long as routing, permutation and row gather together.
+    shared_expert_fork_after_permutation_max_tokens: int = 128
 
     # Split-KV decode attention: keys per split by the number of requests in the step, as (up to this
     # many requests, keys per split) pairs, then the kernel's default of 512.  One or two requests alone

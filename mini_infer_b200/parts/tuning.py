@@ -18,9 +18,11 @@ from typing import Tuple
 class Tuning:
     # Dense products (o_proj, shared expert, dense MLP, output head) of steps with at most this many tokens
     # run on the engine's own decode kernel, which streams the weights once with 16 features per block;
-    # above it the library product is used.  Checked by decoding at batch 2, 4, 8, 16 and 32: throughput
-    # rises steadily across the threshold (no cliff between 8 and 16 tokens).
-    dense_skinny_max_tokens: int = 8
+    # above it the library product is used.  The four thresholds of the "smallest steps" (this one, the shared
+    # expert forked after the routing, the L2 hints and dependent launch) moved together from 8 to 15 tokens:
+    # batch 9 +6 % (a step of 9 had been slower per token than a step of 8), 12 +6 %, 15 +4 %; at 16 tokens
+    # and above, where the expert products change to the tcgen05 kernel, the same settings lose 4 to 9 %.
+    dense_skinny_max_tokens: int = 15
 
     # Grouped expert products of steps above 8 tokens: up to this many rows per expert on average (tokens *
     # top_k / experts) the decode-sized mma.sync kernel reads every used expert once into fragments; above it
@@ -40,7 +42,7 @@ class Tuning:
     shared_expert_priority_stream_min_tokens: int = 128
     # In the smallest steps the routing is a chain of short dependent loads that a concurrent weight
     # stream slows down, so there the shared expert is forked after the routing, not before it.
-    shared_expert_fork_after_routing_max_tokens: int = 8
+    shared_expert_fork_after_routing_max_tokens: int = 15
     # The same for larger decode steps, whose expert rows are sorted (routing and permutation in one launch):
     # up to this many tokens the shared expert's library products start after that launch, which they would
     # slow down, and run beside the routed products.  128 against 0 (always before): batch 16 +0.3 %,
@@ -63,14 +65,14 @@ class Tuning:
 
     # Steps of at most this many tokens ask L2 for the next dense weights (q/k/v, o_proj, shared expert)
     # on a second stream while a latency-bound kernel runs (0 = off).
-    l2_prefetch_max_tokens: int = 8
+    l2_prefetch_max_tokens: int = 15
 
     # Steps of at most this many tokens launch their kernels as programmatic dependents of the kernels before
     # them (0 = off): a kernel's blocks are placed while the one before it drains.  At A2.7B sizes: batch 1
     # +3.4 %, 2 +0.6 %, 4 +2.1 %, 8 +1.6 %; nothing either way from 16 tokens on, where library products stand
     # between the kernels that are written for it.  (Letting the next kernel's blocks in at a kernel's first
     # line instead of at its blocks' exit lost 5 to 8 % at batch 1 and 2: waiting blocks crowd the running ones.)
-    dependent_launch_max_tokens: int = 8
+    dependent_launch_max_tokens: int = 15
 
     # A step with a prompt portion beside decoding requests serves the decoding requests (they stand first)
     # with the split-KV decode attention and the portion with the prefill attention, from this many decoding

@@ -179,6 +179,39 @@ class LLM:
             sched.submit(r)
         return sched, reqs
 
+    def warm_up(self, batch_sizes: Optional[Sequence[int]] = None) -> int:
+        """Capture the decode passes ahead of the first request: one step of ``B`` one-token requests for every
+        captured batch size up to ``max_running`` (or for ``batch_sizes``), in the smallest context bucket.
+        A capture costs tens of milliseconds, which the first requests of a serving process would otherwise
+        wait for whenever their batch reaches a new size.  Returns the number of passes captured.  The
+        requests it uses are released again; nothing of them stays in the cache."""
+        runner = self.runner
+        if not runner.cuda_graphs:
+            return 0
+        limit = min(runner.max_requests, runner.max_tokens)
+        if batch_sizes is None:
+            sizes = sorted({runner._graph_batch(b) for b in range(1, limit + 1)})
+        else:
+            sizes = sorted({runner._graph_batch(int(b)) for b in batch_sizes if 1 <= int(b) <= limit})
+        sizes = sizes[:max(0, runner.max_context - 1)]       # the first request takes part in every step
+        before = len(runner._graphs)
+        rids = [("warm-up", i) for i in range(max(sizes, default=0))]
+        done: List = []
+        try:
+            for rid in rids:
+                runner.add_request(rid)
+                done.append(rid)
+            if rids:
+                runner.step([StepEntry(rid, [0], []) for rid in rids])          # a first token each
+            for b in sizes:
+                runner.step([StepEntry(rid, [0], [0]) for rid in rids[:b]])     # the captured decode step
+        except OutOfPages:
+            pass                                              # a pool too small for this many requests: as far as it went
+        finally:
+            for rid in done:
+                runner.release(rid)
+        return len(runner._graphs) - before
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[GenerationOutput]:
         """Token ids in, token ids out; request ``i`` samples from random stream ``i``."""

@@ -309,6 +309,11 @@ class MiniInfer:
     def generate(self, prompt: Prompt, config: Optional[InferenceConfig] = None) -> GenerationResult:
         return self.generate_ids([prompt], config)[0]
 
+    def warm_up(self) -> int:
+        """Capture the decode passes of every batch size ahead of the first request (in-process backend only;
+        see ``LLM.warm_up``).  Returns how many were captured."""
+        return self.llm.warm_up() if self.llm is not None else 0
+
     def chat(self, system_prompt: Optional[str] = None, config: Optional[InferenceConfig] = None) -> ChatSession:
         return ChatSession(self, system_prompt=system_prompt, config=config)
 

@@ -393,3 +393,24 @@ def test_command_line_with_text_and_the_chat_command(tmp_path):
     ids = [1, 5, 7, 2, 1, 3, 20, 21, 2, 1, 4]
     words = " ".join(f"t{t}" for t in pm.generate(cfg, w, ids, 4, stop_ids=[2]) if t > 5)
     assert f"assistant> {words}" in chat.stdout
+
+
+def test_warm_up_captures_the_decode_passes_ahead(folders):
+    """``LLM.warm_up`` captures one pass per captured batch size; generation afterwards replays them, captures
+    nothing more in the same context bucket, and gives the tokens it gives without a warm-up."""
+    from mini_infer_b200.engine.llm import LLM
+    from mini_infer_b200.sampling import SamplingParams
+    folder, cfg, w = folders["A"]
+    cases = [clear_prompt(cfg, w, n, 100 * n, 6) for n in (5, 11, 17)]
+    sp = SamplingParams(greedy=True, max_new_tokens=6)
+    llm = LLM(folder, dtype="float32", max_seq_len=128, max_running=20, max_tokens_per_step=64)
+    captured = llm.warm_up()
+    assert captured == 16 + 2 == len(llm.runner._graphs)                   # 1..16, 18, 20
+    assert llm.runner.cache.used_pages() == [0] and llm.warm_up() == 0
+    llm.runner.cache.check_invariants()
+    outs = llm.generate([c[0] for c in cases], sp)
+    assert [o.token_ids for o in outs] == [c[1] for c in cases]
+    assert len(llm.runner._graphs) == captured and llm.runner.graph_replays > captured
+    small = LLM(folder, dtype="float32", max_seq_len=128, max_running=4, max_tokens_per_step=64, num_pages=3)
+    assert small.warm_up() == 0 and small.runner.cache.used_pages() == [0]     # too few pages: nothing happens
+    assert small.warm_up([1, 2]) == 2

@@ -23,7 +23,7 @@ def chat_loop(args) -> int:
                                                   seed=args.seed))
     engine = MiniInfer(model_path=args.model, config=cfg)
     chat = engine.chat(system_prompt=args.system)
-    print(f"mini-infer chat ({engine}). Type 'exit' to quit.")
+    print(f"chat with {engine.model_name} ({args.dtype}); an empty line or 'exit' ends it")
     while True:
         try:
             user = input("user> ").strip()

@@ -165,3 +165,30 @@ def test_prompt_portions_behind_decoding_requests_take_two_attention_kernels(tmp
         assert calls["decode"] == (mixed + decode_only) * layers
         assert calls["prefill"] == (len(steps) - decode_only) * layers
     assert not any(runner.cache.used_pages())
+
+
+@pytest.mark.parametrize("name,seed", [("D", 1), ("E", 2)])
+def test_random_trace_of_24_live_requests_replayed_and_launched_eagerly(tmp_path, name, seed):
+    """Forty requests, up to 24 live at a time, portions beside decoded tokens, requests sitting steps out:
+    the decode steps (1 to 24 requests, above 16 filled up to an even size) replayed from captured passes
+    give what the same trace gives launched kernel by kernel: bit for bit in float32, and in bfloat16 too
+    (the same kernels in the same order); the bfloat16 rows against the plain model as well."""
+    cfg = tiny.CONFIGS[name]
+    folder = tiny.make_folder(str(tmp_path), cfg, seed=71, dtype=torch.bfloat16)
+    w = tiny.read_weights(folder)
+    g = torch.Generator().manual_seed(100 + seed)
+    lens = torch.randint(20, 150, (40,), generator=g).tolist()
+    reqs = {f"q{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate(lens)}
+    steps = traces.mixed(reqs, max_live=24, seed=seed, decode_tail=18, max_portion=40)
+    sizes = {len(st["entries"]) for st in steps if all(len(t) == 1 for _, t, _ in st["entries"])}
+    assert max(sizes) > 16 and any(n % 2 for n in sizes if n > 16)
+    kw = dict(page_size=16, num_pages=400, max_requests=24, max_tokens=1024, max_context=256)
+    for dtype in ("float32", "bfloat16"):
+        replayed = make_runner(folder, dtype, cuda_graphs=True, **kw)
+        a = run_trace(replayed, steps)
+        b = run_trace(make_runner(folder, dtype, cuda_graphs=False, **kw), steps)
+        assert replayed.graph_replays > 0 and not any(key[0] % 2 for key in replayed._graphs if key[0] > 16)
+        assert set(a) == set(b) and len(a) == sum(lens)
+        for key in a:
+            assert torch.equal(a[key], b[key]), (dtype, key)
+    run_and_compare(make_runner(folder, "bfloat16", **kw), steps, cfg, w, reqs, "bfloat16", 3e-2)

@@ -257,7 +257,12 @@ class Qwen2MoeConfig:
                 raise ConfigError("ModelConfig: hidden_size not divisible by num_attention_heads")
             head_dim = hidden // heads
         inter = _get_int(j, "intermediate_size", 0)
-        n_exp = _get_int(j, "num_experts", 0)
+        # the number of experts under the names that the reference reads one after the other
+        # (src/model/model_config.cpp:95-105)
+        n_exp = 0
+        for key in ("num_experts", "num_local_experts", "n_routed_experts"):
+            if n_exp == 0:
+                n_exp = _get_int(j, key, 0)
         moe_inter = _get_int(j, "moe_intermediate_size", 0)
         if n_exp > 0 and moe_inter == 0:
             moe_inter = inter  # src/model/model_config.cpp:108-110

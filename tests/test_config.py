@@ -32,6 +32,16 @@ def test_tolerant_number_forms():
     assert c.hidden_size == 64 and c.num_hidden_layers == 2 and c.rms_norm_eps == 1e-6
 
 
+def test_number_of_experts_under_its_other_names():
+    """The reference takes the first of num_experts, num_local_experts, n_routed_experts that is not zero
+    (src/model/model_config.cpp:95-105)."""
+    j = {k: v for k, v in tiny.CONFIG_B.items() if k != "num_experts"}
+    n = tiny.CONFIG_B["num_experts"]
+    assert Qwen2MoeConfig.from_json_dict(dict(j, num_local_experts=n)).num_experts == n
+    assert Qwen2MoeConfig.from_json_dict(dict(j, n_routed_experts=n)).num_experts == n
+    assert Qwen2MoeConfig.from_json_dict(dict(j, num_experts=n, num_local_experts=n + 1)).num_experts == n
+
+
 def test_sparse_and_window_rules():
     b = Qwen2MoeConfig.from_json_dict(tiny.CONFIG_B)
     assert [b.layer_is_sparse(i) for i in range(3)] == [False, True, False]

@@ -235,7 +235,8 @@ class SparseMoE(FeedForward):
             if overlap and fork_first:
                 side, shared = self._fork_shared_expert(x)
             # (the float32 path routes every step with the same kernel: same bits however the work is cut)
-            if T <= self._route_small_max and self.rt.act == torch.bfloat16:
+            if T <= min(self._route_small_max, TUNING.route_with_permutation_one_launch_max_tokens) \
+                    and self.rt.act == torch.bfloat16:
                 idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
                     want_probs=self.keep_routing)

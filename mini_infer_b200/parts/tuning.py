@@ -74,6 +74,12 @@ class Tuning:
     # line instead of at its blocks' exit lost 5 to 8 % at batch 1 and 2: waiting blocks crowd the running ones.)
     dependent_launch_max_tokens: int = 15
 
+    # Routing with the permutation as one launch (the last block builds the permutation) up to this many
+    # tokens; above, logits kernel, selection kernel and permutation kernel (in isolation 18.5 against 30.8 us
+    # at 128 tokens).  15 against 128, with the shared expert started after the routing: batch 16 +0.4 %,
+    # 32 +1.1 %, 64 +0.2 %, 100 +0.2 %, 128 +1.0 %.
+    route_with_permutation_one_launch_max_tokens: int = 15
+
     # A step with a prompt portion beside decoding requests serves the decoding requests (they stand first)
     # with the split-KV decode attention and the portion with the prefill attention, from this many decoding
     # requests on (below, two more launches per layer cost more than the prefill kernel's wasted tiles).
